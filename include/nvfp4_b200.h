@@ -1,0 +1,123 @@
+/*
+ * C ABI of libnvfp4_b200.so: NVFP4 ScaleSweep quantization and the NVFP4
+ * block-scaled GEMM for NVIDIA B200 (sm_100a).
+ *
+ * Every pointer is a DEVICE pointer unless its name ends in `_host`.  Launches
+ * are asynchronous on `stream` (a cudaStream_t passed as void*; NULL = the
+ * legacy default stream).  No call synchronises the device, copies to the host
+ * or allocates memory.  Return value: 0 = ok, < 0 = NVFP4_ERR_* (nothing was
+ * launched), > 0 = a cudaError_t reported by the launch.
+ *
+ * The "replaces" notes name the interface of efsotr/nvfp4quant_test (paths
+ * inside that project) or of vllm 0.22.0, which that project calls.
+ */
+#ifndef NVFP4_B200_H_
+#define NVFP4_B200_H_
+
+#include <stddef.h>
+#include <stdint.h>
+
+#ifdef __cplusplus
+extern "C" {
+#endif
+
+enum {
+    NVFP4_OK = 0,
+    NVFP4_ERR_NULL_POINTER = -1,
+    NVFP4_ERR_BAD_SHAPE = -2,    /* n or padded_n not a multiple of 16, padded_n < n, K % 64, ... */
+    NVFP4_ERR_BAD_ENUM = -3,     /* unknown variant / dtype / implementation */
+    NVFP4_ERR_MISALIGNED = -4,   /* a pointer is not aligned as documented */
+    NVFP4_ERR_BAD_RANGE = -5,    /* upper < lower or more than 64 candidates */
+    NVFP4_ERR_WORKSPACE = -6,    /* workspace too small */
+    NVFP4_ERR_UNSUPPORTED = -7,
+    NVFP4_ERR_TOO_LARGE = -8
+};
+
+enum { NVFP4_VARIANT_MSE = 0, NVFP4_VARIANT_WEIGHTED = 1, NVFP4_VARIANT_AMAX = 2 };
+enum { NVFP4_DT_BF16 = 0, NVFP4_DT_F16 = 1, NVFP4_DT_F32 = 2 };
+
+/*
+ * Quantize x[m, n] (row-major, contiguous) to packed E2M1 codes and one E4M3
+ * scale per 16 elements.
+ *
+ *   variant   MSE:      sweep raw E4M3 codes base+lower..base+upper around
+ *                       base = RNE_E4M3(amax/6), pick the least fp32 squared error,
+ *                       lowest raw code on ties.
+ *                       replaces kernels/kernel_ScaleSweep_MSE.py:380-413
+ *                       (scalesweep_mse_nvfp4_quant_out) and the Triton kernel :271-377.
+ *             WEIGHTED: same with per-column weights importance[n] and a
+ *                       floor-rounded base.
+ *                       replaces kernels/kernel_ScaleSweep.py:436-480 and :290-416.
+ *             AMAX:     scale = E4M3(gs_inv * amax/6), no sweep.
+ *                       replaces vllm `_C::scaled_fp4_quant.out`
+ *                       (vllm/_custom_ops.py:1600-1665; call site bench.py:118-125).
+ *   x         16-byte aligned; x_dtype one of NVFP4_DT_*.
+ *   importance  n floats (WEIGHTED only, else may be NULL).
+ *   gs_inv    one float on the device: 1 / global_scale.
+ *   codes     uint8 [m, padded_n/2], 8-byte aligned; byte j of a row holds
+ *             element 2j in its low nibble, 2j+1 in its high nibble.
+ *   scales    swizzled != 0: uint8 [round_up(m,128) * round_up(padded_n/16, 4)] in the
+ *             128x4 tile order of the tcgen05 scale-factor layout
+ *             (kernels/kernel_vllm.py:9-26); rows >= m and columns >= padded_n/16
+ *             are written as 0.  4-byte aligned.
+ *             swizzled == 0: uint8 [m, padded_n/16] row-major.
+ *   padded_n  >= n, multiple of 16; columns n..padded_n quantize as zeros.
+ *   lower, upper  candidate window (ignored by AMAX); the reference uses -3..7
+ *             (MSE) and -8..7 (WEIGHTED).
+ */
+int nvfp4_quant_launch(int variant, const void* x, int x_dtype, const float* importance,
+                       const float* gs_inv, uint8_t* codes, uint8_t* scales, int64_t m, int64_t n,
+                       int64_t padded_n, int lower, int upper, int swizzled, void* stream);
+
+/* Same, choosing the kernel body: 0 = default, 1 = scalar (one candidate at a
+ * time, the plainest transcription), 2 = packed f32x2 (two candidates per
+ * instruction).  All give identical bytes; exposed for testing and timing. */
+int nvfp4_quant_launch_impl(int impl, int variant, const void* x, int x_dtype, const float* importance,
+                            const float* gs_inv, uint8_t* codes, uint8_t* scales, int64_t m, int64_t n,
+                            int64_t padded_n, int lower, int upper, int swizzled, void* stream);
+
+/*
+ * out[0] = amax(|x|) / (6 * fp8_max), out[1] = 1 / out[0]  over numel elements.
+ * replaces helper.py:96-100 (get_nvfp4_global_scale).
+ * `scratch` = 2 uint32 that must be zero before the first call; the kernel
+ * leaves them zero again, so one scratch serves any number of calls issued in
+ * stream order.  Concurrent calls need separate scratch.
+ */
+int nvfp4_global_scale_launch(const void* x, int x_dtype, int64_t numel, float fp8_max, float* out,
+                              uint32_t* scratch, void* stream);
+
+/*
+ * out[M, N] (bf16, row-major) = alpha * sum_k dq(a)[m,k] * dq(b)[n,k]
+ *   a: uint8 [M, K/2], b: uint8 [N, K/2] packed E2M1, K-major, 16-byte aligned
+ *   sfa / sfb: swizzled E4M3 scales as written by nvfp4_quant_launch for
+ *              [M, K] and [N, K];  alpha: one float on the device.
+ *   K % 64 == 0 required (K % 16 == 0 operands can be produced with padded_n).
+ * fp32 accumulation on tcgen05 (kind::mxf4nvf4.block_scale) with TMEM accumulators.
+ * replaces vllm `_C::cutlass_scaled_fp4_mm` (vllm/_custom_ops.py:741-752;
+ * named at README.md:68).
+ * workspace: nvfp4_gemm_workspace_bytes(M, N, K) bytes, 256-byte aligned (may be
+ * NULL when that is 0).
+ */
+int nvfp4_gemm_launch(const uint8_t* a, const uint8_t* b, const uint8_t* sfa, const uint8_t* sfb,
+                      const float* alpha, void* out_bf16, int64_t M, int64_t N, int64_t K,
+                      void* workspace, size_t workspace_bytes, void* stream);
+size_t nvfp4_gemm_workspace_bytes(int64_t M, int64_t N, int64_t K);
+
+/* Device status word of the last GEMM on this device: 0 = ok, else a bounded
+ * wait inside the kernel gave up (the kernel returned without hanging).
+ * Synchronises `stream`. */
+int nvfp4_gemm_last_status(void* stream, uint32_t* status_host);
+
+/* Diagnostics used by the tests: out[raw] = bits of div.full.f32(1, e4m3(raw))
+ * for raw = 0..127 (no counterpart in the reference; it pins the CPU oracle's table). */
+int nvfp4_probe_div_full_table(uint32_t* out128, void* stream);
+/* out[raw] = the AMAX variant's multiplier for scale byte raw = 0..127 given gs_inv. */
+int nvfp4_probe_amax_out_scale_table(const float* gs_inv, float* out128, void* stream);
+
+const char* nvfp4_status_string(int status);
+int nvfp4_abi_version(void);
+
+#ifdef __cplusplus
+}
+#endif
+#endif /* NVFP4_B200_H_ */

@@ -1,0 +1,88 @@
+"""ctypes binding of libnvfp4_b200.so (the C ABI declared in include/nvfp4_b200.h).
+
+There is no CPU path: if the library is missing this module raises, it never
+falls back to another implementation.
+"""
+from __future__ import annotations
+
+import ctypes
+import pathlib
+
+_PKG = pathlib.Path(__file__).resolve().parent
+LIB_PATH = _PKG / "libnvfp4_b200.so"
+
+VARIANT_MSE, VARIANT_WEIGHTED, VARIANT_AMAX = 0, 1, 2
+DT_BF16, DT_F16, DT_F32 = 0, 1, 2
+
+EXPORTS = (
+    "nvfp4_quant_launch", "nvfp4_quant_launch_impl", "nvfp4_global_scale_launch",
+    "nvfp4_gemm_launch", "nvfp4_gemm_workspace_bytes", "nvfp4_gemm_last_status",
+    "nvfp4_probe_div_full_table", "nvfp4_probe_amax_out_scale_table",
+    "nvfp4_status_string", "nvfp4_abi_version",
+)
+
+_lib = None
+
+
+class Nvfp4Error(RuntimeError):
+    """A launch was rejected or failed; `.status` holds the C ABI status code."""
+
+    def __init__(self, status: int, what: str):
+        super().__init__(f"{what}: {status_string(status)} (status {status})")
+        self.status = status
+
+
+def lib() -> ctypes.CDLL:
+    global _lib
+    if _lib is None:
+        if not LIB_PATH.exists():
+            raise RuntimeError(
+                f"{LIB_PATH} is missing: build it with `python -m nvfp4quant_test_b200.build` "
+                "(needs nvcc; there is no CPU fallback)")
+        L = ctypes.CDLL(str(LIB_PATH))
+        i64, ci, vp, f32 = ctypes.c_int64, ctypes.c_int, ctypes.c_void_p, ctypes.c_float
+        L.nvfp4_quant_launch.restype = ci
+        L.nvfp4_quant_launch.argtypes = [ci, vp, ci, vp, vp, vp, vp, i64, i64, i64, ci, ci, ci, vp]
+        L.nvfp4_quant_launch_impl.restype = ci
+        L.nvfp4_quant_launch_impl.argtypes = [ci, ci, vp, ci, vp, vp, vp, vp, i64, i64, i64, ci, ci, ci, vp]
+        L.nvfp4_global_scale_launch.restype = ci
+        L.nvfp4_global_scale_launch.argtypes = [vp, ci, i64, f32, vp, vp, vp]
+        L.nvfp4_gemm_launch.restype = ci
+        L.nvfp4_gemm_launch.argtypes = [vp, vp, vp, vp, vp, vp, i64, i64, i64, vp, ctypes.c_size_t, vp]
+        L.nvfp4_gemm_workspace_bytes.restype = ctypes.c_size_t
+        L.nvfp4_gemm_workspace_bytes.argtypes = [i64, i64, i64]
+        L.nvfp4_gemm_last_status.restype = ci
+        L.nvfp4_gemm_last_status.argtypes = [vp, vp]
+        L.nvfp4_probe_div_full_table.restype = ci
+        L.nvfp4_probe_div_full_table.argtypes = [vp, vp]
+        L.nvfp4_probe_amax_out_scale_table.restype = ci
+        L.nvfp4_probe_amax_out_scale_table.argtypes = [vp, vp, vp]
+        L.nvfp4_status_string.restype = ctypes.c_char_p
+        L.nvfp4_status_string.argtypes = [ci]
+        L.nvfp4_abi_version.restype = ci
+        _lib = L
+    return _lib
+
+
+def status_string(status: int) -> str:
+    return lib().nvfp4_status_string(int(status)).decode()
+
+
+def check(status: int, what: str) -> None:
+    if status != 0:
+        raise Nvfp4Error(status, what)
+
+
+def dtype_code(dtype) -> int:
+    import torch
+
+    try:
+        return {torch.bfloat16: DT_BF16, torch.float16: DT_F16, torch.float32: DT_F32}[dtype]
+    except KeyError:
+        raise ValueError(f"input dtype must be bfloat16, float16 or float32, got {dtype}") from None
+
+
+def current_stream_ptr(device) -> int:
+    import torch
+
+    return torch.cuda.current_stream(device).cuda_stream

@@ -1,0 +1,358 @@
+// NVFP4 quantizer for sm_100a: ScaleSweep (unweighted and importance-weighted)
+// and the amax baseline, one kernel family.
+//
+// Behaviour follows efsotr/nvfp4quant_test:
+//   kernels/kernel_ScaleSweep_MSE.py:271-377  (unweighted sweep, RNE base, -3..+7)
+//   kernels/kernel_ScaleSweep.py:290-416      (weighted sweep, floor base, -8..+7)
+// and, for the amax variant, the NVFP4 recipe of vllm's scaled_fp4_quant.
+//
+// Bit-exactness rules kept here: fp32 everywhere with explicit round-to-nearest
+// operations (no contraction), `1/scale` through div.full.f32, squared errors
+// accumulated as one serial FMA chain over elements 0..15 (unweighted) or as the
+// fixed pairwise tree (weighted), candidates visited in ascending raw order with
+// a strict `<`, so the lowest raw code wins ties.
+//
+// Mapping: one 16-element block per thread; a warp covers 32 consecutive blocks
+// of one row (1 KiB of bf16).  Two candidates are evaluated per instruction with
+// the packed f32x2 forms (each lane is an independent IEEE operation, so the
+// result is the same as the scalar transcription kept beside it).
+#include <cuda_bf16.h>
+#include <cuda_fp16.h>
+
+#include "common.cuh"
+
+namespace nvfp4 {
+namespace {
+
+constexpr int kThreads = 256;
+
+struct QuantParams {
+    const void* x;
+    const float* importance;
+    const float* gs_inv;
+    uint8_t* codes;
+    uint8_t* scales;
+    int64_t m, n;
+    int64_t bin, bout;      // 16-element blocks per input / output row
+    int64_t width, rows;    // slot grid: scale columns / rows that get written
+    int64_t k_pad;          // padded scale columns (swizzled layout)
+    int64_t total;          // rows * width
+    int lower, ncand;
+    int swizzled;
+};
+
+template <int DT>
+__device__ __forceinline__ void load16(const void* base, int64_t elem, float v[16]);
+
+template <>
+__device__ __forceinline__ void load16<NVFP4_DT_BF16>(const void* base, int64_t elem, float v[16]) {
+    const uint4* p = reinterpret_cast<const uint4*>(static_cast<const uint16_t*>(base) + elem);
+    uint4 a = __ldg(p), b = __ldg(p + 1);
+    uint32_t w[8] = {a.x, a.y, a.z, a.w, b.x, b.y, b.z, b.w};
+#pragma unroll
+    for (int i = 0; i < 8; ++i) {
+        v[2 * i] = __uint_as_float(w[i] << 16);
+        v[2 * i + 1] = __uint_as_float(w[i] & 0xffff0000u);
+    }
+}
+
+template <>
+__device__ __forceinline__ void load16<NVFP4_DT_F16>(const void* base, int64_t elem, float v[16]) {
+    const uint4* p = reinterpret_cast<const uint4*>(static_cast<const uint16_t*>(base) + elem);
+    uint4 a = __ldg(p), b = __ldg(p + 1);
+    uint32_t w[8] = {a.x, a.y, a.z, a.w, b.x, b.y, b.z, b.w};
+#pragma unroll
+    for (int i = 0; i < 8; ++i) {
+        float2 f = __half22float2(*reinterpret_cast<const __half2*>(&w[i]));
+        v[2 * i] = f.x;
+        v[2 * i + 1] = f.y;
+    }
+}
+
+template <>
+__device__ __forceinline__ void load16<NVFP4_DT_F32>(const void* base, int64_t elem, float v[16]) {
+    const float4* p = reinterpret_cast<const float4*>(static_cast<const float*>(base) + elem);
+#pragma unroll
+    for (int i = 0; i < 4; ++i) {
+        float4 f = __ldg(p + i);
+        v[4 * i] = f.x;
+        v[4 * i + 1] = f.y;
+        v[4 * i + 2] = f.z;
+        v[4 * i + 3] = f.w;
+    }
+}
+
+__device__ __forceinline__ float max_abs16(const float v[16]) {
+    float m[8];
+#pragma unroll
+    for (int i = 0; i < 8; ++i) m[i] = fmaxf(fabsf(v[2 * i]), fabsf(v[2 * i + 1]));
+    return fmaxf(fmaxf(fmaxf(m[0], m[1]), fmaxf(m[2], m[3])), fmaxf(fmaxf(m[4], m[5]), fmaxf(m[6], m[7])));
+}
+
+__device__ __forceinline__ int clamp_raw(int raw) { return min(max(raw, 1), 126); }
+
+// ---- scalar transcription: one candidate at a time --------------------------------------
+template <bool WEIGHTED>
+__device__ __forceinline__ uint32_t sweep_scalar(const float v[16], const float w[16], int first_raw, int ncand,
+                                                 const float2* tab) {
+    float best = __int_as_float(0x7f800000);
+    uint32_t best_raw = 0;
+#pragma unroll 1
+    for (int i = 0; i < ncand; ++i) {
+        const int raw = clamp_raw(first_raw + i);
+        const float2 e = tab[raw];
+        float err;
+        if (!WEIGHTED) {
+            float acc = 0.0f;
+#pragma unroll
+            for (int p = 0; p < 8; ++p) {
+                float x0 = __fmul_rn(v[2 * p], e.x), x1 = __fmul_rn(v[2 * p + 1], e.x), q0, q1;
+                e2m1_round_pair(x0, x1, q0, q1);
+                float d0 = __fsub_rn(q0, x0), d1 = __fsub_rn(q1, x1);
+                acc = __fmaf_rn(d0, d0, acc);  // fma(d, d, +0) == mul.rn(d, d) for the first term
+                acc = __fmaf_rn(d1, d1, acc);
+            }
+            err = __fmul_rn(acc, e.y);
+        } else {
+            float pe[8];
+#pragma unroll
+            for (int p = 0; p < 8; ++p) {
+                float x0 = __fmul_rn(v[2 * p], e.x), x1 = __fmul_rn(v[2 * p + 1], e.x), q0, q1;
+                e2m1_round_pair(x0, x1, q0, q1);
+                float d0 = __fsub_rn(q0, x0), d1 = __fsub_rn(q1, x1);
+                float a = __fmul_rn(__fmul_rn(d0, d0), w[2 * p]);
+                pe[p] = __fmaf_rn(__fmul_rn(d1, d1), w[2 * p + 1], a);
+            }
+            float t = __fadd_rn(__fadd_rn(__fadd_rn(pe[0], pe[1]), __fadd_rn(pe[2], pe[3])),
+                                __fadd_rn(__fadd_rn(pe[4], pe[5]), __fadd_rn(pe[6], pe[7])));
+            err = __fmul_rn(t, e.y);
+        }
+        if (err < best) {
+            best = err;
+            best_raw = raw;
+        }
+    }
+    return best_raw;
+}
+
+// ---- packed: candidates i and i+1 share every instruction ---------------------------------
+template <bool WEIGHTED>
+__device__ __forceinline__ uint32_t sweep_packed(const float v[16], const float w[16], int first_raw, int ncand,
+                                                 const float2* tab) {
+    uint64_t vv[16];
+#pragma unroll
+    for (int j = 0; j < 16; ++j) vv[j] = pack_f32x2(v[j], v[j]);
+    float best = __int_as_float(0x7f800000);
+    uint32_t best_raw = 0;
+#pragma unroll 1
+    for (int i = 0; i < ncand; i += 2) {
+        const int raw_a = clamp_raw(first_raw + i);
+        const int raw_b = clamp_raw(first_raw + min(i + 1, ncand - 1));
+        const float2 ea = tab[raw_a], eb = tab[raw_b];
+        const uint64_t inv2 = pack_f32x2(ea.x, eb.x);
+        uint64_t tot2;
+        if (!WEIGHTED) {
+            uint64_t acc2 = 0;  // (+0, +0)
+#pragma unroll
+            for (int j = 0; j < 16; ++j) {
+                uint64_t x2 = mul_f32x2(vv[j], inv2);
+                float xa, xb, qa, qb;
+                unpack_f32x2(x2, xa, xb);
+                e2m1_round_pair(xa, xb, qa, qb);
+                uint64_t d2 = sub_f32x2(pack_f32x2(qa, qb), x2);
+                acc2 = fma_f32x2(d2, d2, acc2);
+            }
+            tot2 = acc2;
+        } else {
+            uint64_t pe[8];
+#pragma unroll
+            for (int p = 0; p < 8; ++p) {
+                uint64_t d2[2];
+#pragma unroll
+                for (int h = 0; h < 2; ++h) {
+                    uint64_t x2 = mul_f32x2(vv[2 * p + h], inv2);
+                    float xa, xb, qa, qb;
+                    unpack_f32x2(x2, xa, xb);
+                    e2m1_round_pair(xa, xb, qa, qb);
+                    d2[h] = sub_f32x2(pack_f32x2(qa, qb), x2);
+                }
+                uint64_t a = mul_f32x2(mul_f32x2(d2[0], d2[0]), pack_f32x2(w[2 * p], w[2 * p]));
+                pe[p] = fma_f32x2(mul_f32x2(d2[1], d2[1]), pack_f32x2(w[2 * p + 1], w[2 * p + 1]), a);
+            }
+            tot2 = add_f32x2(add_f32x2(add_f32x2(pe[0], pe[1]), add_f32x2(pe[2], pe[3])),
+                             add_f32x2(add_f32x2(pe[4], pe[5]), add_f32x2(pe[6], pe[7])));
+        }
+        float err_a, err_b;
+        unpack_f32x2(mul_f32x2(tot2, pack_f32x2(ea.y, eb.y)), err_a, err_b);
+        if (err_a < best) {
+            best = err_a;
+            best_raw = raw_a;
+        }
+        if (err_b < best) {  // for an odd count the last lane repeats candidate a: never "better"
+            best = err_b;
+            best_raw = raw_b;
+        }
+    }
+    return best_raw;
+}
+
+template <int DT, int VARIANT, int IMPL>
+__global__ void __launch_bounds__(kThreads) quant_kernel(const QuantParams p) {
+    // tab[raw] = (multiplier for the block's elements, scale*scale)
+    __shared__ float2 tab[128];
+    const float gs_inv = __ldg(p.gs_inv);
+    if (threadIdx.x < 128) {
+        const uint32_t raw = threadIdx.x;
+        const float s = e4m3_to_f32(raw);
+        float2 e;
+        if (VARIANT == NVFP4_VARIANT_AMAX) {
+            e.x = (raw == 0) ? 0.0f : rcp_approx_ftz(__fmul_rn(s, rcp_approx_ftz(gs_inv)));
+            e.y = 0.0f;
+        } else {
+            e.x = div_full(1.0f, s);
+            e.y = __fmul_rn(s, s);
+        }
+        tab[raw] = e;
+    }
+    __syncthreads();
+
+    const int64_t id = static_cast<int64_t>(blockIdx.x) * kThreads + threadIdx.x;
+    const bool in_range = id < p.total;
+    const int64_t row = in_range ? id / p.width : 0;
+    const int64_t col = in_range ? id - row * p.width : 0;
+    const bool valid = in_range && row < p.m && col < p.bout;
+
+    float v[16], w[16];
+#pragma unroll
+    for (int j = 0; j < 16; ++j) {
+        v[j] = 0.0f;
+        w[j] = 0.0f;
+    }
+    if (valid && col < p.bin) {
+        load16<DT>(p.x, row * p.n + col * kBlock, v);
+        if (VARIANT == NVFP4_VARIANT_WEIGHTED) load16<NVFP4_DT_F32>(p.importance, col * kBlock, w);
+    }
+
+    uint32_t sbyte = 0;
+    float inv = 0.0f;
+    if (VARIANT == NVFP4_VARIANT_AMAX) {
+        const float amax = max_abs16(v);
+        const float sf = __fmul_rn(gs_inv, __fmul_rn(amax, rcp_approx_ftz(6.0f)));
+        sbyte = f32_to_e4m3(sf);
+        inv = tab[sbyte & 0x7f].x;
+    } else {
+#pragma unroll
+        for (int j = 0; j < 16; ++j) v[j] = __fmul_rn(v[j], gs_inv);
+        const float amax = max_abs16(v);
+        const float base_scale = __fmul_rn(amax, __uint_as_float(0x3E2AAAABu));  // fp32(1/6)
+        const uint32_t base_fp8 = f32_to_e4m3(base_scale);
+        int base_raw = static_cast<int>(base_fp8);
+        if (VARIANT == NVFP4_VARIANT_WEIGHTED) base_raw -= (e4m3_to_f32(base_fp8) > base_scale) ? 1 : 0;
+        constexpr bool W = VARIANT == NVFP4_VARIANT_WEIGHTED;
+        sbyte = (IMPL == 1) ? sweep_scalar<W>(v, w, base_raw + p.lower, p.ncand, tab)
+                            : sweep_packed<W>(v, w, base_raw + p.lower, p.ncand, tab);
+        inv = tab[sbyte].x;
+    }
+
+    if (valid) {
+        const uint32_t lo = f32x8_to_e2m1x8(__fmul_rn(v[0], inv), __fmul_rn(v[1], inv), __fmul_rn(v[2], inv),
+                                            __fmul_rn(v[3], inv), __fmul_rn(v[4], inv), __fmul_rn(v[5], inv),
+                                            __fmul_rn(v[6], inv), __fmul_rn(v[7], inv));
+        const uint32_t hi = f32x8_to_e2m1x8(__fmul_rn(v[8], inv), __fmul_rn(v[9], inv), __fmul_rn(v[10], inv),
+                                            __fmul_rn(v[11], inv), __fmul_rn(v[12], inv), __fmul_rn(v[13], inv),
+                                            __fmul_rn(v[14], inv), __fmul_rn(v[15], inv));
+        *reinterpret_cast<uint2*>(p.codes + (row * p.bout + col) * 8) = make_uint2(lo, hi);
+    } else {
+        sbyte = 0;  // padding rows / columns of the scale buffer read as zero scales
+    }
+
+    // Scale store.  With width % 4 == 0 (always true for the swizzled layout) lanes
+    // 4q..4q+3 hold four consecutive blocks of one row: merge them into one 32-bit store.
+    if ((p.width & 3) == 0) {
+        const uint32_t lane = threadIdx.x & 31;
+        uint32_t word = sbyte << (8 * (lane & 3));
+        word |= __shfl_xor_sync(0xffffffffu, word, 1);
+        word |= __shfl_xor_sync(0xffffffffu, word, 2);
+        if (in_range && (lane & 3) == 0) {
+            const int64_t off = p.swizzled ? swizzled_scale_offset(row, col, p.k_pad) : row * p.width + col;
+            *reinterpret_cast<uint32_t*>(p.scales + off) = word;
+        }
+    } else if (in_range) {
+        p.scales[row * p.width + col] = static_cast<uint8_t>(sbyte);
+    }
+}
+
+template <int DT, int VARIANT>
+cudaError_t launch_impl(int impl, const QuantParams& p, cudaStream_t stream) {
+    const int64_t grid = (p.total + kThreads - 1) / kThreads;
+    if (impl == 1)
+        quant_kernel<DT, VARIANT, 1><<<static_cast<unsigned>(grid), kThreads, 0, stream>>>(p);
+    else
+        quant_kernel<DT, VARIANT, 2><<<static_cast<unsigned>(grid), kThreads, 0, stream>>>(p);
+    return cudaGetLastError();
+}
+
+template <int DT>
+cudaError_t launch_variant(int variant, int impl, const QuantParams& p, cudaStream_t stream) {
+    switch (variant) {
+        case NVFP4_VARIANT_MSE: return launch_impl<DT, NVFP4_VARIANT_MSE>(impl, p, stream);
+        case NVFP4_VARIANT_WEIGHTED: return launch_impl<DT, NVFP4_VARIANT_WEIGHTED>(impl, p, stream);
+        default: return launch_impl<DT, NVFP4_VARIANT_AMAX>(impl, p, stream);
+    }
+}
+
+}  // namespace
+}  // namespace nvfp4
+
+extern "C" int nvfp4_quant_launch_impl(int impl, int variant, const void* x, int x_dtype, const float* importance,
+                                       const float* gs_inv, uint8_t* codes, uint8_t* scales, int64_t m, int64_t n,
+                                       int64_t padded_n, int lower, int upper, int swizzled, void* stream) {
+    using namespace nvfp4;
+    if (variant < NVFP4_VARIANT_MSE || variant > NVFP4_VARIANT_AMAX) return NVFP4_ERR_BAD_ENUM;
+    if (x_dtype < NVFP4_DT_BF16 || x_dtype > NVFP4_DT_F32) return NVFP4_ERR_BAD_ENUM;
+    if (impl < 0 || impl > 2) return NVFP4_ERR_BAD_ENUM;
+    if (m < 0 || n < 0 || (n % kBlock) != 0 || (padded_n % kBlock) != 0 || padded_n < n) return NVFP4_ERR_BAD_SHAPE;
+    if (variant != NVFP4_VARIANT_AMAX && (upper < lower || upper - lower + 1 > 64)) return NVFP4_ERR_BAD_RANGE;
+    QuantParams p;
+    p.m = m;
+    p.n = n;
+    p.bin = n / kBlock;
+    p.bout = padded_n / kBlock;
+    p.k_pad = round_up_i64(p.bout, 4);
+    p.swizzled = swizzled ? 1 : 0;
+    p.width = swizzled ? p.k_pad : p.bout;
+    p.rows = swizzled ? round_up_i64(m, 128) : m;
+    p.total = p.rows * p.width;
+    if (p.total == 0) return NVFP4_OK;
+    if ((p.total + kThreads - 1) / kThreads > 0x7fffffffLL) return NVFP4_ERR_TOO_LARGE;
+    if (!gs_inv || !codes || !scales || (!x && m * n > 0)) return NVFP4_ERR_NULL_POINTER;
+    if (variant == NVFP4_VARIANT_WEIGHTED && !importance && n > 0) return NVFP4_ERR_NULL_POINTER;
+    if ((reinterpret_cast<uintptr_t>(x) & 15) || (reinterpret_cast<uintptr_t>(codes) & 7) ||
+        (reinterpret_cast<uintptr_t>(gs_inv) & 3))
+        return NVFP4_ERR_MISALIGNED;
+    if (swizzled && (reinterpret_cast<uintptr_t>(scales) & 3)) return NVFP4_ERR_MISALIGNED;
+    if (!swizzled && (p.width & 3) == 0 && (reinterpret_cast<uintptr_t>(scales) & 3)) return NVFP4_ERR_MISALIGNED;
+    if (variant == NVFP4_VARIANT_WEIGHTED && (reinterpret_cast<uintptr_t>(importance) & 15)) return NVFP4_ERR_MISALIGNED;
+    p.x = x;
+    p.importance = importance;
+    p.gs_inv = gs_inv;
+    p.codes = codes;
+    p.scales = scales;
+    p.lower = lower;
+    p.ncand = (variant == NVFP4_VARIANT_AMAX) ? 0 : upper - lower + 1;
+    cudaStream_t s = static_cast<cudaStream_t>(stream);
+    cudaError_t err;
+    switch (x_dtype) {
+        case NVFP4_DT_BF16: err = launch_variant<NVFP4_DT_BF16>(variant, impl, p, s); break;
+        case NVFP4_DT_F16: err = launch_variant<NVFP4_DT_F16>(variant, impl, p, s); break;
+        default: err = launch_variant<NVFP4_DT_F32>(variant, impl, p, s); break;
+    }
+    return static_cast<int>(err);
+}
+
+extern "C" int nvfp4_quant_launch(int variant, const void* x, int x_dtype, const float* importance,
+                                  const float* gs_inv, uint8_t* codes, uint8_t* scales, int64_t m, int64_t n,
+                                  int64_t padded_n, int lower, int upper, int swizzled, void* stream) {
+    return nvfp4_quant_launch_impl(0, variant, x, x_dtype, importance, gs_inv, codes, scales, m, n, padded_n, lower,
+                                   upper, swizzled, stream);
+}

@@ -1,0 +1,67 @@
+"""Bench / evaluation helpers with the names of the reference's helper.py.
+
+`get_nvfp4_global_scale` (helper.py:96-100 of efsotr/nvfp4quant_test) runs as a CUDA
+reduction kernel here; the dequantizer and error metrics (helper.py:103-147) are
+plain torch and work on any device.
+"""
+from __future__ import annotations
+
+import torch
+
+from . import _lib
+
+FP4_E2M1_MAX = 6.0
+FP8_E4M3_MAX_NVFP4 = 448.0
+FP8_E4M3_MAX_4OVER6 = 256.0
+
+_scratch: dict = {}
+
+
+def get_nvfp4_global_scale(x: torch.Tensor, FP8_MAX: float = FP8_E4M3_MAX_NVFP4):
+    """(global_scale, global_scale_inv) as 0-dim float32 CUDA tensors; amax(|x|)/(6*FP8_MAX) and its reciprocal."""
+    if not x.is_cuda:
+        raise ValueError("x must be a CUDA tensor")
+    x = x.contiguous()
+    key = (x.device, torch.cuda.current_stream(x.device).cuda_stream)
+    if key not in _scratch:
+        _scratch[key] = torch.zeros(2, dtype=torch.int32, device=x.device)
+    out = torch.empty(2, dtype=torch.float32, device=x.device)
+    with torch.cuda.device(x.device):
+        st = _lib.lib().nvfp4_global_scale_launch(x.data_ptr(), _lib.dtype_code(x.dtype), x.numel(), float(FP8_MAX),
+                                                  out.data_ptr(), _scratch[key].data_ptr(),
+                                                  _lib.current_stream_ptr(x.device))
+    _lib.check(st, "nvfp4_global_scale_launch")
+    return out[0], out[1]
+
+
+def error_stats(ref, pred):
+    diff = pred.float() - ref.float()
+    return torch.mean(diff * diff).item(), torch.max(torch.abs(diff)).item()
+
+
+def weighted_error_stats(weight, reconstructed, imp):
+    err = reconstructed.float() - weight.float()
+    return torch.mean(err * err * imp.float()).item(), torch.max(torch.abs(err)).item()
+
+
+_E2M1 = (0.0, 0.5, 1.0, 1.5, 2.0, 3.0, 4.0, 6.0)
+
+
+def unpack_fp4_e2m1(packed: torch.Tensor) -> torch.Tensor:
+    """uint8 [m, k/2] -> float32 [m, k]; low nibble first."""
+    assert packed.dtype == torch.uint8
+    lut = torch.tensor(_E2M1 + tuple(-v for v in _E2M1), dtype=torch.float32, device=packed.device)
+    both = torch.stack((packed & 0x0F, packed >> 4), dim=-1).long()
+    return lut[both].reshape(packed.shape[0], packed.shape[1] * 2)
+
+
+def dequantize_base(q, scale_fp8, global_scale):
+    """q uint8 [m, k/2], scale_fp8 float8_e4m3fn [m, k/16] (row-major, i.e. already unswizzled)."""
+    scales = scale_fp8.to(torch.float32).repeat_interleave(16, dim=1)
+    return unpack_fp4_e2m1(q) * scales * global_scale.float()
+
+
+def dequantize(kind, *args, **kwargs):
+    if kind == "base":
+        return dequantize_base(*args, **kwargs)
+    raise ValueError(f"unknown dequant kind: {kind}")

@@ -1,0 +1,73 @@
+"""NVFP4 block-scaled GEMM: out = alpha * dq(a) @ dq(b).T in bf16.
+
+Same signature and operand formats as `vllm._custom_ops.cutlass_scaled_fp4_mm`
+(vllm 0.22.0, vllm/_custom_ops.py:741-752), the GEMM the reference feeds with its
+quantizers' output (README.md:11,68): `a` uint8 [M, K/2], `b` uint8 [N, K/2], both
+K-major packed E2M1; block scales in the 128x4-tiled float8_e4m3fn layout; `alpha` a
+one-element float32 CUDA tensor (= global_scale_a * global_scale_b).
+"""
+from __future__ import annotations
+
+import torch
+
+from .. import _lib
+
+
+def _scale_bytes(rows: int, k: int) -> int:
+    return ((rows + 127) // 128 * 128) * ((k // 16 + 3) // 4 * 4)
+
+
+def nvfp4_scaled_mm(a: torch.Tensor, b: torch.Tensor, block_scale_a: torch.Tensor, block_scale_b: torch.Tensor,
+                    alpha: torch.Tensor, out_dtype: torch.dtype = torch.bfloat16,
+                    out: torch.Tensor | None = None) -> torch.Tensor:
+    if a.ndim != 2 or b.ndim != 2:
+        raise ValueError("a and b must be 2D [rows, K/2] uint8 tensors")
+    if a.dtype != torch.uint8 or b.dtype != torch.uint8:
+        raise ValueError("a and b must hold packed E2M1 codes as uint8")
+    if out_dtype != torch.bfloat16:
+        raise ValueError("only bfloat16 output is implemented")
+    if not (a.is_cuda and b.device == a.device and block_scale_a.device == a.device
+            and block_scale_b.device == a.device and alpha.device == a.device):
+        raise ValueError("all operands must be CUDA tensors on one device")
+    m, n, k = a.shape[0], b.shape[0], a.shape[1] * 2
+    if b.shape[1] * 2 != k:
+        raise ValueError(f"a and b disagree on K: {k} vs {b.shape[1] * 2}")
+    if k % 64 != 0:
+        raise ValueError(f"K must be a multiple of 64 (quantize with padded_n to pad it), got {k}")
+    if alpha.dtype != torch.float32 or alpha.numel() < 1:
+        raise ValueError("alpha must be a float32 tensor with one element")
+    a, b = a.contiguous(), b.contiguous()
+    sfa, sfb = block_scale_a.contiguous(), block_scale_b.contiguous()
+    for name, sf, rows in (("block_scale_a", sfa, m), ("block_scale_b", sfb, n)):
+        have = sf.numel() * sf.element_size()
+        if have < _scale_bytes(rows, k):
+            raise ValueError(f"{name} holds {have} bytes, the tiled layout for [{rows}, {k}] needs {_scale_bytes(rows, k)}")
+    if out is None:
+        out = torch.empty((m, n), dtype=torch.bfloat16, device=a.device)
+    elif out.shape != (m, n) or out.dtype != torch.bfloat16 or not out.is_contiguous():
+        raise ValueError("out must be a contiguous bfloat16 [M, N] tensor")
+    if m == 0 or n == 0:
+        return out
+    with torch.cuda.device(a.device):
+        st = _lib.lib().nvfp4_gemm_launch(a.data_ptr(), b.data_ptr(), sfa.data_ptr(), sfb.data_ptr(),
+                                          alpha.data_ptr(), out.data_ptr(), m, n, k, None, 0,
+                                          _lib.current_stream_ptr(a.device))
+    _lib.check(st, "nvfp4_gemm_launch")
+    return out
+
+
+def cutlass_scaled_fp4_mm(a, b, block_scale_a, block_scale_b, alpha, out_dtype):
+    """Drop-in name of the vllm op."""
+    return nvfp4_scaled_mm(a, b, block_scale_a, block_scale_b, alpha, out_dtype)
+
+
+def gemm_last_status(device=None) -> int:
+    """Synchronise and return the device status word of the last GEMM (0 = ok)."""
+    import ctypes
+
+    dev = torch.device("cuda", torch.cuda.current_device()) if device is None else device
+    word = ctypes.c_uint32(0)
+    with torch.cuda.device(dev):
+        st = _lib.lib().nvfp4_gemm_last_status(_lib.current_stream_ptr(dev), ctypes.byref(word))
+    _lib.check(st, "nvfp4_gemm_last_status")
+    return word.value
