@@ -196,6 +196,77 @@ __device__ __forceinline__ uint32_t sweep_packed(const float v[16], const float 
     return best_raw;
 }
 
+// ---- paired: two candidates per loop trip; element pairs share the multiply and both
+// conversions, the difference uses the mixed-precision subtract (f16 grid value minus fp32 x,
+// one full-rate instruction, exact like cvt + sub), and the two candidates' accumulations
+// share one f32x2 instruction -------------------------------------------------------------
+__device__ __forceinline__ void e2m1_diff_pair(uint64_t x2, float& d0, float& d1) {
+    asm("{ .reg .b8 b; .reg .b32 h; .reg .b16 lo, hi; .reg .f32 x0, x1;\n"
+        "  mov.b64 {x0, x1}, %2;\n"
+        "  cvt.rn.satfinite.e2m1x2.f32 b, x1, x0;\n"
+        "  cvt.rn.f16x2.e2m1x2 h, b;\n"
+        "  mov.b32 {lo, hi}, h;\n"
+        "  sub.rn.f32.f16 %0, lo, x0;\n"
+        "  sub.rn.f32.f16 %1, hi, x1; }"
+        : "=f"(d0), "=f"(d1)
+        : "l"(x2));
+}
+
+template <bool WEIGHTED>
+__device__ __forceinline__ uint32_t sweep_paired(const float v[16], const float w[16], int first_raw, int ncand,
+                                                 const float2* tab) {
+    uint64_t vp[8];  // (v[2p], v[2p+1])
+#pragma unroll
+    for (int p = 0; p < 8; ++p) vp[p] = pack_f32x2(v[2 * p], v[2 * p + 1]);
+    float best = __int_as_float(0x7f800000);
+    uint32_t best_raw = 0;
+#pragma unroll 1
+    for (int i = 0; i < ncand; i += 2) {
+        const int raw_a = clamp_raw(first_raw + i);
+        const int raw_b = clamp_raw(first_raw + min(i + 1, ncand - 1));
+        const float2 ea = tab[raw_a], eb = tab[raw_b];
+        const uint64_t inv_a = pack_f32x2(ea.x, ea.x), inv_b = pack_f32x2(eb.x, eb.x);
+        uint64_t tot2;
+        if (!WEIGHTED) {
+            uint64_t acc2 = 0;  // (+0, +0): candidate a in the low lane, b in the high lane
+#pragma unroll
+            for (int p = 0; p < 8; ++p) {
+                float a0, a1, b0, b1;
+                e2m1_diff_pair(mul_f32x2(vp[p], inv_a), a0, a1);
+                e2m1_diff_pair(mul_f32x2(vp[p], inv_b), b0, b1);
+                const uint64_t d0 = pack_f32x2(a0, b0), d1 = pack_f32x2(a1, b1);
+                acc2 = fma_f32x2(d0, d0, acc2);
+                acc2 = fma_f32x2(d1, d1, acc2);
+            }
+            tot2 = acc2;
+        } else {
+            uint64_t pe[8];
+#pragma unroll
+            for (int p = 0; p < 8; ++p) {
+                float a0, a1, b0, b1;
+                e2m1_diff_pair(mul_f32x2(vp[p], inv_a), a0, a1);
+                e2m1_diff_pair(mul_f32x2(vp[p], inv_b), b0, b1);
+                const uint64_t d0 = pack_f32x2(a0, b0), d1 = pack_f32x2(a1, b1);
+                const uint64_t t = mul_f32x2(mul_f32x2(d0, d0), pack_f32x2(w[2 * p], w[2 * p]));
+                pe[p] = fma_f32x2(mul_f32x2(d1, d1), pack_f32x2(w[2 * p + 1], w[2 * p + 1]), t);
+            }
+            tot2 = add_f32x2(add_f32x2(add_f32x2(pe[0], pe[1]), add_f32x2(pe[2], pe[3])),
+                             add_f32x2(add_f32x2(pe[4], pe[5]), add_f32x2(pe[6], pe[7])));
+        }
+        float err_a, err_b;
+        unpack_f32x2(mul_f32x2(tot2, pack_f32x2(ea.y, eb.y)), err_a, err_b);
+        if (err_a < best) {
+            best = err_a;
+            best_raw = raw_a;
+        }
+        if (err_b < best) {
+            best = err_b;
+            best_raw = raw_b;
+        }
+    }
+    return best_raw;
+}
+
 template <int DT, int VARIANT, int IMPL>
 __global__ void __launch_bounds__(kThreads) quant_kernel(const QuantParams p) {
     // tab[raw] = (multiplier for the block's elements, scale*scale)
@@ -249,8 +320,9 @@ __global__ void __launch_bounds__(kThreads) quant_kernel(const QuantParams p) {
         int base_raw = static_cast<int>(base_fp8);
         if (VARIANT == NVFP4_VARIANT_WEIGHTED) base_raw -= (e4m3_to_f32(base_fp8) > base_scale) ? 1 : 0;
         constexpr bool W = VARIANT == NVFP4_VARIANT_WEIGHTED;
-        sbyte = (IMPL == 1) ? sweep_scalar<W>(v, w, base_raw + p.lower, p.ncand, tab)
-                            : sweep_packed<W>(v, w, base_raw + p.lower, p.ncand, tab);
+        sbyte = (IMPL == 1)   ? sweep_scalar<W>(v, w, base_raw + p.lower, p.ncand, tab)
+                : (IMPL == 2) ? sweep_packed<W>(v, w, base_raw + p.lower, p.ncand, tab)
+                              : sweep_paired<W>(v, w, base_raw + p.lower, p.ncand, tab);
         inv = tab[sbyte].x;
     }
 
@@ -287,8 +359,10 @@ cudaError_t launch_impl(int impl, const QuantParams& p, cudaStream_t stream) {
     const int64_t grid = (p.total + kThreads - 1) / kThreads;
     if (impl == 1)
         quant_kernel<DT, VARIANT, 1><<<static_cast<unsigned>(grid), kThreads, 0, stream>>>(p);
-    else
+    else if (impl == 2)
         quant_kernel<DT, VARIANT, 2><<<static_cast<unsigned>(grid), kThreads, 0, stream>>>(p);
+    else
+        quant_kernel<DT, VARIANT, 3><<<static_cast<unsigned>(grid), kThreads, 0, stream>>>(p);
     return cudaGetLastError();
 }
 
@@ -310,7 +384,7 @@ extern "C" int nvfp4_quant_launch_impl(int impl, int variant, const void* x, int
     using namespace nvfp4;
     if (variant < NVFP4_VARIANT_MSE || variant > NVFP4_VARIANT_AMAX) return NVFP4_ERR_BAD_ENUM;
     if (x_dtype < NVFP4_DT_BF16 || x_dtype > NVFP4_DT_F32) return NVFP4_ERR_BAD_ENUM;
-    if (impl < 0 || impl > 2) return NVFP4_ERR_BAD_ENUM;
+    if (impl < 0 || impl > 3) return NVFP4_ERR_BAD_ENUM;
     if (m < 0 || n < 0 || (n % kBlock) != 0 || (padded_n % kBlock) != 0 || padded_n < n) return NVFP4_ERR_BAD_SHAPE;
     if (variant != NVFP4_VARIANT_AMAX && (upper < lower || upper - lower + 1 > 64)) return NVFP4_ERR_BAD_RANGE;
     QuantParams p;

@@ -1,0 +1,83 @@
+"""CPU: the C ABI library loads and exports what include/nvfp4_b200.h declares; argument
+validation answers without touching a GPU."""
+import ctypes
+import pathlib
+import re
+
+import pytest
+
+ROOT = pathlib.Path(__file__).resolve().parents[1]
+
+
+@pytest.fixture(scope="module")
+def L():
+    from nvfp4quant_test_b200 import _lib, build
+
+    build.build()
+    return _lib.lib()
+
+
+def declared_functions():
+    text = (ROOT / "include" / "nvfp4_b200.h").read_text()
+    text = re.sub(r"/\*.*?\*/", "", text, flags=re.S)
+    return sorted(set(re.findall(r"\b(nvfp4_[a-z0-9_]+)\s*\(", text)))
+
+
+def test_every_declared_symbol_is_exported(L):
+    from nvfp4quant_test_b200 import _lib
+
+    names = declared_functions()
+    assert len(names) >= 10
+    for n in names:
+        assert hasattr(L, n), f"{n} declared in the header but not exported"
+    assert set(_lib.EXPORTS) <= set(names)
+
+
+def test_abi_version_and_status_strings(L):
+    from nvfp4quant_test_b200 import _lib
+
+    assert L.nvfp4_abi_version() >= 1
+    assert _lib.status_string(0) == "ok"
+    for code in range(-8, 0):
+        s = _lib.status_string(code)
+        assert s and s != "unknown status"
+    assert _lib.status_string(-99) == "unknown status"
+
+
+def test_quant_launch_rejects_bad_arguments_before_launching(L):
+    q = L.nvfp4_quant_launch
+    P = 0x1000  # fake, aligned, never dereferenced: validation fails first
+    assert q(7, P, 0, None, P, P, P, 4, 64, 64, -3, 7, 1, None) == -3          # variant
+    assert q(0, P, 9, None, P, P, P, 4, 64, 64, -3, 7, 1, None) == -3          # dtype
+    assert q(0, P, 0, None, P, P, P, 4, 60, 64, -3, 7, 1, None) == -2          # n % 16
+    assert q(0, P, 0, None, P, P, P, 4, 64, 48, -3, 7, 1, None) == -2          # padded_n < n
+    assert q(0, P, 0, None, P, P, P, 4, 64, 72, -3, 7, 1, None) == -2          # padded_n % 16
+    assert q(0, P, 0, None, P, P, P, -1, 64, 64, -3, 7, 1, None) == -2
+    assert q(0, P, 0, None, P, P, P, 4, 64, 64, 3, 2, 1, None) == -5           # empty window
+    assert q(0, P, 0, None, P, P, P, 4, 64, 64, -40, 40, 1, None) == -5        # > 64 candidates
+    assert q(0, None, 0, None, P, P, P, 4, 64, 64, -3, 7, 1, None) == -1       # null x
+    assert q(1, P, 0, None, P, P, P, 4, 64, 64, -8, 7, 1, None) == -1          # weighted without importance
+    assert q(0, P + 2, 0, None, P, P, P, 4, 64, 64, -3, 7, 1, None) == -4      # misaligned x
+    assert q(0, P, 0, None, P, P + 1, P, 4, 64, 64, -3, 7, 1, None) == -4      # misaligned codes
+    assert q(0, P, 0, None, P, P, P, 0, 64, 64, -3, 7, 1, None) == 0           # empty input: nothing to do
+    assert L.nvfp4_quant_launch_impl(5, 0, P, 0, None, P, P, P, 4, 64, 64, -3, 7, 1, None) == -3
+
+
+def test_gemm_launch_rejects_bad_arguments_before_launching(L):
+    g = L.nvfp4_gemm_launch
+    P = 0x1000
+    assert g(P, P, P, P, P, P, 128, 128, 96, None, 0, None) == -2    # K % 64
+    assert g(P, P, P, P, P, P, -1, 128, 64, None, 0, None) == -2
+    assert g(None, P, P, P, P, P, 128, 128, 64, None, 0, None) == -1
+    assert g(P + 4, P, P, P, P, P, 128, 128, 64, None, 0, None) == -4
+    assert g(P, P, P, P, P, P, 0, 128, 64, None, 0, None) == 0       # empty output
+    assert L.nvfp4_gemm_workspace_bytes(8192, 8192, 8192) >= 0
+
+
+def test_global_scale_rejects_bad_arguments(L):
+    f = L.nvfp4_global_scale_launch
+    P = 0x1000
+    assert f(P, 5, 16, 448.0, P, P, None) == -3
+    assert f(P, 0, -1, 448.0, P, P, None) == -2
+    assert f(P, 0, 16, 448.0, None, P, None) == -1
+    assert f(P + 2, 0, 16, 448.0, P, P, None) == -4

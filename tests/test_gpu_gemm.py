@@ -1,0 +1,109 @@
+"""GPU: the tcgen05 NVFP4 GEMM against the fp64 oracle and against cutlass_scaled_fp4_mm outputs.
+
+Tolerance: fp32 accumulation of exact products, rounded once to bf16.  Every element must be within
+2^-7 relative (one bf16 ulp) of the fp64 result, or within 2^-16 of the largest magnitude for values
+near cancellation; in practice almost all elements equal the correctly rounded bf16 value."""
+import numpy as np
+import pytest
+import torch
+
+import cases as C
+
+pytestmark = pytest.mark.gpu
+
+
+def _quantize(x, imp=None):
+    import nvfp4quant_test_b200.kernels as K
+    from nvfp4quant_test_b200 import helper as H
+
+    gs, gs_inv = H.get_nvfp4_global_scale(x, 256.0)
+    if imp is None:
+        q, s = K.scalesweep_mse_nvfp4_quant_impl(x, gs_inv)
+    else:
+        q, s = K.scalesweep_weighted_mse_nvfp4_quant_impl(x, imp, gs_inv)
+    return q, s, gs
+
+
+def _check(out, ref):
+    o = out.float().cpu().numpy()
+    tol = np.maximum(np.abs(ref) * 2.0 ** -7, np.abs(ref).max() * 2.0 ** -16)
+    assert not np.isnan(o).any()
+    assert (np.abs(o - ref) <= tol).all(), float(np.abs(o - ref).max())
+    want = torch.from_numpy(ref).to(torch.bfloat16).float().numpy()
+    assert (o == want).mean() > 0.97
+
+
+@pytest.mark.parametrize("M,N,K_", [(128, 256, 256), (130, 264, 512), (1, 512, 1024), (16, 128, 64), (300, 520, 320),
+                                    (128, 128, 8192), (257, 1000, 192), (129, 8, 64), (256, 1024, 2048)])
+def test_gemm_matches_fp64_oracle(cuda_lib, oracle, M, N, K_):
+    import nvfp4quant_test_b200.kernels as K
+    from nvfp4quant_test_b200.kernels.kernel_gemm import gemm_last_status
+
+    a, b = C.gemm_operands(M, N, K_, 40 + M + N)
+    a, b = a.cuda(), b.cuda()
+    qa, sa, gsa = _quantize(a, (b.float() ** 2).sum(0, keepdim=True))
+    qb, sb, gsb = _quantize(b, (a.float() ** 2).sum(0, keepdim=True))
+    alpha = (gsa * gsb).reshape(1).float()
+    out = K.nvfp4_scaled_mm(qa, qb, sa, sb, alpha, torch.bfloat16)
+    assert gemm_last_status() == 0
+    ref = oracle.gemm(qa.cpu().numpy(), qb.cpu().numpy(), sa.view(torch.uint8).cpu().numpy().reshape(-1),
+                      sb.view(torch.uint8).cpu().numpy().reshape(-1), float(alpha))
+    _check(out, ref)
+    # drop-in name of the vllm op and exact alpha scaling by a power of two
+    out2 = K.cutlass_scaled_fp4_mm(qa, qb, sa, sb, alpha * 4, torch.bfloat16)
+    assert torch.equal(out2.float(), out.float() * 4)
+
+
+def test_gemm_matches_cutlass_fixture(cuda_lib, golden):
+    """Same quantized operands as the fixture -> compare with what cutlass_scaled_fp4_mm returned on a B200."""
+    import nvfp4quant_test_b200.kernels as K
+
+    meta, arrays = golden
+    assert meta["gemm"]
+    for name, info in meta["gemm"].items():
+        qa = torch.from_numpy(arrays[name + ".qa"]).cuda()
+        qb = torch.from_numpy(arrays[name + ".qb"]).cuda()
+        sa = torch.from_numpy(arrays[name + ".sa"]).cuda()
+        sb = torch.from_numpy(arrays[name + ".sb"]).cuda()
+        alpha = torch.from_numpy(np.array([info["alpha_bits"]], dtype=np.int32).view(np.float32)).cuda()
+        out = K.nvfp4_scaled_mm(qa, qb, sa, sb, alpha, torch.bfloat16)
+        want = torch.from_numpy(arrays[name + ".out_bf16_bits"]).view(torch.bfloat16).float()
+        got = out.float().cpu()
+        # both accumulate exact products in fp32 (different orders): at most one bf16 ulp apart
+        tol = torch.maximum(want.abs() * 2.0 ** -7, want.abs().max() * 2.0 ** -16)
+        assert bool(((got - want).abs() <= tol).all()), name
+        assert float((got == want).float().mean()) > 0.97, name
+
+
+def test_gemm_full_size_sampled(cuda_lib, oracle):
+    """M = N = K = 8192 (the benchmark's GEMM): sampled rows/columns against fp64 dot products, plus
+    linearity in alpha and independence from how N is sharded."""
+    import nvfp4quant_test_b200.kernels as K
+    from nvfp4quant_test_b200.kernels.kernel_gemm import gemm_last_status
+
+    g = torch.Generator(device="cuda")
+    g.manual_seed(3)
+    a = torch.randn((8192, 8192), generator=g, device="cuda").bfloat16()
+    b = torch.randn((8192, 8192), generator=g, device="cuda").bfloat16()
+    qa, sa, gsa = _quantize(a)
+    qb, sb, gsb = _quantize(b)
+    alpha = (gsa * gsb).reshape(1).float()
+    out = K.nvfp4_scaled_mm(qa, qb, sa, sb, alpha, torch.bfloat16)
+    assert gemm_last_status() == 0
+    rows = [0, 127, 128, 4095, 8191]
+    cols = list(range(0, 8192, 97))
+    sa_u = K.unswizzle_vllm_fp4_scale(sa, 8192, 8192)
+    sb_u = K.unswizzle_vllm_fp4_scale(sb, 8192, 8192)
+    from nvfp4quant_test_b200 import helper as H
+
+    da = H.dequantize_base(qa[rows], sa_u[rows], torch.tensor(1.0)).double()
+    db = H.dequantize_base(qb[cols], sb_u[cols], torch.tensor(1.0)).double()
+    ref = (da @ db.T * float(alpha)).cpu().numpy()
+    got = out[rows][:, cols].float().cpu().numpy()
+    tol = np.maximum(np.abs(ref) * 2.0 ** -7, np.abs(ref).max() * 2.0 ** -16)
+    assert (np.abs(got - ref) <= tol).all()
+    # N-sharding (the multi-GPU partitioning): each 1024-row slice of b gives the same output columns
+    for n0 in (0, 3072, 7168):
+        part = K.nvfp4_scaled_mm(qa, qb[n0:n0 + 1024], sa, sb.view(torch.uint8).reshape(-1)[n0 * 512:(n0 + 1024) * 512],
+                                 alpha, torch.bfloat16)
+        assert torch.equal(part, out[:, n0:n0 + 1024])

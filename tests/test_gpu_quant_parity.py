@@ -1,0 +1,226 @@
+"""GPU: the CUDA quantizers, called through the C ABI, against the CPU oracle and the reference fixtures.
+Bit-exact: every code byte and every logical scale byte must match."""
+import numpy as np
+import pytest
+import torch
+
+import cases as C
+import util
+
+pytestmark = pytest.mark.gpu
+
+
+def _amax_table(cuda_lib, gs_inv: float):
+    from nvfp4quant_test_b200 import _lib
+
+    g = torch.tensor([gs_inv], dtype=torch.float32, device="cuda")
+    t = torch.zeros(128, dtype=torch.float32, device="cuda")
+    _lib.check(cuda_lib.nvfp4_probe_amax_out_scale_table(g.data_ptr(), t.data_ptr(), None), "probe")
+    torch.cuda.synchronize()
+    return t.cpu().numpy()
+
+
+def _run_cuda(c, gs_inv: float, impl: int = 0, fill: int = 0xA5):
+    """Call nvfp4_quant_launch_impl on canary-filled buffers; returns (codes, scale bytes, canaries intact)."""
+    from nvfp4quant_test_b200 import _lib
+
+    L = _lib.lib()
+    x = c["x"].cuda()
+    m, n = x.shape
+    P = c["padded_n"] or n
+    blocks = P // 16
+    sc_bytes = ((m + 127) // 128 * 128) * ((blocks + 3) // 4 * 4) if c["swizzled"] else m * blocks
+    guard = 256
+    codes = torch.full((m * P // 2 + 2 * guard,), fill, dtype=torch.uint8, device="cuda")
+    scales = torch.full((sc_bytes + 2 * guard,), fill, dtype=torch.uint8, device="cuda")
+    g = torch.tensor([gs_inv], dtype=torch.float32, device="cuda")
+    imp = c["importance"].cuda().contiguous() if c["importance"] is not None else None
+    lo, up = util.window(c)
+    st = L.nvfp4_quant_launch_impl(impl, util.VARIANT[c["variant"]], x.data_ptr(), _lib.dtype_code(x.dtype),
+                                   imp.data_ptr() if imp is not None else None, g.data_ptr(),
+                                   codes.data_ptr() + guard, scales.data_ptr() + guard, m, n, P, lo, up,
+                                   int(c["swizzled"]), torch.cuda.current_stream().cuda_stream)
+    _lib.check(st, "nvfp4_quant_launch_impl")
+    torch.cuda.synchronize()
+    ch, sh = codes.cpu().numpy(), scales.cpu().numpy()
+    intact = bool((ch[:guard] == fill).all() and (ch[-guard:] == fill).all() and (sh[:guard] == fill).all()
+                  and (sh[-guard:] == fill).all())
+    return ch[guard:-guard].reshape(m, P // 2), sh[guard:-guard], intact
+
+
+@pytest.mark.parametrize("name", sorted(C.build_cases()))
+def test_cuda_matches_oracle_bit_for_bit(cuda_lib, oracle, name):
+    c = C.build_cases()[name]
+    gs_inv = c["gs_inv"] if c["gs_inv"] is not None else C.global_scale_cpu(c["x"], c["fp8_max"])[1]
+    table = _amax_table(cuda_lib, gs_inv) if c["variant"] == "amax" else None
+    want_codes, want_scales = util.oracle_quant_case(oracle, c, gs_inv, table)
+    m, n = c["x"].shape
+    blocks = (c["padded_n"] or n) // 16
+    idx = util.logical_scale_index(m, blocks, c["swizzled"])
+    pad = np.ones(want_scales.size, dtype=bool)
+    pad[idx] = False
+    for impl in (0, 1, 2, 3):
+        codes, scales, intact = _run_cuda(c, gs_inv, impl)
+        assert intact, f"impl {impl} wrote outside its buffers"
+        assert np.array_equal(codes, want_codes), f"impl {impl}: {(codes != want_codes).sum()} code bytes differ"
+        assert np.array_equal(scales[idx], want_scales[idx]), f"impl {impl}: scale bytes differ"
+        assert (scales[pad] == 0).all(), f"impl {impl}: scale padding must be zero"
+
+
+def test_cuda_matches_reference_fixtures(cuda_lib, golden):
+    """Against bytes the reference's Triton kernels / vllm's op produced on a B200."""
+    meta, arrays = golden
+    cs = C.build_cases()
+    for name, info in meta["cases"].items():
+        c = cs[name]
+        gs_inv = float(np.array([info["gs_inv_bits"]], dtype=np.int32).view(np.float32)[0])
+        codes, scales, intact = _run_cuda(c, gs_inv)
+        m, n = c["x"].shape
+        idx = util.logical_scale_index(m, (c["padded_n"] or n) // 16, c["swizzled"])
+        assert intact
+        assert np.array_equal(scales[idx], arrays[name + ".scales"].reshape(-1)[idx]), name
+        assert np.array_equal(codes, arrays[name + ".codes"]), (name, int((codes != arrays[name + ".codes"]).sum()))
+
+
+@pytest.mark.parametrize("m", [1, 2, 127, 128, 129])
+@pytest.mark.parametrize("n", [16, 48, 64, 8192])
+@pytest.mark.parametrize("swizzled", [True, False])
+def test_edge_shapes(cuda_lib, oracle, m, n, swizzled):
+    x = C._gauss((m, n), 1000 + m + n)
+    gs_inv = C.global_scale_cpu(x, 256.0)[1]
+    for variant, imp in (("mse", None), ("weighted", C._importance("random", n))):
+        c = dict(x=x, variant=variant, importance=imp, swizzled=swizzled, padded_n=None, lower=None, upper=None)
+        want_codes, want_scales = util.oracle_quant_case(oracle, c, gs_inv)
+        codes, scales, intact = _run_cuda(c, gs_inv)
+        idx = util.logical_scale_index(m, n // 16, swizzled)
+        assert intact and np.array_equal(codes, want_codes) and np.array_equal(scales[idx], want_scales[idx])
+
+
+def test_python_entry_points_and_layouts(cuda_lib, oracle):
+    """The reference-facing functions: _impl allocates, _out writes in place, int32- or uint8-typed scale
+    buffers, padded_n, non-contiguous input, linear layout, and swizzle(linear) == swizzled output."""
+    import nvfp4quant_test_b200.kernels as K
+    from nvfp4quant_test_b200 import helper as H
+
+    x = C._laplace((200, 400), 5).cuda()[:, :384]                       # non-contiguous view, n = 384
+    assert not x.is_contiguous()
+    gs, gs_inv = H.get_nvfp4_global_scale(x, 256.0)
+    codes, scales = K.scalesweep_mse_nvfp4_quant_impl(x, gs_inv)
+    assert codes.shape == (200, 192) and scales.dtype == torch.float8_e4m3fn and scales.numel() == 256 * 24
+    lin_codes, lin_scales = K.scalesweep_mse_nvfp4_quant_impl(x, gs_inv, False)
+    assert torch.equal(codes, lin_codes) and lin_scales.shape == (200, 24)
+    assert torch.equal(K.unswizzle_vllm_fp4_scale(scales, 200, 384).view(torch.uint8), lin_scales.view(torch.uint8))
+    assert torch.equal(K.swizzle_vllm_fp4_scale(lin_scales, 200, 384).view(torch.uint8),
+                       scales.view(torch.uint8).reshape(-1))
+    want_codes, want_scales = oracle.quant(0, oracle.bf16_bits(x.contiguous().cpu()), float(gs_inv), swizzled=False)
+    assert np.array_equal(lin_codes.cpu().numpy(), want_codes)
+    assert np.array_equal(lin_scales.view(torch.uint8).cpu().numpy(), want_scales)
+    # _out with a uint8-typed scale buffer and K padding
+    out = torch.empty((200, 256), dtype=torch.uint8, device="cuda")
+    out_scale = torch.empty((256, 32), dtype=torch.uint8, device="cuda")
+    K.scalesweep_mse_nvfp4_quant_out(x, gs_inv, True, output=out, output_scale=out_scale)
+    assert torch.equal(out[:, :192], codes) and bool((out[:, 192:] == 0).all())
+    pc, ps = K.scalesweep_mse_nvfp4_quant_impl(x, gs_inv, True, padded_n=512)
+    assert torch.equal(pc, out) and torch.equal(ps.view(torch.uint8).reshape(-1), out_scale.reshape(-1))
+    # ScaleSweep_MSE_round is the same function; weighted with unit importance picks equal-or-better scales
+    rc, rs = K.scalesweep_mse_round_nvfp4_quant_impl(x, gs_inv)
+    assert torch.equal(rc, codes) and torch.equal(rs.view(torch.uint8), scales.view(torch.uint8))
+    imp = torch.ones((1, 384), device="cuda")
+    wc, ws = K.scalesweep_weighted_mse_nvfp4_quant_impl(x, imp, gs_inv)
+    deq_m = H.dequantize_base(codes, K.unswizzle_vllm_fp4_scale(scales, 200, 384), gs)
+    deq_w = H.dequantize_base(wc, K.unswizzle_vllm_fp4_scale(ws, 200, 384), gs)
+    assert H.error_stats(x, deq_w)[0] <= H.error_stats(x, deq_m)[0] * (1 + 1e-6)
+    # amax entry point with vllm's signature flattens leading dimensions
+    ac, a_s = K.scaled_fp4_quant(x.reshape(2, 100, 384), gs_inv)
+    assert ac.shape == (200, 192)
+    with pytest.raises(ValueError):
+        K.scalesweep_mse_nvfp4_quant_out(x, gs_inv, True, output=out[:, :100], output_scale=out_scale)
+    with pytest.raises(ValueError):
+        K.scalesweep_mse_nvfp4_quant_out(x, gs_inv, True, output=out, output_scale=out_scale[:10])
+
+
+def test_full_size_8192_matches_oracle_and_properties(cuda_lib, oracle):
+    """The benchmark's workload (8192 x 8192 bf16): whole-tensor bit comparison with the oracle, plus the
+    size-independent properties: row independence (any row subset quantizes to the same bytes) and a
+    checksum that does not depend on how rows are split."""
+    import nvfp4quant_test_b200.kernels as K
+    from nvfp4quant_test_b200 import helper as H
+
+    g = torch.Generator(device="cuda")
+    g.manual_seed(0)
+    x = torch.normal(0.0, 1.0, size=(8192, 8192), generator=g, device="cuda", dtype=torch.bfloat16)
+    gs, gs_inv = H.get_nvfp4_global_scale(x, 256.0)
+    assert float(gs_inv) == C.global_scale_cpu(x.cpu(), 256.0)[1]
+    codes, scales = K.scalesweep_mse_nvfp4_quant_impl(x, gs_inv)
+    want_codes, want_scales = oracle.quant(0, oracle.bf16_bits(x.cpu()), float(gs_inv), nthreads=0)
+    assert np.array_equal(codes.cpu().numpy(), want_codes)
+    assert np.array_equal(scales.view(torch.uint8).cpu().numpy().reshape(-1), want_scales.reshape(-1))
+    # row independence: rows 4096..4223 alone give the same bytes as inside the full tensor
+    sub_c, sub_s = K.scalesweep_mse_nvfp4_quant_impl(x[4096:4224], gs_inv)
+    assert torch.equal(sub_c, codes[4096:4224])
+    full_sc = scales.view(torch.uint8).reshape(-1)
+    assert torch.equal(sub_s.view(torch.uint8).reshape(-1), full_sc[4096 * 512:4224 * 512])
+    # shard-and-concatenate checksum (the multi-GPU partitioning rule) equals the whole
+    from nvfp4quant_test_b200.sharding import row_shards, scale_slab
+
+    total = 0
+    for a, b in row_shards(8192, 8):
+        c_, s_ = K.scalesweep_mse_nvfp4_quant_impl(x[a:b], gs_inv)
+        lo, hi = scale_slab(a, b, 512)
+        assert torch.equal(s_.view(torch.uint8).reshape(-1), full_sc[lo:hi])
+        total += int(c_.long().sum())
+    assert total == int(codes.long().sum())
+    # quality: ScaleSweep's reconstruction error is below the amax baseline's on the same data
+    deq = H.dequantize_base(codes, K.unswizzle_vllm_fp4_scale(scales, 8192, 8192), gs)
+    mse, _ = H.error_stats(x, deq)
+    gs4, gs4_inv = H.get_nvfp4_global_scale(x, 448.0)
+    ac, a_s = K.amax_nvfp4_quant_impl(x, gs4_inv)
+    mse_amax, _ = H.error_stats(x, H.dequantize_base(ac, K.unswizzle_vllm_fp4_scale(a_s, 8192, 8192), gs4))
+    assert 0.0060 < mse < 0.0072 and 0.0085 < mse_amax < 0.0096
+
+
+def test_weighted_full_size_rows_sample(cuda_lib, oracle):
+    """Config 3 shape: [8192, 8192] Laplace weight, importance = channel square norms of a Laplace batch."""
+    import nvfp4quant_test_b200.kernels as K
+    from nvfp4quant_test_b200 import helper as H
+
+    w = torch.distributions.Laplace(0.0, 1.0).sample((2048, 8192)).bfloat16().cuda()
+    act = torch.distributions.Laplace(0.0, 1.0).sample((512, 8192)).bfloat16().cuda()
+    imp = (act.float() ** 2).sum(0, keepdim=True)
+    gs, gs_inv = H.get_nvfp4_global_scale(w, 256.0)
+    codes, scales = K.scalesweep_weighted_mse_nvfp4_quant_impl(w, imp, gs_inv)
+    want_codes, want_scales = oracle.quant(1, oracle.bf16_bits(w.cpu()), float(gs_inv), imp.cpu().numpy(),
+                                           lower=-8, upper=7)
+    assert np.array_equal(codes.cpu().numpy(), want_codes)
+    assert np.array_equal(scales.view(torch.uint8).cpu().numpy().reshape(-1), want_scales.reshape(-1))
+
+
+def test_global_scale_kernel(cuda_lib):
+    from nvfp4quant_test_b200 import helper as H
+
+    for shape, dt in (((128, 8192), torch.bfloat16), ((33, 64), torch.float16), ((16, 128), torch.float32),
+                      ((1, 7), torch.bfloat16), ((1000, 1001), torch.bfloat16), ((3000, 4096), torch.float32)):
+        x = C._gauss(shape, 11, dt).cuda()
+        for fm in (448.0, 256.0):
+            for _ in range(2):   # the scratch words must come back to zero between calls
+                gs, gs_inv = H.get_nvfp4_global_scale(x, fm)
+                cg, cgi = C.global_scale_cpu(x.cpu(), fm)
+                assert float(gs) == cg and float(gs_inv) == cgi
+                ref = x.abs().max().float() / (6.0 * fm)          # helper.py:96-100 as torch runs it on CUDA
+                assert bool(gs == ref) and bool(gs_inv == ref.reciprocal())
+    x = torch.zeros(64, 64, dtype=torch.bfloat16, device="cuda")
+    x[3, 3] = float("nan")
+    gs, _ = H.get_nvfp4_global_scale(x)
+    assert torch.isnan(gs)
+
+
+def test_div_full_table_matches_oracle(cuda_lib, oracle):
+    """The table the oracle uses for 1/scale is what this GPU's div.full.f32 returns."""
+    from nvfp4quant_test_b200 import _lib
+
+    t = torch.zeros(128, dtype=torch.int32, device="cuda")
+    _lib.check(cuda_lib.nvfp4_probe_div_full_table(t.data_ptr(), None), "probe")
+    torch.cuda.synchronize()
+    bits = t.cpu().numpy().view(np.uint32)
+    for raw in range(1, 127):
+        assert int(bits[raw]) == oracle.lib().nvfp4_oracle_div_full_bits(raw), raw

@@ -1,0 +1,94 @@
+"""CPU: the host-side mirror of the reference's `kernels` package - names, signatures, allocation
+contract and error behaviour (no kernel is launched here)."""
+import inspect
+
+import pytest
+import torch
+
+
+def test_module_surface_matches_the_reference():
+    from nvfp4quant_test_b200.kernels import kernel_ScaleSweep as W
+    from nvfp4quant_test_b200.kernels import kernel_ScaleSweep_MSE as M
+    from nvfp4quant_test_b200.kernels import kernel_vllm as V
+
+    assert (M.BLOCK_SIZE, M.LOWER_BOUND, M.UPPER_BOUND) == (16, -3, 7)
+    assert (W.BLOCK_SIZE, W.LOWER_BOUND, W.UPPER_BOUND) == (16, -8, 7)
+    sig = inspect.signature(M.scalesweep_mse_nvfp4_quant_impl)
+    assert list(sig.parameters) == ["input", "input_scale", "is_sf_swizzled_layout", "padded_n"]
+    sig = inspect.signature(M.scalesweep_mse_nvfp4_quant_out)
+    assert list(sig.parameters) == ["input", "input_scale", "is_sf_swizzled_layout", "output", "output_scale"]
+    assert sig.parameters["output"].kind is inspect.Parameter.KEYWORD_ONLY
+    sig = inspect.signature(W.scalesweep_weighted_mse_nvfp4_quant_impl)
+    assert list(sig.parameters) == ["input", "importance", "input_scale", "is_sf_swizzled_layout", "padded_n",
+                                    "lower_bound", "upper_bound"]
+    assert sig.parameters["lower_bound"].default == -8 and sig.parameters["upper_bound"].default == 7
+    sig = inspect.signature(W.scalesweep_weighted_mse_nvfp4_quant_out)
+    assert list(sig.parameters) == ["input", "importance", "input_scale", "is_sf_swizzled_layout", "output",
+                                    "output_scale", "lower_bound", "upper_bound"]
+    assert V.round_up(130, 128) == 256 and V.round_up(128, 128) == 128
+    import nvfp4quant_test_b200.kernels as K
+
+    for name in ("scalesweep_mse_round_nvfp4_quant_impl", "amax_nvfp4_quant_impl", "scaled_fp4_quant",
+                 "nvfp4_scaled_mm", "cutlass_scaled_fp4_mm", "create_fp4_output_tensors"):
+        assert hasattr(K, name)
+
+
+def test_output_allocation_contract():
+    """Shapes and dtypes of vllm's create_fp4_output_tensors (vllm/_custom_ops.py:36-86)."""
+    from nvfp4quant_test_b200.kernels import create_fp4_output_tensors
+
+    c, s = create_fp4_output_tensors(130, 208, "cpu", True)
+    assert c.shape == (130, 104) and c.dtype == torch.uint8
+    assert s.shape == (256, 4) and s.dtype == torch.int32          # round_up(13, 4) / 4 int32 per row
+    c, s = create_fp4_output_tensors(130, 208, "cpu", True, padded_n=256)
+    assert c.shape == (130, 128) and s.shape == (256, 4)
+    c, s = create_fp4_output_tensors(7, 48, "cpu", False)
+    assert c.shape == (7, 24) and s.shape == (7, 3) and s.dtype == torch.uint8
+
+
+def test_weighted_input_checks_raise_value_error():
+    """Same conditions as the reference's _check_inputs (kernels/kernel_ScaleSweep.py:419-433)."""
+    from nvfp4quant_test_b200.kernels import scalesweep_weighted_mse_nvfp4_quant_impl as q
+
+    gs = torch.ones(1)
+    with pytest.raises(ValueError, match="input must be 2D"):
+        q(torch.zeros(4, 4, 16), torch.ones(1, 16), gs)
+    with pytest.raises(ValueError, match="divisible by 16"):
+        q(torch.zeros(4, 24), torch.ones(1, 24), gs)
+    with pytest.raises(ValueError, match=r"importance must have shape \[1, dim\]"):
+        q(torch.zeros(4, 32), torch.ones(32), gs)
+    with pytest.raises(ValueError, match=r"importance must have shape \[1, dim\]"):
+        q(torch.zeros(4, 32), torch.ones(1, 16), gs)
+
+
+def test_no_cpu_fallback():
+    """CPU tensors are rejected: the product path has no CPU implementation."""
+    import nvfp4quant_test_b200.kernels as K
+
+    x = torch.zeros(4, 32, dtype=torch.bfloat16)
+    gs = torch.ones(1)
+    with pytest.raises(ValueError, match="CUDA tensor"):
+        K.scalesweep_mse_nvfp4_quant_impl(x, gs)
+    with pytest.raises(ValueError, match="CUDA tensor"):
+        K.amax_nvfp4_quant_impl(x, gs)
+    with pytest.raises(ValueError, match="CUDA tensor"):
+        K.scalesweep_weighted_mse_nvfp4_quant_impl(x, torch.ones(1, 32), gs)
+    with pytest.raises(ValueError, match="CUDA"):
+        K.nvfp4_scaled_mm(torch.zeros(4, 32, dtype=torch.uint8), torch.zeros(4, 32, dtype=torch.uint8),
+                          torch.zeros(128, 4, dtype=torch.uint8), torch.zeros(128, 4, dtype=torch.uint8),
+                          torch.ones(1), torch.bfloat16)
+    from nvfp4quant_test_b200 import helper as H
+
+    with pytest.raises(ValueError, match="CUDA"):
+        H.get_nvfp4_global_scale(x)
+
+
+def test_product_package_never_imports_the_oracle():
+    import pathlib
+
+    pkg = pathlib.Path(__file__).resolve().parents[1] / "nvfp4quant_test_b200"
+    for f in pkg.rglob("*.py"):
+        text = f.read_text()
+        assert "oracle" not in text.replace("the CPU oracle", ""), f"{f} mentions the oracle"
+    for f in pkg.rglob("*.cu*"):
+        assert "nvfp4_oracle" not in f.read_text()

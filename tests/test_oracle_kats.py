@@ -1,0 +1,147 @@
+"""CPU: the oracle against the reference's own known answers and format definitions."""
+import json
+import pathlib
+
+import numpy as np
+import pytest
+import torch
+
+GOLDEN = pathlib.Path(__file__).resolve().parent / "golden"
+
+
+def test_e4m3_roundtrip_and_rounding(oracle):
+    vals = [oracle.e4m3_to_f32(r) for r in range(127)]
+    assert vals[0] == 0.0 and vals[1] == 2.0 ** -9 and vals[8] == 2.0 ** -6 and vals[126] == 448.0
+    assert all(b > a for a, b in zip(vals, vals[1:]))
+    for r in range(127):
+        assert oracle.f32_to_e4m3(vals[r]) == r
+    # ties go to the even mantissa, everything above 448 saturates, NaN -> 0x7f
+    for r in range(1, 126):
+        mid = (vals[r] + vals[r + 1]) / 2
+        assert oracle.f32_to_e4m3(mid) == (r if r % 2 == 0 else r + 1)
+        assert oracle.f32_to_e4m3(float(np.nextafter(np.float32(mid), np.float32(0)))) == r
+        assert oracle.f32_to_e4m3(float(np.nextafter(np.float32(mid), np.float32(1e9)))) == r + 1
+    assert oracle.f32_to_e4m3(1e30) == 126 and oracle.f32_to_e4m3(float("inf")) == 126
+    assert oracle.f32_to_e4m3(float("nan")) == 127
+    assert oracle.f32_to_e4m3(464.0) == 126
+    # matches torch's float8_e4m3fn cast wherever that cast is finite
+    xs = torch.linspace(0, 440, 100001, dtype=torch.float32)
+    tb = xs.to(torch.float8_e4m3fn).view(torch.uint8).numpy()
+    ob = np.array([oracle.f32_to_e4m3(float(v)) for v in xs[::97]], dtype=np.uint8)
+    assert np.array_equal(ob, tb[::97])
+
+
+def test_e2m1_rounding_matches_lut_nearest_even(oracle):
+    """Quantize single values with scale 1 (raw 0x38) through the amax path's table hook."""
+    grid = np.array([0, .5, 1, 1.5, 2, 3, 4, 6], dtype=np.float32)
+    probe = np.array([0.0, 0.2, 0.25, 0.26, 0.75, 1.25, 1.75, 2.5, 3.5, 5.0, 5.01, 6.0, 7.0, 100.0,
+                      -0.25, -0.75], dtype=np.float32)
+    expect = np.array([0, 0, 0, 1, 2, 2, 4, 4, 6, 6, 7, 7, 7, 7, 8, 10])
+    x = np.zeros((1, 16), dtype=np.float32)
+    x[0, :] = probe
+    table = np.ones(128, dtype=np.float32)  # multiplier 1 for every scale byte
+    table[127] = 1.0 / 6.0
+    codes, _ = oracle.quant(2, x, 1.0, swizzled=False, amax_table=table, amax_sixth=1.0 / 6.0)
+    nib = np.stack([codes[0] & 0xF, codes[0] >> 4], -1).reshape(-1)
+    assert np.array_equal(nib, expect)
+    assert np.allclose(grid[nib[:14] & 7], [0, 0, 0, .5, 1, 1, 2, 2, 4, 4, 6, 6, 6, 6])
+
+
+def test_proof_known_answers(oracle):
+    """proof/nvfp4_bound_example.py: the sweep must return the exhaustive optimum q0 + offset."""
+    rows = json.loads((GOLDEN / "proof_kats.json").read_text())
+    assert len(rows) == 37
+    checked = 0
+    for k in rows:
+        x = np.array(k["x_f64"], dtype=np.float32)
+        base = oracle.f32_to_e4m3(float(np.float32(np.abs(x).max()) * np.float32(1 / 6)))
+        assert base == k["q0_bits"], k
+        assert oracle.best_raw_exhaustive(x) == k["best_bits"] == k["q0_bits"] + k["offset"], k
+        if -3 <= k["offset"] <= 7:
+            assert oracle.sweep_block(0, x) == k["best_bits"], k
+            checked += 1
+        else:  # the saturation b=6 example needs -4: outside the window by construction
+            assert (k["part"], k["b"], k["offset"]) == ("saturation", 6, -4)
+            assert oracle.sweep_block(0, x) != k["best_bits"]
+            assert oracle.sweep_block(0, x, lower=-4, upper=7) == k["best_bits"]
+    assert checked == 36
+
+
+def test_weighted_with_unit_weights_equals_exhaustive_on_kats(oracle):
+    """With all-ones importance and the wider -8..+7 window the weighted variant also finds the optimum."""
+    rows = json.loads((GOLDEN / "proof_kats.json").read_text())
+    w = np.ones(16, dtype=np.float32)
+    for k in rows:
+        x = np.array(k["x_f64"], dtype=np.float32)
+        assert oracle.sweep_block(1, x, w, lower=-8, upper=7) == k["best_bits"], k
+
+
+def test_swizzle_offset_is_the_reference_permutation(oracle):
+    """kernels/kernel_vllm.py:29-48: reshape(m/128, 4, 32, k/4, 4).permute(0, 3, 2, 1, 4)."""
+    from nvfp4quant_test_b200.kernels import kernel_vllm as kv
+
+    for m, k in ((1, 4), (130, 13), (128, 512), (300, 20), (257, 64)):
+        m_pad, k_pad = kv.round_up(m, 128), kv.round_up(k, 4)
+        lin = torch.arange(m_pad * k_pad, dtype=torch.int32).reshape(m_pad, k_pad)
+        perm = lin.reshape(m_pad // 128, 4, 32, k_pad // 4, 4).permute(0, 3, 2, 1, 4).reshape(-1)
+        # perm[offset] = linear index stored at that offset
+        for row, col in ((0, 0), (m - 1, k - 1), (min(m - 1, 37), min(k - 1, 2)), (m // 2, k // 2)):
+            off = oracle.swizzled_offset(row, col, k_pad)
+            assert perm[off].item() == row * k_pad + col
+        scale = torch.randint(0, 127, (m, k), dtype=torch.uint8)
+        sw = kv.swizzle_vllm_fp4_scale(scale, m, k * 16)
+        padded = torch.zeros((m_pad, k_pad), dtype=torch.uint8)
+        padded[:m, :k] = scale
+        ref = padded.reshape(m_pad // 128, 4, 32, k_pad // 4, 4).permute(0, 3, 2, 1, 4).reshape(-1)
+        assert torch.equal(sw, ref)
+        assert torch.equal(kv.unswizzle_vllm_fp4_scale(sw, m, k * 16), scale)
+        f8 = scale.view(torch.float8_e4m3fn)
+        assert torch.equal(kv.unswizzle_vllm_fp4_scale(kv.swizzle_vllm_fp4_scale(f8, m, k * 16), m, k * 16).view(torch.uint8), scale)
+
+
+def test_degenerate_blocks(oracle):
+    """All-zero and padded blocks store scale byte 0x01 and zero codes; sign of zero is kept."""
+    x = np.zeros((2, 32), dtype=np.float32)
+    x[1, :16] = -0.0
+    codes, scales = oracle.quant(0, x, 1.0, swizzled=False, padded_n=48)
+    assert scales.tolist() == [[1, 1, 1], [1, 1, 1]]
+    assert (codes[0] == 0).all() and (codes[1, :8] == 0x88).all() and (codes[1, 8:] == 0).all()
+    codes, scales = oracle.quant(1, x, 1.0, np.ones(32, np.float32), swizzled=False, padded_n=48, lower=-8, upper=7)
+    assert scales.tolist() == [[1, 1, 1], [1, 1, 1]]
+    # NaN never wins: a block of NaN keeps best_raw 0
+    x[0, :16] = np.nan
+    codes, scales = oracle.quant(0, x, 1.0, swizzled=False)
+    assert scales[0, 0] == 0
+
+
+def test_dequant_and_error_statistics(oracle):
+    """Oracle dequant == the reference formula LUT[nibble] * scale * gs (helper.py:134-147)."""
+    import cases as C
+    from nvfp4quant_test_b200 import helper as H
+    from nvfp4quant_test_b200.kernels import kernel_vllm as kv
+
+    x = C._gauss((64, 256), 3)
+    gs, gs_inv = C.global_scale_cpu(x, 256.0)
+    codes, scales = oracle.quant(0, oracle.bf16_bits(x), gs_inv)
+    deq = oracle.dequant(codes, scales, gs)
+    sc = kv.unswizzle_vllm_fp4_scale(torch.from_numpy(scales.reshape(-1)).view(torch.float8_e4m3fn), 64, 256)
+    deq_t = H.dequantize_base(torch.from_numpy(codes), sc, torch.tensor(gs))
+    assert np.array_equal(deq, deq_t.numpy())
+    mse, max_abs = H.error_stats(x, deq_t)
+    # ScaleSweep beats the amax baseline on the same data (ratio ~0.79 in README.md:58-63; ~0.74 here)
+    gs4, gs4_inv = C.global_scale_cpu(x, 448.0)
+    c2, s2 = oracle.quant(2, oracle.bf16_bits(x), gs4_inv)
+    mse_amax, _ = H.error_stats(x, torch.from_numpy(oracle.dequant(c2, s2, gs4)))
+    assert 0.005 < mse < 0.008 and 0.007 < mse_amax < 0.011 and mse < 0.85 * mse_amax
+
+
+@pytest.mark.parametrize("variant", [0, 1])
+def test_window_clamps_at_both_ends(oracle, variant):
+    """Tiny blocks clamp candidates at raw 1, huge ones at raw 126 (kernel_ScaleSweep_MSE.py:327-330)."""
+    w = np.ones(16, np.float32)
+    tiny = np.full(16, 2.0 ** -12, np.float32)
+    huge = np.full(16, 1e6, np.float32)
+    lo, up = ((-3, 7), (-8, 7))[variant]
+    r_tiny = oracle.sweep_block(variant, tiny, w, lo, up)
+    r_huge = oracle.sweep_block(variant, huge, w, lo, up)
+    assert 1 <= r_tiny <= 8 and r_huge == 126
