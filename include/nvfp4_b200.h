@@ -30,7 +30,8 @@ enum {
     NVFP4_ERR_BAD_RANGE = -5,    /* upper < lower or more than 64 candidates */
     NVFP4_ERR_WORKSPACE = -6,    /* workspace too small */
     NVFP4_ERR_UNSUPPORTED = -7,
-    NVFP4_ERR_TOO_LARGE = -8
+    NVFP4_ERR_TOO_LARGE = -8,
+    NVFP4_ERR_STATIC_SCRATCH = -9 /* input needs more scratch than the library's built-in array holds */
 };
 
 enum { NVFP4_VARIANT_MSE = 0, NVFP4_VARIANT_WEIGHTED = 1, NVFP4_VARIANT_AMAX = 2 };
@@ -85,6 +86,25 @@ int nvfp4_quant_launch_impl(int impl, int variant, const void* x, int x_dtype, c
  */
 int nvfp4_global_scale_launch(const void* x, int x_dtype, int64_t numel, float fp8_max, float* out,
                               uint32_t* scratch, void* stream);
+
+/*
+ * The same result as nvfp4_global_scale_launch for callers that cannot allocate device memory
+ * (this entry point has no counterpart in the reference).  Typical callers: a plugin that only
+ * receives raw device pointers from a runtime which owns all allocations, a serving process whose
+ * memory pool is frozen, code running where cudaMalloc is not permitted.  The block-level partial
+ * maxima live in an array compiled into the library (16.25 KiB per GPU, held until process exit)
+ * instead of caller-provided scratch, and the call performs no allocation of any kind.
+ *   - Limit: numel * sizeof(element) <= nvfp4_global_scale_static_max_bytes() (512 MiB); larger
+ *     inputs return NVFP4_ERR_STATIC_SCRATCH and launch nothing.
+ *   - The first call on each device resolves the array's device address (with that device
+ *     current); issue it before starting any stream capture.
+ *   - All calls on one GPU share the array: calls that may overlap on the GPU (other streams or
+ *     host threads) race and must be serialised by the caller.  Calls in one stream are safe; each
+ *     call re-clears the counter it relies on.
+ */
+int nvfp4_global_scale_launch_static(const void* x, int x_dtype, int64_t numel, float fp8_max, float* out,
+                                     void* stream);
+int64_t nvfp4_global_scale_static_max_bytes(void);
 
 /*
  * out[M, N] (bf16, row-major) = alpha * sum_k dq(a)[m,k] * dq(b)[n,k]

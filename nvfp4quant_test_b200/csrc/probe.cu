@@ -44,6 +44,7 @@ extern "C" const char* nvfp4_status_string(int status) {
         case NVFP4_ERR_WORKSPACE: return "workspace is NULL or too small";
         case NVFP4_ERR_UNSUPPORTED: return "unsupported configuration";
         case NVFP4_ERR_TOO_LARGE: return "problem exceeds the supported size";
+        case NVFP4_ERR_STATIC_SCRATCH: return "input is larger than the library's built-in scratch array can serve (see nvfp4_global_scale_static_max_bytes)";
         default: break;
     }
     if (status > 0) return cudaGetErrorString(static_cast<cudaError_t>(status));
