@@ -123,6 +123,9 @@ int nvfp4_gemm_launch(const uint8_t* a, const uint8_t* b, const uint8_t* sfa, co
                       const float* alpha, void* out_bf16, int64_t M, int64_t N, int64_t K,
                       void* workspace, size_t workspace_bytes, void* stream);
 size_t nvfp4_gemm_workspace_bytes(int64_t M, int64_t N, int64_t K);
+/* Testing hook (process-wide): 0 = pick the GEMM kernel by shape (default), 1 = 128x128 tiles,
+ * 2 = 128x256 tiles, 3 = CTA-pair 256x256 tiles.  All paths give identical results. */
+int nvfp4_gemm_force_path(int path);
 
 /* Device status word of the last GEMM on this device: 0 = ok, else a bounded
  * wait inside the kernel gave up (the kernel returned without hanging).

@@ -31,6 +31,10 @@ constexpr int kTmemCols = 512;
 constexpr uint64_t kWaitLimitNs = 2000000000ull;  // 2 s: far above any legitimate wait
 
 __device__ uint32_t g_gemm_status;  // 0 = ok; else (role << 24) | detail of the wait that expired
+// Per-CTA cycle counters of the last launch (diagnostics): [cta][0] MMA loop total, [1] MMA waiting for data,
+// [2] MMA waiting for a free accumulator, [3] producer waiting for a free slot, [4] epilogue waiting for the
+// accumulator, [5] epilogue draining it, [6] tiles done by this CTA.
+__device__ unsigned long long g_gemm_cycles[160][8];
 
 template <int BN>
 struct Cfg {
@@ -42,9 +46,12 @@ struct Cfg {
     static constexpr int kSfbBytes = 2048 * kNG;
     static constexpr int kStageBytes = kABytes + kBBytes + kSfaBytes + kSfbBytes;
     static constexpr int kSmemBytes = kStages * kStageBytes + 1024 /*align*/ + 256 /*barriers*/;
-    static constexpr int kSfaCol = kAcc * BN;               // TMEM column of the A scales
-    static constexpr int kSfbCol = kSfaCol + 16;            // TMEM column of the B scales
-    static_assert(kSfbCol + 16 * kNG <= kTmemCols, "TMEM budget");
+    // scale factors sit behind the accumulators, in two sets used by alternate K tiles so that the
+    // copies for the next K tile do not have to wait for the MMAs still reading the current set
+    static constexpr int kSfSetCols = 16 + 16 * kNG;
+    static constexpr int kSfaCol = kAcc * BN;               // TMEM column of the A scales (set 0)
+    static constexpr int kSfbCol = kSfaCol + 16;            // TMEM column of the B scales (set 0)
+    static_assert(kSfaCol + 2 * kSfSetCols <= kTmemCols, "TMEM budget");
 };
 
 // ---------------------------------------------------------------------------------------------
@@ -133,6 +140,38 @@ __device__ __forceinline__ void tc_ld_32x32b_x32(uint32_t taddr, uint32_t v[32])
 }
 __device__ __forceinline__ void tc_ld_wait() { asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory"); }
 
+// One lane of a converged warp (elect.sync).  The MMA warp runs its loops with all 32 lanes so that stage
+// indices, descriptors and TMEM addresses stay warp-uniform (they then live in uniform registers, which is
+// what the tcgen05 instructions take); only the tcgen05 instruction itself is issued by the elected lane.
+__device__ __forceinline__ bool elect_one() {
+    uint32_t pred;
+    asm volatile("{ .reg .b32 rx; .reg .pred px; elect.sync rx|px, 0xffffffff; selp.u32 %0, 1, 0, px; }" : "=r"(pred));
+    return pred != 0;
+}
+// Bounded wait executed by the whole warp; the verdict is lane 0's, so it is uniform.
+__device__ __forceinline__ bool mbar_wait_warp(uint32_t bar, uint32_t parity, volatile uint32_t* abort_flag, uint32_t code) {
+    const bool ok = mbar_wait(bar, parity, abort_flag, code);
+    return __shfl_sync(0xffffffffu, ok ? 1 : 0, 0) != 0;
+}
+
+// Descriptors as (lo, hi) words: hi is a constant per operand kind, lo = (smem address >> 4) [| LBO], so stepping
+// through a tile is one 32-bit add.  Keeps the single issuing thread to a few instructions per tcgen05 op.
+constexpr uint32_t kDescHiSw128 = (1024u >> 4) | (1u << 14) | (2u << 29);   // SBO 1024 B, version 1, 128-byte swizzle
+constexpr uint32_t kDescHiSf = (128u >> 4) | (1u << 14);                   // SBO 128 B, version 1, no swizzle
+__device__ __forceinline__ void tc_cp_lohi(uint32_t taddr, uint32_t lo) {
+    asm volatile("{ .reg .b64 d; mov.b64 d, {%1, %2}; tcgen05.cp.cta_group::1.32x128b.warpx4 [%0], d; }" ::"r"(taddr),
+                 "r"(lo), "r"(kDescHiSf)
+                 : "memory");
+}
+__device__ __forceinline__ void tc_mma_lohi(uint32_t d_tmem, uint32_t a_lo, uint32_t b_lo, uint32_t idesc, uint32_t sfa_tmem,
+                                            uint32_t sfb_tmem, uint32_t accumulate) {
+    asm volatile(
+        "{ .reg .pred p; .reg .b64 da, db; setp.ne.b32 p, %4, 0; mov.b64 da, {%1, %7}; mov.b64 db, {%2, %7};\n"
+        "  tcgen05.mma.cta_group::1.kind::mxf4nvf4.block_scale.block16 [%0], da, db, %3, [%5], [%6], p; }" ::"r"(d_tmem),
+        "r"(a_lo), "r"(b_lo), "r"(idesc), "r"(accumulate), "r"(sfa_tmem), "r"(sfb_tmem), "r"(kDescHiSw128)
+        : "memory");
+}
+
 // K-major operand tile, 128-byte swizzle: rows are 128 B apart, 8-row groups 1024 B apart.
 __device__ __forceinline__ uint64_t smem_desc_sw128(uint32_t addr) {
     return static_cast<uint64_t>((addr & 0x3ffffu) >> 4) | (1ull << 16) | (static_cast<uint64_t>(1024 >> 4) << 32) |
@@ -213,23 +252,30 @@ gemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant__ 
 
     if (warp == 0) {
         // ------------------------------------------------------------------ producer
-        if (lane == 0) {
-            asm volatile("prefetch.tensormap [%0];" ::"l"(&tmap_a) : "memory");
-            asm volatile("prefetch.tensormap [%0];" ::"l"(&tmap_b) : "memory");
+        {
+            const bool issuer = elect_one();
+            if (issuer) {
+                asm volatile("prefetch.tensormap [%0];" ::"l"(&tmap_a) : "memory");
+                asm volatile("prefetch.tensormap [%0];" ::"l"(&tmap_b) : "memory");
+            }
             int stage = 0;
             uint32_t phase = 0;
             bool ok = true;
+            long long w_empty = 0;
             for (int tile = blockIdx.x; ok && tile < total_tiles; tile += gridDim.x) {
                 const int mt = tile % m_tiles, nt = tile / m_tiles;
                 for (int kt = 0; kt < k_tiles; ++kt) {
-                    if (!(ok = mbar_wait(empty_bar(stage), phase ^ 1u, abort_flag, (1u << 24) | kt))) break;
+                    const long long c0 = clock64();
+                    if (!(ok = mbar_wait_warp(empty_bar(stage), phase ^ 1u, abort_flag, (1u << 24) | kt))) break;
+                    w_empty += clock64() - c0;
                     const int kb_count = min(4, (p.K - kt * kBK + 63) / 64);  // 64-element K blocks in this stage
                     const uint32_t sf_bytes = 512u * kb_count;
                     int sfb_present = 0;
                     for (int g = 0; g < C::kNG; ++g) sfb_present += (nt * C::kNG + g < p.sfb_groups) ? 1 : 0;
                     const uint32_t tx = C::kABytes + C::kBBytes + sf_bytes * (1 + sfb_present);
-                    mbar_expect_tx(full_bar(stage), tx);
                     const uint32_t sbase = base + stage * C::kStageBytes;
+                    if (issuer) {
+                    mbar_expect_tx(full_bar(stage), tx);
                     tma_load_2d(sbase, &tmap_a, kt * kBKBytes, mt * kBM, full_bar(stage));
                     tma_load_2d(sbase + C::kABytes, &tmap_b, kt * kBKBytes, nt * BN, full_bar(stage));
                     bulk_load_1d(sbase + C::kABytes + C::kBBytes,
@@ -243,58 +289,94 @@ gemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant__ 
                                              static_cast<int64_t>(kt) * 2048,
                                          sf_bytes, full_bar(stage));
                     }
+                    }
+                    __syncwarp();
                     if (++stage == kStages) {
                         stage = 0;
                         phase ^= 1u;
                     }
                 }
             }
+            if (issuer && blockIdx.x < 160) g_gemm_cycles[blockIdx.x][3] = w_empty;
         }
     } else if (warp == 1) {
         // ------------------------------------------------------------------ MMA issuer
-        if (lane == 0) {
+        {
+            const bool issuer = elect_one();
             constexpr uint32_t idesc = instr_desc<BN>();
             int stage = 0;
             uint32_t phase = 0;
             int acc = 0;
             uint32_t acc_phase = 0;
             bool ok = true;
+            long long w_full = 0, w_acc = 0, ntile = 0;
+            const long long t_begin = clock64();
             for (int tile = blockIdx.x; ok && tile < total_tiles; tile += gridDim.x) {
-                if (!(ok = mbar_wait(tempty_bar(acc), acc_phase ^ 1u, abort_flag, (2u << 24) | 0xffff))) break;
+                long long c0 = clock64();
+                if (!(ok = mbar_wait_warp(tempty_bar(acc), acc_phase ^ 1u, abort_flag, (2u << 24) | 0xffff))) break;
+                w_acc += clock64() - c0;
+                ++ntile;
                 tc_fence_after();
                 const uint32_t d_tmem = tmem_base + acc * BN;
                 for (int kt = 0; kt < k_tiles; ++kt) {
-                    if (!(ok = mbar_wait(full_bar(stage), phase, abort_flag, (2u << 24) | kt))) break;
+                    c0 = clock64();
+                    if (!(ok = mbar_wait_warp(full_bar(stage), phase, abort_flag, (2u << 24) | kt))) break;
+                    w_full += clock64() - c0;
                     tc_fence_after();
                     const int kb_count = min(4, (p.K - kt * kBK + 63) / 64);
                     const uint32_t sbase = base + stage * C::kStageBytes;
-                    const uint32_t sfa_s = sbase + C::kABytes + C::kBBytes;
-                    const uint32_t sfb_s = sfa_s + C::kSfaBytes;
-                    for (int kb = 0; kb < kb_count; ++kb) {
-                        tc_cp_32x128b_warpx4(tmem_base + C::kSfaCol + 4 * kb, smem_desc_sf(sfa_s + 512 * kb));
-                        for (int g = 0; g < C::kNG; ++g)
-                            tc_cp_32x128b_warpx4(tmem_base + C::kSfbCol + 4 * C::kNG * kb + 4 * g,
-                                                 smem_desc_sf(sfb_s + 2048 * g + 512 * kb));
+                    const uint32_t a_lo = ((sbase & 0x3ffffu) >> 4) | (1u << 16);
+                    const uint32_t b_lo = a_lo + (C::kABytes >> 4);
+                    const uint32_t sfa_lo = ((sbase + C::kABytes + C::kBBytes) & 0x3ffffu) >> 4;
+                    const uint32_t sfb_lo = sfa_lo + (C::kSfaBytes >> 4);
+                    const uint32_t set = (kt & 1) * C::kSfSetCols;
+                    const uint32_t sfa_t = tmem_base + C::kSfaCol + set;
+                    const uint32_t sfb_t = tmem_base + C::kSfbCol + set;
+                    const uint32_t first = kt > 0 ? 1u : 0u;
+                    if (!issuer) {
+                        // nothing to issue on this lane
+                    } else if (kb_count == 4) {
+#pragma unroll
+                        for (int kb = 0; kb < 4; ++kb) {
+                            tc_cp_lohi(sfa_t + 4 * kb, sfa_lo + 32 * kb);
+#pragma unroll
+                            for (int g = 0; g < C::kNG; ++g)
+                                tc_cp_lohi(sfb_t + 4 * C::kNG * kb + 4 * g, sfb_lo + 128 * g + 32 * kb);
+                        }
+#pragma unroll
+                        for (int kb = 0; kb < 4; ++kb)   // 32 bytes of K per instruction: start address + 2 (x16 B)
+                            tc_mma_lohi(d_tmem, a_lo + 2 * kb, b_lo + 2 * kb, idesc, sfa_t + 4 * kb, sfb_t + 4 * C::kNG * kb,
+                                        kb == 0 ? first : 1u);
+                    } else {
+                        for (int kb = 0; kb < kb_count; ++kb) {
+                            tc_cp_lohi(sfa_t + 4 * kb, sfa_lo + 32 * kb);
+                            for (int g = 0; g < C::kNG; ++g)
+                                tc_cp_lohi(sfb_t + 4 * C::kNG * kb + 4 * g, sfb_lo + 128 * g + 32 * kb);
+                        }
+                        for (int kb = 0; kb < kb_count; ++kb)
+                            tc_mma_lohi(d_tmem, a_lo + 2 * kb, b_lo + 2 * kb, idesc, sfa_t + 4 * kb, sfb_t + 4 * C::kNG * kb,
+                                        kb == 0 ? first : 1u);
                     }
-                    const uint64_t adesc = smem_desc_sw128(sbase);
-                    const uint64_t bdesc = smem_desc_sw128(sbase + C::kABytes);
-                    for (int kb = 0; kb < kb_count; ++kb) {
-                        // 32 bytes of K per instruction: advance the descriptor start address by 2 (x16 B)
-                        tc_mma_nvf4(d_tmem, adesc + 2u * kb, bdesc + 2u * kb, idesc, tmem_base + C::kSfaCol + 4 * kb,
-                                    tmem_base + C::kSfbCol + 4 * C::kNG * kb, (kt > 0 || kb > 0) ? 1u : 0u);
-                    }
-                    tc_commit(empty_bar(stage));  // slot reusable once these MMAs have read it
+                    if (issuer) tc_commit(empty_bar(stage));  // slot reusable once these MMAs have read it
+                    __syncwarp();
                     if (++stage == kStages) {
                         stage = 0;
                         phase ^= 1u;
                     }
                 }
                 if (!ok) break;
-                tc_commit(tfull_bar(acc));  // accumulator complete
+                if (issuer) tc_commit(tfull_bar(acc));  // accumulator complete
+                __syncwarp();
                 if (++acc == C::kAcc) {
                     acc = 0;
                     acc_phase ^= 1u;
                 }
+            }
+            if (issuer && blockIdx.x < 160) {
+                g_gemm_cycles[blockIdx.x][0] = clock64() - t_begin;
+                g_gemm_cycles[blockIdx.x][1] = w_full;
+                g_gemm_cycles[blockIdx.x][2] = w_acc;
+                g_gemm_cycles[blockIdx.x][6] = ntile;
             }
         }
     } else {
@@ -305,11 +387,15 @@ gemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant__ 
         uint32_t acc_phase = 0;
         bool ok = true;
         const bool vec_ok = (p.N % 8) == 0;
+        long long w_tfull = 0, t_drain = 0;
         for (int tile = blockIdx.x; ok && tile < total_tiles; tile += gridDim.x) {
             const int mt = tile % m_tiles, nt = tile / m_tiles;
+            const long long c0 = clock64();
             ok = mbar_wait(tfull_bar(acc), acc_phase, abort_flag, (3u << 24) | (tile & 0xffff));
             ok = __shfl_sync(0xffffffffu, ok ? 1 : 0, 0) != 0;
             if (!ok) break;
+            const long long c1 = clock64();
+            w_tfull += c1 - c0;
             tc_fence_after();
             const int row = mt * kBM + sp * 32 + lane;
             __nv_bfloat16* orow = p.out + static_cast<int64_t>(row) * p.N;
@@ -342,10 +428,15 @@ gemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant__ 
             tc_fence_before();
             __syncwarp();
             if (lane == 0) mbar_arrive(tempty_bar(acc));
+            t_drain += clock64() - c1;
             if (++acc == C::kAcc) {
                 acc = 0;
                 acc_phase ^= 1u;
             }
+        }
+        if (warp == 2 && lane == 0 && blockIdx.x < 160) {
+            g_gemm_cycles[blockIdx.x][4] = w_tfull;
+            g_gemm_cycles[blockIdx.x][5] = t_drain;
         }
     }
 
@@ -417,10 +508,354 @@ static int launch(const uint8_t* a, const uint8_t* b, const GemmParams& p, cudaS
     return static_cast<int>(cudaGetLastError());
 }
 
+
+// =============================================================================================
+// Two-CTA variant (cta_group::2): a CTA pair owns a 256 x 256 output tile.  Each CTA loads its own
+// 128 rows of A and HALF of the B tile (128 of the 256 weight rows); the pair's tensor cores read
+// both halves, so B crosses L2 -> shared memory once per pair instead of once per CTA.  No
+// multicast load is involved: every TMA copy has exactly one destination CTA.  The CTA with
+// cluster rank 0 issues all MMAs; copies of both CTAs report to rank 0's "full" barrier
+// (cp.async.bulk.tensor ... .cta_group::2), and tcgen05.commit signals the "empty" and
+// "accumulator ready" barriers of both CTAs.
+// =============================================================================================
+namespace pair {
+
+constexpr int kStages2 = 5;
+constexpr int kABytes2 = 128 * kBKBytes;   // this CTA's 128 rows of A
+constexpr int kBBytes2 = 128 * kBKBytes;   // this CTA's half of the 256 B rows
+constexpr int kSfaBytes2 = 2048;           // scales of this CTA's A rows
+constexpr int kSfbBytes2 = 4096;           // scales of all 256 B rows (each CTA needs all of them)
+constexpr int kStageBytes2 = kABytes2 + kBBytes2 + kSfaBytes2 + kSfbBytes2;   // 38 KiB
+constexpr int kSmemBytes2 = kStages2 * kStageBytes2 + 1024 + 256;
+constexpr int kSfaCol2 = 256, kSfbCol2 = 272, kSfSetCols2 = 48;   // two scale sets: columns 256..351
+
+__device__ __forceinline__ uint32_t cluster_ctarank() {
+    uint32_t r;
+    asm volatile("mov.u32 %0, %%cluster_ctarank;" : "=r"(r));
+    return r;
+}
+__device__ __forceinline__ uint32_t map_to_cta(uint32_t smem_addr, uint32_t rank) {
+    uint32_t r;
+    asm volatile("mapa.shared::cluster.u32 %0, %1, %2;" : "=r"(r) : "r"(smem_addr), "r"(rank));
+    return r;
+}
+__device__ __forceinline__ void cluster_sync_all() {
+    asm volatile("barrier.cluster.arrive.release.aligned;" ::: "memory");
+    asm volatile("barrier.cluster.wait.acquire.aligned;" ::: "memory");
+}
+__device__ __forceinline__ void mbar_arrive_cluster(uint32_t cluster_addr) {
+    asm volatile("mbarrier.arrive.release.cluster.shared::cluster.b64 _, [%0];" ::"r"(cluster_addr) : "memory");
+}
+// tile load whose completion bytes are reported to a barrier that may live in the peer CTA
+__device__ __forceinline__ void tma_load_2d_pair(uint32_t dst, const CUtensorMap* map, int x, int y, uint32_t bar_cluster) {
+    asm volatile(
+        "cp.async.bulk.tensor.2d.cta_group::2.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1, {%2, %3}], [%4];" ::"r"(dst),
+        "l"(map), "r"(x), "r"(y), "r"(bar_cluster)
+        : "memory");
+}
+__device__ __forceinline__ void tc_commit_pair(uint32_t bar) {
+    asm volatile("tcgen05.commit.cta_group::2.mbarrier::arrive::one.shared::cluster.multicast::cluster.b64 [%0], %1;" ::"r"(bar),
+                 "h"(static_cast<uint16_t>(3))
+                 : "memory");
+}
+__device__ __forceinline__ void tc_cp_pair(uint32_t taddr, uint32_t lo) {
+    asm volatile("{ .reg .b64 d; mov.b64 d, {%1, %2}; tcgen05.cp.cta_group::2.32x128b.warpx4 [%0], d; }" ::"r"(taddr),
+                 "r"(lo), "r"(kDescHiSf)
+                 : "memory");
+}
+__device__ __forceinline__ void tc_mma_pair(uint32_t d_tmem, uint32_t a_lo, uint32_t b_lo, uint32_t idesc,
+                                            uint32_t sfa_tmem, uint32_t sfb_tmem, uint32_t accumulate) {
+    asm volatile(
+        "{ .reg .pred p; .reg .b64 da, db; setp.ne.b32 p, %4, 0; mov.b64 da, {%1, %7}; mov.b64 db, {%2, %7};\n"
+        "  tcgen05.mma.cta_group::2.kind::mxf4nvf4.block_scale.block16 [%0], da, db, %3, [%5], [%6], p; }" ::"r"(d_tmem),
+        "r"(a_lo), "r"(b_lo), "r"(idesc), "r"(accumulate), "r"(sfa_tmem), "r"(sfb_tmem), "r"(kDescHiSw128)
+        : "memory");
+}
+
+__global__ void __launch_bounds__(kThreads, 1)
+gemm_pair_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant__ CUtensorMap tmap_b,
+                 const __grid_constant__ CUtensorMap tmap_sfa, const __grid_constant__ CUtensorMap tmap_sfb,
+                 const GemmParams p) {
+    extern __shared__ uint8_t smem_raw[];
+    const uint32_t raw_addr = smem_u32(smem_raw);
+    const uint32_t base = (raw_addr + 1023u) & ~1023u;
+    uint8_t* aligned = smem_raw + (base - raw_addr);
+    uint64_t* bars = reinterpret_cast<uint64_t*>(aligned + kStages2 * kStageBytes2);
+    const uint32_t bar_base = smem_u32(bars);
+    auto full_bar = [&](int s) { return bar_base + 8u * s; };
+    auto empty_bar = [&](int s) { return bar_base + 8u * (kStages2 + s); };
+    const uint32_t tfull_bar = bar_base + 8u * (2 * kStages2);
+    const uint32_t tempty_bar = bar_base + 8u * (2 * kStages2 + 1);
+    volatile uint32_t* tmem_slot = reinterpret_cast<volatile uint32_t*>(bars + 2 * kStages2 + 2);
+    volatile uint32_t* abort_flag = tmem_slot + 1;
+
+    const int warp = __shfl_sync(0xffffffffu, threadIdx.x >> 5, 0);
+    const int lane = threadIdx.x & 31;
+    const uint32_t rank = cluster_ctarank();           // 0 = leader (issues the MMAs)
+    const int pair_id = blockIdx.x >> 1;
+    const int num_pairs = gridDim.x >> 1;
+
+    if (threadIdx.x == 0) {
+        for (int s = 0; s < kStages2; ++s) {
+            mbar_init(full_bar(s), 1);    // leader's producer; bytes of both CTAs' copies land here
+            mbar_init(empty_bar(s), 1);   // one tcgen05.commit
+        }
+        mbar_init(tfull_bar, 1);
+        mbar_init(tempty_bar, 8);         // 4 epilogue warps of each CTA
+        *abort_flag = 0;
+        asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+        asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
+    }
+    if (warp == 1) {
+        asm volatile("tcgen05.alloc.cta_group::2.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(
+                         smem_u32(const_cast<uint32_t*>(tmem_slot))),
+                     "r"(kTmemCols)
+                     : "memory");
+        asm volatile("tcgen05.relinquish_alloc_permit.cta_group::2.sync.aligned;" ::: "memory");
+    }
+    tc_fence_before();
+    __syncthreads();
+    cluster_sync_all();   // the peer's barriers exist before anything is signalled across CTAs
+    tc_fence_after();
+    const uint32_t tmem_base = *tmem_slot;
+
+    const int m_tiles = (p.M + 255) / 256;
+    const int n_tiles = (p.N + 255) / 256;
+    const int total_tiles = m_tiles * n_tiles;
+    const int k_tiles = (p.K + kBK - 1) / kBK;
+
+    if (warp == 0) {
+        // ------------------------------------------------------------------ producer (both CTAs)
+        {
+            const bool issuer = elect_one();
+            if (issuer) {
+            asm volatile("prefetch.tensormap [%0];" ::"l"(&tmap_a) : "memory");
+            asm volatile("prefetch.tensormap [%0];" ::"l"(&tmap_b) : "memory");
+            asm volatile("prefetch.tensormap [%0];" ::"l"(&tmap_sfa) : "memory");
+            asm volatile("prefetch.tensormap [%0];" ::"l"(&tmap_sfb) : "memory");
+            }
+            int stage = 0;
+            uint32_t phase = 0;
+            bool ok = true;
+            for (int tile = pair_id; ok && tile < total_tiles; tile += num_pairs) {
+                const int mt = tile % m_tiles, nt = tile / m_tiles;
+                for (int kt = 0; kt < k_tiles; ++kt) {
+                    if (!(ok = mbar_wait_warp(empty_bar(stage), phase ^ 1u, abort_flag, (1u << 24) | kt))) break;
+                    if (issuer) {
+                    if (rank == 0) mbar_expect_tx(full_bar(stage), 2u * kStageBytes2);
+                    const uint32_t lead_full = map_to_cta(full_bar(stage), 0);
+                    const uint32_t sbase = base + stage * kStageBytes2;
+                    tma_load_2d_pair(sbase, &tmap_a, kt * kBKBytes, mt * 256 + static_cast<int>(rank) * 128, lead_full);
+                    tma_load_2d_pair(sbase + kABytes2, &tmap_b, kt * kBKBytes, nt * 256 + static_cast<int>(rank) * 128, lead_full);
+                    // scale tiles: x counts 8-byte elements (2048 B per K tile), y = 128-row group
+                    tma_load_2d_pair(sbase + kABytes2 + kBBytes2, &tmap_sfa, kt * 256, mt * 2 + static_cast<int>(rank), lead_full);
+                    tma_load_2d_pair(sbase + kABytes2 + kBBytes2 + kSfaBytes2, &tmap_sfb, kt * 256, nt * 2, lead_full);
+                    tma_load_2d_pair(sbase + kABytes2 + kBBytes2 + kSfaBytes2 + 2048, &tmap_sfb, kt * 256, nt * 2 + 1, lead_full);
+                    }
+                    __syncwarp();
+                    if (++stage == kStages2) {
+                        stage = 0;
+                        phase ^= 1u;
+                    }
+                }
+            }
+        }
+    } else if (warp == 1) {
+        // ------------------------------------------------------------------ MMA issuer (leader only)
+        if (rank == 0) {
+            const bool issuer = elect_one();
+            constexpr uint32_t idesc = (1u << 7) | (1u << 10) | (static_cast<uint32_t>(256 >> 3) << 17) |
+                                       (static_cast<uint32_t>(256 >> 4) << 24);
+            int stage = 0;
+            uint32_t phase = 0, acc_phase = 0;
+            bool ok = true;
+            long long w_full = 0, w_acc = 0, ntile = 0, c0;
+            const long long t_begin = clock64();
+            for (int tile = pair_id; ok && tile < total_tiles; tile += num_pairs) {
+                c0 = clock64();
+                if (!(ok = mbar_wait_warp(tempty_bar, acc_phase ^ 1u, abort_flag, (2u << 24) | 0xffff))) break;
+                w_acc += clock64() - c0;
+                ++ntile;
+                tc_fence_after();
+                for (int kt = 0; kt < k_tiles; ++kt) {
+                    c0 = clock64();
+                    if (!(ok = mbar_wait_warp(full_bar(stage), phase, abort_flag, (2u << 24) | kt))) break;
+                    w_full += clock64() - c0;
+                    tc_fence_after();
+                    const int kb_count = min(4, (p.K - kt * kBK + 63) / 64);
+                    const uint32_t sbase = base + stage * kStageBytes2;
+                    const uint32_t a_lo = ((sbase & 0x3ffffu) >> 4) | (1u << 16);
+                    const uint32_t b_lo = a_lo + (kABytes2 >> 4);
+                    const uint32_t sfa_lo = ((sbase + kABytes2 + kBBytes2) & 0x3ffffu) >> 4;
+                    const uint32_t sfb_lo = sfa_lo + (kSfaBytes2 >> 4);
+                    const uint32_t set = (kt & 1) * kSfSetCols2;
+                    const uint32_t sfa_t = tmem_base + kSfaCol2 + set;
+                    const uint32_t sfb_t = tmem_base + kSfbCol2 + set;
+                    const uint32_t first = kt > 0 ? 1u : 0u;
+                    if (!issuer) {
+                        // nothing to issue on this lane
+                    } else if (kb_count == 4) {
+#pragma unroll
+                        for (int kb = 0; kb < 4; ++kb) {
+                            tc_cp_pair(sfa_t + 4 * kb, sfa_lo + 32 * kb);
+                            tc_cp_pair(sfb_t + 8 * kb, sfb_lo + 32 * kb);
+                            tc_cp_pair(sfb_t + 8 * kb + 4, sfb_lo + 128 + 32 * kb);
+                        }
+#pragma unroll
+                        for (int kb = 0; kb < 4; ++kb)
+                            tc_mma_pair(tmem_base, a_lo + 2 * kb, b_lo + 2 * kb, idesc, sfa_t + 4 * kb, sfb_t + 8 * kb,
+                                        kb == 0 ? first : 1u);
+                    } else {
+                        for (int kb = 0; kb < kb_count; ++kb) {
+                            tc_cp_pair(sfa_t + 4 * kb, sfa_lo + 32 * kb);
+                            tc_cp_pair(sfb_t + 8 * kb, sfb_lo + 32 * kb);
+                            tc_cp_pair(sfb_t + 8 * kb + 4, sfb_lo + 128 + 32 * kb);
+                        }
+                        for (int kb = 0; kb < kb_count; ++kb)
+                            tc_mma_pair(tmem_base, a_lo + 2 * kb, b_lo + 2 * kb, idesc, sfa_t + 4 * kb, sfb_t + 8 * kb,
+                                        kb == 0 ? first : 1u);
+                    }
+                    if (issuer) tc_commit_pair(empty_bar(stage));   // frees this slot in both CTAs
+                    __syncwarp();
+                    if (++stage == kStages2) {
+                        stage = 0;
+                        phase ^= 1u;
+                    }
+                }
+                if (!ok) break;
+                if (issuer) tc_commit_pair(tfull_bar);              // accumulators of both CTAs are complete
+                __syncwarp();
+                acc_phase ^= 1u;
+            }
+            if (issuer && pair_id < 160) {
+                g_gemm_cycles[pair_id][0] = clock64() - t_begin;
+                g_gemm_cycles[pair_id][1] = w_full;
+                g_gemm_cycles[pair_id][2] = w_acc;
+                g_gemm_cycles[pair_id][6] = ntile;
+            }
+        }
+    } else {
+        // ------------------------------------------------------------------ epilogue (both CTAs)
+        const int sp = warp & 3;
+        const float alpha = __ldg(p.alpha);
+        uint32_t acc_phase = 0;
+        bool ok = true;
+        const bool vec_ok = (p.N % 8) == 0;
+        const uint32_t lead_tempty = map_to_cta(tempty_bar, 0);
+        for (int tile = pair_id; ok && tile < total_tiles; tile += num_pairs) {
+            const int mt = tile % m_tiles, nt = tile / m_tiles;
+            ok = mbar_wait(tfull_bar, acc_phase, abort_flag, (3u << 24) | (tile & 0xffff));
+            ok = __shfl_sync(0xffffffffu, ok ? 1 : 0, 0) != 0;
+            if (!ok) break;
+            tc_fence_after();
+            const int row = mt * 256 + static_cast<int>(rank) * 128 + sp * 32 + lane;
+            __nv_bfloat16* orow = p.out + static_cast<int64_t>(row) * p.N;
+#pragma unroll 1
+            for (int c = 0; c < 8; ++c) {
+                uint32_t v[32];
+                tc_ld_32x32b_x32(tmem_base + (static_cast<uint32_t>(sp * 32) << 16) + c * 32, v);
+                tc_ld_wait();
+                const int col0 = nt * 256 + c * 32;
+                if (row < p.M && col0 < p.N) {
+                    if (vec_ok && col0 + 32 <= p.N) {
+#pragma unroll
+                        for (int q = 0; q < 4; ++q) {
+                            uint32_t w[4];
+#pragma unroll
+                            for (int e = 0; e < 4; ++e) {
+                                const float lo = __fmul_rn(__uint_as_float(v[q * 8 + 2 * e]), alpha);
+                                const float hi = __fmul_rn(__uint_as_float(v[q * 8 + 2 * e + 1]), alpha);
+                                __nv_bfloat162 b2 = __floats2bfloat162_rn(lo, hi);
+                                w[e] = *reinterpret_cast<uint32_t*>(&b2);
+                            }
+                            *reinterpret_cast<uint4*>(orow + col0 + q * 8) = make_uint4(w[0], w[1], w[2], w[3]);
+                        }
+                    } else {
+                        for (int e = 0; e < 32; ++e)
+                            if (col0 + e < p.N) orow[col0 + e] = __float2bfloat16_rn(__fmul_rn(__uint_as_float(v[e]), alpha));
+                    }
+                }
+            }
+            tc_fence_before();
+            __syncwarp();
+            if (lane == 0) mbar_arrive_cluster(lead_tempty);
+            acc_phase ^= 1u;
+        }
+    }
+
+    // ---------------------------------------------------------------------- teardown
+    if (*abort_flag) {
+        const uint64_t t0 = global_timer_ns();
+        while (global_timer_ns() - t0 < 200000ull) __nanosleep(1000);
+    }
+    tc_fence_before();
+    __syncthreads();
+    cluster_sync_all();   // neither CTA leaves while its partner may still signal or read it
+    if (warp == 1) {
+        tc_fence_after();
+        asm volatile("tcgen05.dealloc.cta_group::2.sync.aligned.b32 %0, %1;" ::"r"(tmem_base), "r"(kTmemCols) : "memory");
+    }
+}
+
+// Scale buffer as a 2-D array of 8-byte words: row = 128-row group, 2048 B (one K tile) per box.
+static int make_scale_map(CUtensorMap* map, const void* ptr, int64_t groups, int64_t group_stride_bytes) {
+    EncodeTiledFn enc = encode_tiled_fn();
+    if (!enc) return NVFP4_ERR_UNSUPPORTED;
+    cuuint64_t dims[2] = {static_cast<cuuint64_t>(group_stride_bytes / 8), static_cast<cuuint64_t>(groups)};
+    cuuint64_t strides[1] = {static_cast<cuuint64_t>(group_stride_bytes)};
+    cuuint32_t box[2] = {256, 1};
+    cuuint32_t estr[2] = {1, 1};
+    CUresult r = enc(map, CU_TENSOR_MAP_DATA_TYPE_UINT64, 2, const_cast<void*>(ptr), dims, strides, box, estr,
+                     CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_NONE, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
+                     CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+    return r == CUDA_SUCCESS ? NVFP4_OK : NVFP4_ERR_UNSUPPORTED;
+}
+
+static int launch_pair(const uint8_t* a, const uint8_t* b, const GemmParams& p, cudaStream_t stream) {
+    CUtensorMap ma, mb, msa, msb;
+    int st = make_operand_map(&ma, a, p.M, p.K / 2, 128);
+    if (st == NVFP4_OK) st = make_operand_map(&mb, b, p.N, p.K / 2, 128);
+    if (st == NVFP4_OK) st = make_scale_map(&msa, p.sfa, p.sfa_groups, p.sf_group_stride);
+    if (st == NVFP4_OK) st = make_scale_map(&msb, p.sfb, p.sfb_groups, p.sf_group_stride);
+    if (st != NVFP4_OK) return st;
+    cudaError_t e = cudaFuncSetAttribute(gemm_pair_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, kSmemBytes2);
+    if (e != cudaSuccess) return static_cast<int>(e);
+    int dev = 0, sms = 148;
+    cudaGetDevice(&dev);
+    cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev);
+    const int tiles = ((p.M + 255) / 256) * ((p.N + 255) / 256);
+    const int pairs = tiles < sms / 2 ? tiles : sms / 2;
+    cudaLaunchConfig_t cfg = {};
+    cfg.gridDim = dim3(2 * pairs, 1, 1);
+    cfg.blockDim = dim3(kThreads, 1, 1);
+    cfg.dynamicSmemBytes = kSmemBytes2;
+    cfg.stream = stream;
+    cudaLaunchAttribute attr[1];
+    attr[0].id = cudaLaunchAttributeClusterDimension;
+    attr[0].val.clusterDim.x = 2;
+    attr[0].val.clusterDim.y = 1;
+    attr[0].val.clusterDim.z = 1;
+    cfg.attrs = attr;
+    cfg.numAttrs = 1;
+    e = cudaLaunchKernelEx(&cfg, gemm_pair_kernel, ma, mb, msa, msb, p);
+    return static_cast<int>(e);
+}
+
+}  // namespace pair
+
 }  // namespace gemm
 }  // namespace nvfp4
 
+static int g_gemm_force_path = 0;
+
 extern "C" size_t nvfp4_gemm_workspace_bytes(int64_t, int64_t, int64_t) { return 0; }
+
+// Testing hook: 0 = choose the kernel by shape, 1 = 128x128 tiles, 2 = 128x256 tiles, 3 = CTA-pair 256x256 tiles.
+extern "C" int nvfp4_gemm_force_path(int path) {
+    if (path < 0 || path > 3) return NVFP4_ERR_BAD_ENUM;
+    g_gemm_force_path = path;
+    return NVFP4_OK;
+}
 
 extern "C" int nvfp4_gemm_launch(const uint8_t* a, const uint8_t* b, const uint8_t* sfa, const uint8_t* sfb,
                                  const float* alpha, void* out_bf16, int64_t M, int64_t N, int64_t K, void* workspace,
@@ -451,8 +886,20 @@ extern "C" int nvfp4_gemm_launch(const uint8_t* a, const uint8_t* b, const uint8
     cudaStream_t s = static_cast<cudaStream_t>(stream);
     // Wide tiles feed the tensor pipe best; narrow ones keep more SMs busy when there are few tiles.
     const int64_t wide_tiles = ((M + 127) / 128) * ((N + 255) / 256);
-    if (N > 128 && wide_tiles >= 148) return gemm::launch<256>(a, b, p, s);
+    const int64_t pair_tiles = ((M + 255) / 256) * ((N + 255) / 256);
+    int path = g_gemm_force_path;   // 0 = choose by shape
+    if (path == 0) path = (M > 128 && N > 128 && pair_tiles >= 74) ? 3 : ((N > 128 && wide_tiles >= 148) ? 2 : 1);
+    if (path == 3) return gemm::pair::launch_pair(a, b, p, s);
+    if (path == 2) return gemm::launch<256>(a, b, p, s);
     return gemm::launch<128>(a, b, p, s);
+}
+
+// Diagnostics: copies the per-CTA cycle counters of the last 1-CTA GEMM launch (160 x 8 uint64) to the host.
+extern "C" int nvfp4_gemm_debug_cycles(unsigned long long* host_160x8) {
+    if (!host_160x8) return NVFP4_ERR_NULL_POINTER;
+    cudaError_t e = cudaDeviceSynchronize();
+    if (e != cudaSuccess) return static_cast<int>(e);
+    return static_cast<int>(cudaMemcpyFromSymbol(host_160x8, nvfp4::gemm::g_gemm_cycles, sizeof(unsigned long long) * 160 * 8));
 }
 
 extern "C" int nvfp4_gemm_last_status(void* stream, uint32_t* status_host) {
