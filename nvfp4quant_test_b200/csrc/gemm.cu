@@ -520,14 +520,24 @@ static int launch(const uint8_t* a, const uint8_t* b, const GemmParams& p, cudaS
 // =============================================================================================
 namespace pair {
 
-constexpr int kStages2 = 5;
-constexpr int kABytes2 = 128 * kBKBytes;   // this CTA's 128 rows of A
-constexpr int kBBytes2 = 128 * kBKBytes;   // this CTA's half of the 256 B rows
-constexpr int kSfaBytes2 = 2048;           // scales of this CTA's A rows
-constexpr int kSfbBytes2 = 4096;           // scales of all 256 B rows (each CTA needs all of them)
-constexpr int kStageBytes2 = kABytes2 + kBBytes2 + kSfaBytes2 + kSfbBytes2;   // 38 KiB
-constexpr int kSmemBytes2 = kStages2 * kStageBytes2 + 1024 + 256;
-constexpr int kSfaCol2 = 256, kSfbCol2 = 272, kSfSetCols2 = 48;   // two scale sets: columns 256..351
+// Tile-width dependent constants of the pair kernel.  BN = 256: one accumulator (256 columns) per CTA.
+// BN = 192: two accumulators (2 x 192 columns), so the epilogue of one tile overlaps the MMAs of the next.
+template <int BN>
+struct PairCfg {
+    static constexpr int kAcc = (BN == 192) ? 2 : 1;
+    static constexpr int kABytes = 128 * kBKBytes;          // this CTA's 128 rows of A
+    static constexpr int kBBytes = (BN / 2) * kBKBytes;     // this CTA's half of the B rows
+    static constexpr int kSfaBytes = 2048;                  // scales of this CTA's A rows
+    static constexpr int kSfbBytes = 4096;                  // two 128-row scale groups cover the B tile
+    static constexpr int kStageBytes = kABytes + kBBytes + kSfaBytes + kSfbBytes;
+    static constexpr int kStages = (BN == 192) ? 6 : 5;
+    static constexpr int kSmemBytes = kStages * kStageBytes + 1024 + 256;
+    static constexpr int kSfaCol = kAcc * BN;               // scale set 0; set 1 follows 48 columns later
+    static constexpr int kSfbCol = kSfaCol + 16;
+    static constexpr int kSfSetCols = 48;
+    static_assert(kSfaCol + 2 * kSfSetCols <= kTmemCols, "TMEM budget");
+    static_assert(kStageBytes % 1024 == 0, "stage alignment for the 128-byte swizzle");
+};
 
 __device__ __forceinline__ uint32_t cluster_ctarank() {
     uint32_t r;
@@ -572,21 +582,23 @@ __device__ __forceinline__ void tc_mma_pair(uint32_t d_tmem, uint32_t a_lo, uint
         : "memory");
 }
 
+template <int BN>
 __global__ void __launch_bounds__(kThreads, 1)
 gemm_pair_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant__ CUtensorMap tmap_b,
                  const __grid_constant__ CUtensorMap tmap_sfa, const __grid_constant__ CUtensorMap tmap_sfb,
                  const GemmParams p) {
+    using C = PairCfg<BN>;
     extern __shared__ uint8_t smem_raw[];
     const uint32_t raw_addr = smem_u32(smem_raw);
     const uint32_t base = (raw_addr + 1023u) & ~1023u;
     uint8_t* aligned = smem_raw + (base - raw_addr);
-    uint64_t* bars = reinterpret_cast<uint64_t*>(aligned + kStages2 * kStageBytes2);
+    uint64_t* bars = reinterpret_cast<uint64_t*>(aligned + C::kStages * C::kStageBytes);
     const uint32_t bar_base = smem_u32(bars);
     auto full_bar = [&](int s) { return bar_base + 8u * s; };
-    auto empty_bar = [&](int s) { return bar_base + 8u * (kStages2 + s); };
-    const uint32_t tfull_bar = bar_base + 8u * (2 * kStages2);
-    const uint32_t tempty_bar = bar_base + 8u * (2 * kStages2 + 1);
-    volatile uint32_t* tmem_slot = reinterpret_cast<volatile uint32_t*>(bars + 2 * kStages2 + 2);
+    auto empty_bar = [&](int s) { return bar_base + 8u * (C::kStages + s); };
+    auto tfull_bar = [&](int a) { return bar_base + 8u * (2 * C::kStages + a); };
+    auto tempty_bar = [&](int a) { return bar_base + 8u * (2 * C::kStages + 2 + a); };
+    volatile uint32_t* tmem_slot = reinterpret_cast<volatile uint32_t*>(bars + 2 * C::kStages + 4);
     volatile uint32_t* abort_flag = tmem_slot + 1;
 
     const int warp = __shfl_sync(0xffffffffu, threadIdx.x >> 5, 0);
@@ -596,12 +608,14 @@ gemm_pair_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_consta
     const int num_pairs = gridDim.x >> 1;
 
     if (threadIdx.x == 0) {
-        for (int s = 0; s < kStages2; ++s) {
+        for (int s = 0; s < C::kStages; ++s) {
             mbar_init(full_bar(s), 1);    // leader's producer; bytes of both CTAs' copies land here
             mbar_init(empty_bar(s), 1);   // one tcgen05.commit
         }
-        mbar_init(tfull_bar, 1);
-        mbar_init(tempty_bar, 8);         // 4 epilogue warps of each CTA
+        for (int a = 0; a < 2; ++a) {
+            mbar_init(tfull_bar(a), 1);
+            mbar_init(tempty_bar(a), 8);  // 4 epilogue warps of each CTA
+        }
         *abort_flag = 0;
         asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
         asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
@@ -620,7 +634,7 @@ gemm_pair_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_consta
     const uint32_t tmem_base = *tmem_slot;
 
     const int m_tiles = (p.M + 255) / 256;
-    const int n_tiles = (p.N + 255) / 256;
+    const int n_tiles = (p.N + BN - 1) / BN;
     const int total_tiles = m_tiles * n_tiles;
     const int k_tiles = (p.K + kBK - 1) / kBK;
 
@@ -642,18 +656,18 @@ gemm_pair_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_consta
                 for (int kt = 0; kt < k_tiles; ++kt) {
                     if (!(ok = mbar_wait_warp(empty_bar(stage), phase ^ 1u, abort_flag, (1u << 24) | kt))) break;
                     if (issuer) {
-                    if (rank == 0) mbar_expect_tx(full_bar(stage), 2u * kStageBytes2);
+                    if (rank == 0) mbar_expect_tx(full_bar(stage), 2u * C::kStageBytes);
                     const uint32_t lead_full = map_to_cta(full_bar(stage), 0);
-                    const uint32_t sbase = base + stage * kStageBytes2;
+                    const uint32_t sbase = base + stage * C::kStageBytes;
                     tma_load_2d_pair(sbase, &tmap_a, kt * kBKBytes, mt * 256 + static_cast<int>(rank) * 128, lead_full);
-                    tma_load_2d_pair(sbase + kABytes2, &tmap_b, kt * kBKBytes, nt * 256 + static_cast<int>(rank) * 128, lead_full);
+                    tma_load_2d_pair(sbase + C::kABytes, &tmap_b, kt * kBKBytes, nt * BN + static_cast<int>(rank) * (BN / 2), lead_full);
                     // scale tiles: x counts 8-byte elements (2048 B per K tile), y = 128-row group
-                    tma_load_2d_pair(sbase + kABytes2 + kBBytes2, &tmap_sfa, kt * 256, mt * 2 + static_cast<int>(rank), lead_full);
-                    tma_load_2d_pair(sbase + kABytes2 + kBBytes2 + kSfaBytes2, &tmap_sfb, kt * 256, nt * 2, lead_full);
-                    tma_load_2d_pair(sbase + kABytes2 + kBBytes2 + kSfaBytes2 + 2048, &tmap_sfb, kt * 256, nt * 2 + 1, lead_full);
+                    tma_load_2d_pair(sbase + C::kABytes + C::kBBytes, &tmap_sfa, kt * 256, mt * 2 + static_cast<int>(rank), lead_full);
+                    tma_load_2d_pair(sbase + C::kABytes + C::kBBytes + C::kSfaBytes, &tmap_sfb, kt * 256, (nt * BN) / 128, lead_full);
+                    tma_load_2d_pair(sbase + C::kABytes + C::kBBytes + C::kSfaBytes + 2048, &tmap_sfb, kt * 256, (nt * BN) / 128 + 1, lead_full);
                     }
                     __syncwarp();
-                    if (++stage == kStages2) {
+                    if (++stage == C::kStages) {
                         stage = 0;
                         phase ^= 1u;
                     }
@@ -664,33 +678,37 @@ gemm_pair_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_consta
         // ------------------------------------------------------------------ MMA issuer (leader only)
         if (rank == 0) {
             const bool issuer = elect_one();
-            constexpr uint32_t idesc = (1u << 7) | (1u << 10) | (static_cast<uint32_t>(256 >> 3) << 17) |
+            constexpr uint32_t idesc = (1u << 7) | (1u << 10) | (static_cast<uint32_t>(BN >> 3) << 17) |
                                        (static_cast<uint32_t>(256 >> 4) << 24);
             int stage = 0;
             uint32_t phase = 0, acc_phase = 0;
+            int acc = 0;
             bool ok = true;
             long long w_full = 0, w_acc = 0, ntile = 0, c0;
             const long long t_begin = clock64();
             for (int tile = pair_id; ok && tile < total_tiles; tile += num_pairs) {
                 c0 = clock64();
-                if (!(ok = mbar_wait_warp(tempty_bar, acc_phase ^ 1u, abort_flag, (2u << 24) | 0xffff))) break;
+                if (!(ok = mbar_wait_warp(tempty_bar(acc), acc_phase ^ 1u, abort_flag, (2u << 24) | 0xffff))) break;
                 w_acc += clock64() - c0;
                 ++ntile;
                 tc_fence_after();
+                const uint32_t d_tmem = tmem_base + acc * BN;
+                // a 192-wide tile starts 0 or 64 rows into its first scale group: 64 rows = 2 TMEM columns
+                const uint32_t sfb_shift = ((tile / m_tiles) * BN % 128) / 32;
                 for (int kt = 0; kt < k_tiles; ++kt) {
                     c0 = clock64();
                     if (!(ok = mbar_wait_warp(full_bar(stage), phase, abort_flag, (2u << 24) | kt))) break;
                     w_full += clock64() - c0;
                     tc_fence_after();
                     const int kb_count = min(4, (p.K - kt * kBK + 63) / 64);
-                    const uint32_t sbase = base + stage * kStageBytes2;
+                    const uint32_t sbase = base + stage * C::kStageBytes;
                     const uint32_t a_lo = ((sbase & 0x3ffffu) >> 4) | (1u << 16);
-                    const uint32_t b_lo = a_lo + (kABytes2 >> 4);
-                    const uint32_t sfa_lo = ((sbase + kABytes2 + kBBytes2) & 0x3ffffu) >> 4;
-                    const uint32_t sfb_lo = sfa_lo + (kSfaBytes2 >> 4);
-                    const uint32_t set = (kt & 1) * kSfSetCols2;
-                    const uint32_t sfa_t = tmem_base + kSfaCol2 + set;
-                    const uint32_t sfb_t = tmem_base + kSfbCol2 + set;
+                    const uint32_t b_lo = a_lo + (C::kABytes >> 4);
+                    const uint32_t sfa_lo = ((sbase + C::kABytes + C::kBBytes) & 0x3ffffu) >> 4;
+                    const uint32_t sfb_lo = sfa_lo + (C::kSfaBytes >> 4);
+                    const uint32_t set = (kt & 1) * C::kSfSetCols;
+                    const uint32_t sfa_t = tmem_base + C::kSfaCol + set;
+                    const uint32_t sfb_t = tmem_base + C::kSfbCol + set;
                     const uint32_t first = kt > 0 ? 1u : 0u;
                     if (!issuer) {
                         // nothing to issue on this lane
@@ -703,7 +721,7 @@ gemm_pair_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_consta
                         }
 #pragma unroll
                         for (int kb = 0; kb < 4; ++kb)
-                            tc_mma_pair(tmem_base, a_lo + 2 * kb, b_lo + 2 * kb, idesc, sfa_t + 4 * kb, sfb_t + 8 * kb,
+                            tc_mma_pair(d_tmem, a_lo + 2 * kb, b_lo + 2 * kb, idesc, sfa_t + 4 * kb, sfb_t + 8 * kb + sfb_shift,
                                         kb == 0 ? first : 1u);
                     } else {
                         for (int kb = 0; kb < kb_count; ++kb) {
@@ -712,20 +730,23 @@ gemm_pair_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_consta
                             tc_cp_pair(sfb_t + 8 * kb + 4, sfb_lo + 128 + 32 * kb);
                         }
                         for (int kb = 0; kb < kb_count; ++kb)
-                            tc_mma_pair(tmem_base, a_lo + 2 * kb, b_lo + 2 * kb, idesc, sfa_t + 4 * kb, sfb_t + 8 * kb,
+                            tc_mma_pair(d_tmem, a_lo + 2 * kb, b_lo + 2 * kb, idesc, sfa_t + 4 * kb, sfb_t + 8 * kb + sfb_shift,
                                         kb == 0 ? first : 1u);
                     }
                     if (issuer) tc_commit_pair(empty_bar(stage));   // frees this slot in both CTAs
                     __syncwarp();
-                    if (++stage == kStages2) {
+                    if (++stage == C::kStages) {
                         stage = 0;
                         phase ^= 1u;
                     }
                 }
                 if (!ok) break;
-                if (issuer) tc_commit_pair(tfull_bar);              // accumulators of both CTAs are complete
+                if (issuer) tc_commit_pair(tfull_bar(acc));         // accumulators of both CTAs are complete
                 __syncwarp();
-                acc_phase ^= 1u;
+                if (++acc == C::kAcc) {
+                    acc = 0;
+                    acc_phase ^= 1u;
+                }
             }
             if (issuer && pair_id < 160) {
                 g_gemm_cycles[pair_id][0] = clock64() - t_begin;
@@ -739,23 +760,23 @@ gemm_pair_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_consta
         const int sp = warp & 3;
         const float alpha = __ldg(p.alpha);
         uint32_t acc_phase = 0;
+        int acc = 0;
         bool ok = true;
         const bool vec_ok = (p.N % 8) == 0;
-        const uint32_t lead_tempty = map_to_cta(tempty_bar, 0);
         for (int tile = pair_id; ok && tile < total_tiles; tile += num_pairs) {
             const int mt = tile % m_tiles, nt = tile / m_tiles;
-            ok = mbar_wait(tfull_bar, acc_phase, abort_flag, (3u << 24) | (tile & 0xffff));
+            ok = mbar_wait(tfull_bar(acc), acc_phase, abort_flag, (3u << 24) | (tile & 0xffff));
             ok = __shfl_sync(0xffffffffu, ok ? 1 : 0, 0) != 0;
             if (!ok) break;
             tc_fence_after();
             const int row = mt * 256 + static_cast<int>(rank) * 128 + sp * 32 + lane;
             __nv_bfloat16* orow = p.out + static_cast<int64_t>(row) * p.N;
 #pragma unroll 1
-            for (int c = 0; c < 8; ++c) {
+            for (int c = 0; c < BN / 32; ++c) {
                 uint32_t v[32];
-                tc_ld_32x32b_x32(tmem_base + (static_cast<uint32_t>(sp * 32) << 16) + c * 32, v);
+                tc_ld_32x32b_x32(tmem_base + (static_cast<uint32_t>(sp * 32) << 16) + acc * BN + c * 32, v);
                 tc_ld_wait();
-                const int col0 = nt * 256 + c * 32;
+                const int col0 = nt * BN + c * 32;
                 if (row < p.M && col0 < p.N) {
                     if (vec_ok && col0 + 32 <= p.N) {
 #pragma unroll
@@ -778,8 +799,11 @@ gemm_pair_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_consta
             }
             tc_fence_before();
             __syncwarp();
-            if (lane == 0) mbar_arrive_cluster(lead_tempty);
-            acc_phase ^= 1u;
+            if (lane == 0) mbar_arrive_cluster(map_to_cta(tempty_bar(acc), 0));
+            if (++acc == C::kAcc) {
+                acc = 0;
+                acc_phase ^= 1u;
+            }
         }
     }
 
@@ -811,24 +835,26 @@ static int make_scale_map(CUtensorMap* map, const void* ptr, int64_t groups, int
     return r == CUDA_SUCCESS ? NVFP4_OK : NVFP4_ERR_UNSUPPORTED;
 }
 
+template <int BN>
 static int launch_pair(const uint8_t* a, const uint8_t* b, const GemmParams& p, cudaStream_t stream) {
+    using C = PairCfg<BN>;
     CUtensorMap ma, mb, msa, msb;
     int st = make_operand_map(&ma, a, p.M, p.K / 2, 128);
-    if (st == NVFP4_OK) st = make_operand_map(&mb, b, p.N, p.K / 2, 128);
+    if (st == NVFP4_OK) st = make_operand_map(&mb, b, p.N, p.K / 2, BN / 2);
     if (st == NVFP4_OK) st = make_scale_map(&msa, p.sfa, p.sfa_groups, p.sf_group_stride);
     if (st == NVFP4_OK) st = make_scale_map(&msb, p.sfb, p.sfb_groups, p.sf_group_stride);
     if (st != NVFP4_OK) return st;
-    cudaError_t e = cudaFuncSetAttribute(gemm_pair_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, kSmemBytes2);
+    cudaError_t e = cudaFuncSetAttribute(gemm_pair_kernel<BN>, cudaFuncAttributeMaxDynamicSharedMemorySize, C::kSmemBytes);
     if (e != cudaSuccess) return static_cast<int>(e);
     int dev = 0, sms = 148;
     cudaGetDevice(&dev);
     cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev);
-    const int tiles = ((p.M + 255) / 256) * ((p.N + 255) / 256);
+    const int tiles = ((p.M + 255) / 256) * ((p.N + BN - 1) / BN);
     const int pairs = tiles < sms / 2 ? tiles : sms / 2;
     cudaLaunchConfig_t cfg = {};
     cfg.gridDim = dim3(2 * pairs, 1, 1);
     cfg.blockDim = dim3(kThreads, 1, 1);
-    cfg.dynamicSmemBytes = kSmemBytes2;
+    cfg.dynamicSmemBytes = C::kSmemBytes;
     cfg.stream = stream;
     cudaLaunchAttribute attr[1];
     attr[0].id = cudaLaunchAttributeClusterDimension;
@@ -837,7 +863,7 @@ static int launch_pair(const uint8_t* a, const uint8_t* b, const GemmParams& p, 
     attr[0].val.clusterDim.z = 1;
     cfg.attrs = attr;
     cfg.numAttrs = 1;
-    e = cudaLaunchKernelEx(&cfg, gemm_pair_kernel, ma, mb, msa, msb, p);
+    e = cudaLaunchKernelEx(&cfg, gemm_pair_kernel<BN>, ma, mb, msa, msb, p);
     return static_cast<int>(e);
 }
 
@@ -850,9 +876,10 @@ static int g_gemm_force_path = 0;
 
 extern "C" size_t nvfp4_gemm_workspace_bytes(int64_t, int64_t, int64_t) { return 0; }
 
-// Testing hook: 0 = choose the kernel by shape, 1 = 128x128 tiles, 2 = 128x256 tiles, 3 = CTA-pair 256x256 tiles.
+// Testing hook: 0 = choose the kernel by shape, 1 = 128x128 tiles, 2 = 128x256 tiles, 3 = CTA-pair 256x256 tiles,
+// 4 = CTA-pair 256x192 tiles with two accumulators.
 extern "C" int nvfp4_gemm_force_path(int path) {
-    if (path < 0 || path > 3) return NVFP4_ERR_BAD_ENUM;
+    if (path < 0 || path > 4) return NVFP4_ERR_BAD_ENUM;
     g_gemm_force_path = path;
     return NVFP4_OK;
 }
@@ -886,10 +913,17 @@ extern "C" int nvfp4_gemm_launch(const uint8_t* a, const uint8_t* b, const uint8
     cudaStream_t s = static_cast<cudaStream_t>(stream);
     // Wide tiles feed the tensor pipe best; narrow ones keep more SMs busy when there are few tiles.
     const int64_t wide_tiles = ((M + 127) / 128) * ((N + 255) / 256);
-    const int64_t pair_tiles = ((M + 255) / 256) * ((N + 255) / 256);
     int path = g_gemm_force_path;   // 0 = choose by shape
-    if (path == 0) path = (M > 128 && N > 128 && pair_tiles >= 74) ? 3 : ((N > 128 && wide_tiles >= 148) ? 2 : 1);
-    if (path == 3) return gemm::pair::launch_pair(a, b, p, s);
+    if (path == 0) {
+        // CTA pairs with 256x192 tiles and two accumulators are fastest whenever there is enough work to
+        // fill the 74 pairs; small problems use single-CTA tiles so that more SMs get a tile.
+        const int64_t pair192_tiles = ((M + 255) / 256) * ((N + 191) / 192);
+        if (M > 128 && N > 128 && pair192_tiles >= 74) path = 4;
+        else if (N > 128 && wide_tiles >= 148) path = 2;
+        else path = 1;
+    }
+    if (path == 3) return gemm::pair::launch_pair<256>(a, b, p, s);
+    if (path == 4) return gemm::pair::launch_pair<192>(a, b, p, s);
     if (path == 2) return gemm::launch<256>(a, b, p, s);
     return gemm::launch<128>(a, b, p, s);
 }

@@ -68,7 +68,7 @@ def test_gemm_kernel_paths_agree(cuda_lib, oracle, M, N, K_):
     alpha = (gsa * gsb).reshape(1).float()
     outs = []
     try:
-        for path in (1, 2, 3):
+        for path in (1, 2, 3, 4):
             assert cuda_lib.nvfp4_gemm_force_path(path) == 0
             out = torch.full((M, N), float("nan"), dtype=torch.bfloat16, device="cuda")
             K.nvfp4_scaled_mm(qa, qb, sa, sb, alpha, torch.bfloat16, out=out)
@@ -78,9 +78,9 @@ def test_gemm_kernel_paths_agree(cuda_lib, oracle, M, N, K_):
         cuda_lib.nvfp4_gemm_force_path(0)
     ref = oracle.gemm(qa.cpu().numpy(), qb.cpu().numpy(), sa.view(torch.uint8).cpu().numpy().reshape(-1),
                       sb.view(torch.uint8).cpu().numpy().reshape(-1), float(alpha))
-    for path, out in zip((1, 2, 3), outs):
+    for path, out in zip((1, 2, 3, 4), outs):
         _check(out, ref)
-    assert torch.equal(outs[0], outs[1]) and torch.equal(outs[0], outs[2])
+    assert all(torch.equal(outs[0], o) for o in outs[1:])
 
 
 def test_gemm_matches_cutlass_fixture(cuda_lib, golden):
