@@ -9,8 +9,8 @@ plus the NVFP4 GEMM that consumes such operands.
 One JSON line is printed by rank 0.  A step = one quantization of this rank's [8192, 8192] shard
 (rows are independent, so ranks share nothing: weak scaling, no collective on the data path).
 `value` = algorithmic bytes moved per second over all ranks, inputs resident in HBM, timed with CUDA
-events (max over ranks).  `e2e` = the same metric through the public `_impl` entry point with the
-input in pinned host memory and codes + scales copied back, every step.
+events (max over ranks).  `e2e` = the same metric through the public host-buffer entry point
+(host_pipeline.HostQuantizer: pinned host input, codes + scales copied back to pinned host memory, every step).
 Algorithmic bytes per row of 8192 elements: 16384 read + 4096 codes + 512 scales = 20992.
 `--impl reference` times the CPU restatement of the reference's algorithm (oracle/) on all host
 threads; the reference itself is GPU-only Triton code and has no CPU implementation.
@@ -227,19 +227,19 @@ def main():
     value = world * ALGO_BYTES / (ms_step * 1e-3) / 1e9
     kernel_gbs = ALGO_BYTES / (ms_step * 1e-3) / 1e9     # one kernel per step: its average duration is the step
 
-    # ---- end to end through the public entry point: pinned host input -> device -> quantize -> host
+    # ---- end to end through the public host-buffer entry point: pinned host input -> device -> quantize
+    #      -> pinned host codes + scales, every step (row chunks pipelined over three streams)
+    from nvfp4quant_test_b200.host_pipeline import HostQuantizer
+
     host_in = torch.empty((ROWS, DIM), dtype=torch.bfloat16, pin_memory=True)
     host_in.copy_(xs[0])
     host_codes = torch.empty((ROWS, DIM // 2), dtype=torch.uint8, pin_memory=True)
     host_scales = torch.empty((ROWS * DIM // 16,), dtype=torch.uint8, pin_memory=True)
-    dev_in = torch.empty_like(xs[0])
+    hq = HostQuantizer(ROWS, DIM, torch.bfloat16, dev, chunk_rows=1024)
     e2e_steps = max(3, min(args.steps, 20))
 
     def e2e_step():
-        dev_in.copy_(host_in, non_blocking=True)
-        c, s = K.scalesweep_mse_nvfp4_quant_impl(dev_in, gs_inv[0], True)
-        host_codes.copy_(c, non_blocking=True)
-        host_scales.copy_(s.view(torch.uint8).reshape(-1), non_blocking=True)
+        hq(host_in, gs_inv[0], host_codes, host_scales)
 
     for _ in range(3):
         e2e_step()

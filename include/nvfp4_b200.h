@@ -116,8 +116,9 @@ int64_t nvfp4_global_scale_static_max_bytes(void);
  * fp32 accumulation on tcgen05 (kind::mxf4nvf4.block_scale) with TMEM accumulators.
  * replaces vllm `_C::cutlass_scaled_fp4_mm` (vllm/_custom_ops.py:741-752;
  * named at README.md:68).
- * workspace: nvfp4_gemm_workspace_bytes(M, N, K) bytes, 256-byte aligned (may be
- * NULL when that is 0).
+ * workspace: nvfp4_gemm_workspace_bytes(M, N, K) bytes, 16-byte aligned (may be NULL when that is 0).
+ * It is non-zero only for small M, where K is cut into ranges whose fp32 partial tiles are summed by a
+ * second kernel; contents need no initialisation.
  */
 int nvfp4_gemm_launch(const uint8_t* a, const uint8_t* b, const uint8_t* sfa, const uint8_t* sfb,
                       const float* alpha, void* out_bf16, int64_t M, int64_t N, int64_t K,
@@ -126,6 +127,9 @@ size_t nvfp4_gemm_workspace_bytes(int64_t M, int64_t N, int64_t K);
 /* Testing hook (process-wide): 0 = pick the GEMM kernel by shape (default), 1 = 128x128 tiles,
  * 2 = 128x256 tiles, 3 = CTA-pair 256x256 tiles.  All paths give identical results. */
 int nvfp4_gemm_force_path(int path);
+/* Testing hook (process-wide) for the single-CTA kernel: number of K ranges (0 = by shape) and K-loop
+ * rotation (-1 = by shape, 0 = off, 1 = on).  nvfp4_gemm_workspace_bytes reflects the current setting. */
+int nvfp4_gemm_tune(int k_splits, int k_rotate);
 
 /* Device status word of the last GEMM on this device: 0 = ok, else a bounded
  * wait inside the kernel gave up (the kernel returned without hanging).

@@ -197,6 +197,11 @@ struct GemmParams {
     int M, N, K;
     int64_t sf_group_stride;  // bytes between consecutive 128-row scale groups = round_up(K/16, 4) * 128
     int sfa_groups, sfb_groups;  // 128-row groups present in each scale buffer
+    // single-CTA kernel only: K is cut into k_splits ranges of k_tiles_per_split stages; with more than one range
+    // each work item writes an fp32 partial tile to `partial` ([k_splits, M, N]) and a second kernel sums them.
+    int k_splits, k_tiles_per_split;
+    int k_rotate;             // != 0: each tile starts its K loop at a different stage (spreads requests for shared A rows)
+    float* partial;
 };
 
 template <int BN>
@@ -247,7 +252,8 @@ gemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant__ 
 
     const int m_tiles = (p.M + kBM - 1) / kBM;
     const int n_tiles = (p.N + BN - 1) / BN;
-    const int total_tiles = m_tiles * n_tiles;
+    const int mn_tiles = m_tiles * n_tiles;
+    const int total_tiles = mn_tiles * p.k_splits;   // work items: (K range, n tile, m tile)
     const int k_tiles = (p.K + kBK - 1) / kBK;
 
     if (warp == 0) {
@@ -263,8 +269,13 @@ gemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant__ 
             bool ok = true;
             long long w_empty = 0;
             for (int tile = blockIdx.x; ok && tile < total_tiles; tile += gridDim.x) {
-                const int mt = tile % m_tiles, nt = tile / m_tiles;
-                for (int kt = 0; kt < k_tiles; ++kt) {
+                const int ks = tile / mn_tiles, t2 = tile - ks * mn_tiles;
+                const int mt = t2 % m_tiles, nt = t2 / m_tiles;
+                const int kt_begin = ks * p.k_tiles_per_split;
+                const int kcount = min(k_tiles, kt_begin + p.k_tiles_per_split) - kt_begin;
+                const int rot = p.k_rotate ? (t2 * 5) % kcount : 0;
+                for (int i = 0; i < kcount; ++i) {
+                    const int kt = kt_begin + (i + rot) % kcount;
                     const long long c0 = clock64();
                     if (!(ok = mbar_wait_warp(empty_bar(stage), phase ^ 1u, abort_flag, (1u << 24) | kt))) break;
                     w_empty += clock64() - c0;
@@ -318,7 +329,12 @@ gemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant__ 
                 ++ntile;
                 tc_fence_after();
                 const uint32_t d_tmem = tmem_base + acc * BN;
-                for (int kt = 0; kt < k_tiles; ++kt) {
+                const int ks = tile / mn_tiles, t2 = tile - ks * mn_tiles;
+                const int kt_begin = ks * p.k_tiles_per_split;
+                const int kcount = min(k_tiles, kt_begin + p.k_tiles_per_split) - kt_begin;
+                const int rot = p.k_rotate ? (t2 * 5) % kcount : 0;
+                for (int i = 0; i < kcount; ++i) {
+                    const int kt = kt_begin + (i + rot) % kcount;
                     c0 = clock64();
                     if (!(ok = mbar_wait_warp(full_bar(stage), phase, abort_flag, (2u << 24) | kt))) break;
                     w_full += clock64() - c0;
@@ -329,10 +345,10 @@ gemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant__ 
                     const uint32_t b_lo = a_lo + (C::kABytes >> 4);
                     const uint32_t sfa_lo = ((sbase + C::kABytes + C::kBBytes) & 0x3ffffu) >> 4;
                     const uint32_t sfb_lo = sfa_lo + (C::kSfaBytes >> 4);
-                    const uint32_t set = (kt & 1) * C::kSfSetCols;
+                    const uint32_t set = (i & 1) * C::kSfSetCols;
                     const uint32_t sfa_t = tmem_base + C::kSfaCol + set;
                     const uint32_t sfb_t = tmem_base + C::kSfbCol + set;
-                    const uint32_t first = kt > 0 ? 1u : 0u;
+                    const uint32_t first = i > 0 ? 1u : 0u;
                     if (!issuer) {
                         // nothing to issue on this lane
                     } else if (kb_count == 4) {
@@ -389,7 +405,8 @@ gemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant__ 
         const bool vec_ok = (p.N % 8) == 0;
         long long w_tfull = 0, t_drain = 0;
         for (int tile = blockIdx.x; ok && tile < total_tiles; tile += gridDim.x) {
-            const int mt = tile % m_tiles, nt = tile / m_tiles;
+            const int ks = tile / mn_tiles, t2 = tile - ks * mn_tiles;
+            const int mt = t2 % m_tiles, nt = t2 / m_tiles;
             const long long c0 = clock64();
             ok = mbar_wait(tfull_bar(acc), acc_phase, abort_flag, (3u << 24) | (tile & 0xffff));
             ok = __shfl_sync(0xffffffffu, ok ? 1 : 0, 0) != 0;
@@ -405,7 +422,20 @@ gemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant__ 
                 tc_ld_32x32b_x32(tmem_base + (static_cast<uint32_t>(sp * 32) << 16) + acc * BN + c * 32, v);
                 tc_ld_wait();
                 const int col0 = nt * BN + c * 32;
-                if (row < p.M && col0 < p.N) {
+                if (p.k_splits > 1) {
+                    // fp32 partial of this K range; alpha and the bf16 rounding happen in the reduction kernel
+                    if (row < p.M && col0 < p.N) {
+                        float* prow = p.partial + (static_cast<int64_t>(ks) * p.M + row) * p.N + col0;
+                        if ((p.N % 4) == 0 && col0 + 32 <= p.N) {
+#pragma unroll
+                            for (int q = 0; q < 8; ++q)
+                                *reinterpret_cast<uint4*>(prow + 4 * q) = make_uint4(v[4 * q], v[4 * q + 1], v[4 * q + 2], v[4 * q + 3]);
+                        } else {
+                            for (int e = 0; e < 32; ++e)
+                                if (col0 + e < p.N) prow[e] = __uint_as_float(v[e]);
+                        }
+                    }
+                } else if (row < p.M && col0 < p.N) {
                     if (vec_ok && col0 + 32 <= p.N) {
 #pragma unroll
                         for (int q = 0; q < 4; ++q) {
@@ -451,6 +481,17 @@ gemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant__ 
     if (warp == 1) {
         tc_fence_after();
         asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(tmem_base), "r"(kTmemCols) : "memory");
+    }
+}
+
+// out[m, n] = bf16(alpha * sum over K ranges of partial[s][m][n]); ranges are added in ascending order.
+__global__ void __launch_bounds__(256) splitk_reduce_kernel(const float* __restrict__ partial, const float* alpha_ptr,
+                                                            __nv_bfloat16* __restrict__ out, int64_t mn, int splits) {
+    const float alpha = __ldg(alpha_ptr);
+    for (int64_t i = static_cast<int64_t>(blockIdx.x) * 256 + threadIdx.x; i < mn; i += static_cast<int64_t>(gridDim.x) * 256) {
+        float acc = partial[i];
+        for (int s = 1; s < splits; ++s) acc = __fadd_rn(acc, partial[static_cast<int64_t>(s) * mn + i]);
+        out[i] = __float2bfloat16_rn(__fmul_rn(acc, alpha));
     }
 }
 
@@ -502,9 +543,15 @@ static int launch(const uint8_t* a, const uint8_t* b, const GemmParams& p, cudaS
     int dev = 0, sms = 148;
     cudaGetDevice(&dev);
     cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev);
-    const int tiles = ((p.M + kBM - 1) / kBM) * ((p.N + BN - 1) / BN);
+    const int tiles = ((p.M + kBM - 1) / kBM) * ((p.N + BN - 1) / BN) * p.k_splits;
     const int grid = tiles < sms ? tiles : sms;
     gemm_kernel<BN><<<grid, kThreads, C::kSmemBytes, stream>>>(ma, mb, p);
+    e = cudaGetLastError();
+    if (e != cudaSuccess || p.k_splits == 1) return static_cast<int>(e);
+    const int64_t mn = static_cast<int64_t>(p.M) * p.N;
+    int64_t rblocks = (mn + 255) / 256;
+    if (rblocks > 148 * 8) rblocks = 148 * 8;
+    splitk_reduce_kernel<<<static_cast<unsigned>(rblocks), 256, 0, stream>>>(p.partial, p.alpha, p.out, mn, p.k_splits);
     return static_cast<int>(cudaGetLastError());
 }
 
@@ -873,8 +920,31 @@ static int launch_pair(const uint8_t* a, const uint8_t* b, const GemmParams& p, 
 }  // namespace nvfp4
 
 static int g_gemm_force_path = 0;
+static int g_gemm_force_splits = 0;    // 0 = by shape
+static int g_gemm_force_rotate = -1;   // -1 = by shape
 
-extern "C" size_t nvfp4_gemm_workspace_bytes(int64_t, int64_t, int64_t) { return 0; }
+// K ranges for the single-CTA kernel.  Measured on B200 (M <= 128, K = 8192): cutting K never paid, the fixed
+// cost of a second kernel and of the partial tiles outweighs the extra SMs, so the default is one range and the
+// feature stays available through nvfp4_gemm_tune for shapes with very few tiles and very long K.
+static int choose_k_splits(int64_t, int64_t, int64_t K) {
+    if (g_gemm_force_splits <= 0) return 1;
+    const int64_t k_tiles = (K + 255) / 256;
+    return static_cast<int>(g_gemm_force_splits < k_tiles ? g_gemm_force_splits : k_tiles);
+}
+
+extern "C" size_t nvfp4_gemm_workspace_bytes(int64_t M, int64_t N, int64_t K) {
+    if (M <= 0 || N <= 0 || K <= 0) return 0;
+    const int splits = choose_k_splits(M, N, K);
+    return splits > 1 ? static_cast<size_t>(splits) * static_cast<size_t>(M) * static_cast<size_t>(N) * sizeof(float) : 0;
+}
+
+// Testing hook: K ranges (0 = by shape) and K-loop rotation (-1 = by shape, 0 = off, 1 = on) of the single-CTA kernel.
+extern "C" int nvfp4_gemm_tune(int k_splits, int k_rotate) {
+    if (k_splits < 0 || k_splits > 16 || k_rotate < -1 || k_rotate > 1) return NVFP4_ERR_BAD_ENUM;
+    g_gemm_force_splits = k_splits;
+    g_gemm_force_rotate = k_rotate;
+    return NVFP4_OK;
+}
 
 // Testing hook: 0 = choose the kernel by shape, 1 = 128x128 tiles, 2 = 128x256 tiles, 3 = CTA-pair 256x256 tiles,
 // 4 = CTA-pair 256x192 tiles with two accumulators.
@@ -888,8 +958,6 @@ extern "C" int nvfp4_gemm_launch(const uint8_t* a, const uint8_t* b, const uint8
                                  const float* alpha, void* out_bf16, int64_t M, int64_t N, int64_t K, void* workspace,
                                  size_t workspace_bytes, void* stream) {
     using namespace nvfp4;
-    (void)workspace;
-    (void)workspace_bytes;
     if (M < 0 || N < 0 || K < 0 || (K % 64) != 0) return NVFP4_ERR_BAD_SHAPE;
     if (M == 0 || N == 0) return NVFP4_OK;
     if (M > 0x7fffff00LL || N > 0x7fffff00LL || K > 0x7fffff00LL) return NVFP4_ERR_TOO_LARGE;
@@ -910,18 +978,32 @@ extern "C" int nvfp4_gemm_launch(const uint8_t* a, const uint8_t* b, const uint8
     p.sf_group_stride = round_up_i64(K / 16, 4) * 128;
     p.sfa_groups = static_cast<int>((M + 127) / 128);
     p.sfb_groups = static_cast<int>((N + 127) / 128);
+    p.k_splits = choose_k_splits(M, N, K);
+    const int k_tiles_total = static_cast<int>((K + 255) / 256);
+    p.k_tiles_per_split = (k_tiles_total + p.k_splits - 1) / p.k_splits;
+    p.k_splits = (k_tiles_total + p.k_tiles_per_split - 1) / p.k_tiles_per_split;   // no empty range
+    p.k_rotate = g_gemm_force_rotate > 0 ? 1 : 0;
+    p.partial = static_cast<float*>(workspace);
+    if (p.k_splits > 1) {
+        const size_t need = static_cast<size_t>(p.k_splits) * static_cast<size_t>(M) * static_cast<size_t>(N) * sizeof(float);
+        if (!workspace || workspace_bytes < need) return NVFP4_ERR_WORKSPACE;
+        if (reinterpret_cast<uintptr_t>(workspace) & 15) return NVFP4_ERR_MISALIGNED;
+    }
     cudaStream_t s = static_cast<cudaStream_t>(stream);
-    // Wide tiles feed the tensor pipe best; narrow ones keep more SMs busy when there are few tiles.
-    const int64_t wide_tiles = ((M + 127) / 128) * ((N + 255) / 256);
+    // Kernel choice by a small cost model fitted to measurements on B200: time ~ waves x cost of one tile, where a
+    // wave is 148 single-CTA tiles or 74 CTA-pair tiles.  Relative tile costs: 128x128 -> 0.55, 128x256 -> 1.0,
+    // pair 256x192 -> 0.68 (0.75 of the MMA work per SM, and its epilogue overlaps the next tile).
     int path = g_gemm_force_path;   // 0 = choose by shape
     if (path == 0) {
-        // CTA pairs with 256x192 tiles and two accumulators are fastest whenever there is enough work to
-        // fill the 74 pairs; small problems use single-CTA tiles so that more SMs get a tile.
-        const int64_t pair192_tiles = ((M + 255) / 256) * ((N + 191) / 192);
-        if (M > 128 && N > 128 && pair192_tiles >= 74) path = 4;
-        else if (N > 128 && wide_tiles >= 148) path = 2;
-        else path = 1;
+        const int64_t mt = (M + 127) / 128;
+        const double c1 = static_cast<double>((mt * ((N + 127) / 128) + 147) / 148) * 0.55;
+        const double c2 = static_cast<double>((mt * ((N + 255) / 256) + 147) / 148) * 1.0;
+        const double c4 = static_cast<double>((((M + 255) / 256) * ((N + 191) / 192) + 73) / 74) * 0.68;
+        path = (c1 <= c2) ? 1 : 2;
+        const double best = c1 <= c2 ? c1 : c2;
+        if (M > 128 && N > 128 && p.k_splits == 1 && c4 <= best) path = 4;
     }
+    if (p.k_splits > 1 && path != 1 && path != 2) path = 1;
     if (path == 3) return gemm::pair::launch_pair<256>(a, b, p, s);
     if (path == 4) return gemm::pair::launch_pair<192>(a, b, p, s);
     if (path == 2) return gemm::launch<256>(a, b, p, s);

@@ -48,10 +48,14 @@ def nvfp4_scaled_mm(a: torch.Tensor, b: torch.Tensor, block_scale_a: torch.Tenso
         raise ValueError("out must be a contiguous bfloat16 [M, N] tensor")
     if m == 0 or n == 0:
         return out
+    L = _lib.lib()
+    ws_bytes = L.nvfp4_gemm_workspace_bytes(m, n, k)
+    ws = torch.empty(ws_bytes, dtype=torch.uint8, device=a.device) if ws_bytes else None   # caching allocator
     with torch.cuda.device(a.device):
-        st = _lib.lib().nvfp4_gemm_launch(a.data_ptr(), b.data_ptr(), sfa.data_ptr(), sfb.data_ptr(),
-                                          alpha.data_ptr(), out.data_ptr(), m, n, k, None, 0,
-                                          _lib.current_stream_ptr(a.device))
+        st = L.nvfp4_gemm_launch(a.data_ptr(), b.data_ptr(), sfa.data_ptr(), sfb.data_ptr(),
+                                 alpha.data_ptr(), out.data_ptr(), m, n, k,
+                                 ws.data_ptr() if ws is not None else None, ws_bytes,
+                                 _lib.current_stream_ptr(a.device))
     _lib.check(st, "nvfp4_gemm_launch")
     return out
 

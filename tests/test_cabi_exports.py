@@ -71,7 +71,17 @@ def test_gemm_launch_rejects_bad_arguments_before_launching(L):
     assert g(None, P, P, P, P, P, 128, 128, 64, None, 0, None) == -1
     assert g(P + 4, P, P, P, P, P, 128, 128, 64, None, 0, None) == -4
     assert g(P, P, P, P, P, P, 0, 128, 64, None, 0, None) == 0       # empty output
-    assert L.nvfp4_gemm_workspace_bytes(8192, 8192, 8192) >= 0
+    assert L.nvfp4_gemm_workspace_bytes(8192, 8192, 8192) == 0
+    assert L.nvfp4_gemm_workspace_bytes(16, 8192, 8192) == 0
+    try:                                                          # K ranges need fp32 partial tiles
+        assert L.nvfp4_gemm_tune(4, 0) == 0
+        need = L.nvfp4_gemm_workspace_bytes(16, 8192, 8192)
+        assert need == 4 * 16 * 8192 * 4
+        assert g(P, P, P, P, P, P, 16, 8192, 8192, None, 0, None) == -6      # workspace missing
+        assert g(P, P, P, P, P, P, 16, 8192, 8192, P, need - 1, None) == -6  # workspace too small
+    finally:
+        L.nvfp4_gemm_tune(0, -1)
+    assert L.nvfp4_gemm_tune(99, 0) == -3
 
 
 def test_global_scale_rejects_bad_arguments(L):

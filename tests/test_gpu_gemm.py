@@ -83,6 +83,31 @@ def test_gemm_kernel_paths_agree(cuda_lib, oracle, M, N, K_):
     assert all(torch.equal(outs[0], o) for o in outs[1:])
 
 
+@pytest.mark.parametrize("M,N,K_,splits,rotate", [(1, 512, 2048, 2, 1), (16, 8192, 8192, 4, 1), (128, 1024, 4096, 2, 0),
+                                                  (130, 264, 2304, 2, 0), (130, 264, 2304, 3, 1), (64, 520, 8192, 4, 1),
+                                                  (300, 520, 1280, 5, 0)])
+def test_gemm_k_ranges_and_rotation(cuda_lib, oracle, M, N, K_, splits, rotate):
+    """Optional K ranges (fp32 partial tiles summed by a second kernel) and K-loop rotation of the single-CTA
+    kernel, switched on through the tuning hook.  Same tolerance as every other path (the summation order differs, nothing else)."""
+    import nvfp4quant_test_b200.kernels as K
+    from nvfp4quant_test_b200.kernels.kernel_gemm import gemm_last_status
+
+    a, b = C.gemm_operands(M, N, K_, 70 + M)
+    qa, sa, gsa = _quantize(a.cuda())
+    qb, sb, gsb = _quantize(b.cuda())
+    alpha = (gsa * gsb).reshape(1).float()
+    try:
+        assert cuda_lib.nvfp4_gemm_tune(splits, rotate) == 0
+        assert cuda_lib.nvfp4_gemm_workspace_bytes(M, N, K_) >= 2 * M * N * 4
+        out = K.nvfp4_scaled_mm(qa, qb, sa, sb, alpha, torch.bfloat16)
+        assert gemm_last_status() == 0
+    finally:
+        cuda_lib.nvfp4_gemm_tune(0, -1)
+    ref = oracle.gemm(qa.cpu().numpy(), qb.cpu().numpy(), sa.view(torch.uint8).cpu().numpy().reshape(-1),
+                      sb.view(torch.uint8).cpu().numpy().reshape(-1), float(alpha))
+    _check(out, ref)
+
+
 def test_gemm_matches_cutlass_fixture(cuda_lib, golden):
     """Same quantized operands as the fixture -> compare with what cutlass_scaled_fp4_mm returned on a B200."""
     import nvfp4quant_test_b200.kernels as K

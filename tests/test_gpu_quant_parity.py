@@ -224,3 +224,26 @@ def test_div_full_table_matches_oracle(cuda_lib, oracle):
     bits = t.cpu().numpy().view(np.uint32)
     for raw in range(1, 127):
         assert int(bits[raw]) == oracle.lib().nvfp4_oracle_div_full_bits(raw), raw
+
+
+@pytest.mark.parametrize("rows,dim,chunk", [(1000, 512, 256), (4096, 2048, 1024), (130, 64, 128)])
+def test_host_pipeline_equals_single_launch(cuda_lib, rows, dim, chunk):
+    """Pinned-host in / pinned-host out with chunked, stream-overlapped copies == one launch on the whole tensor."""
+    import nvfp4quant_test_b200.kernels as K
+    from nvfp4quant_test_b200 import helper as H
+    from nvfp4quant_test_b200.host_pipeline import HostQuantizer
+
+    x_host = C._gauss((rows, dim), 300 + rows).pin_memory()
+    x = x_host.cuda()
+    gs, gs_inv = H.get_nvfp4_global_scale(x, 256.0)
+    want_codes, want_scales = K.scalesweep_mse_nvfp4_quant_impl(x, gs_inv)
+    codes_host = torch.zeros((rows, dim // 2), dtype=torch.uint8).pin_memory()
+    scales_host = torch.zeros(want_scales.numel(), dtype=torch.uint8).pin_memory()
+    hq = HostQuantizer(rows, dim, torch.bfloat16, "cuda", chunk_rows=chunk)
+    for _ in range(2):      # second call reuses the staging buffers
+        codes_host.zero_()
+        scales_host.zero_()
+        hq(x_host, gs_inv.reshape(1), codes_host, scales_host)
+        torch.cuda.synchronize()
+        assert torch.equal(codes_host, want_codes.cpu())
+        assert torch.equal(scales_host, want_scales.view(torch.uint8).reshape(-1).cpu())

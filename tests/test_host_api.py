@@ -92,3 +92,14 @@ def test_product_package_never_imports_the_oracle():
         assert "oracle" not in text.replace("the CPU oracle", ""), f"{f} mentions the oracle"
     for f in pkg.rglob("*.cu*"):
         assert "nvfp4_oracle" not in f.read_text()
+
+
+def test_host_pipeline_chunk_plan():
+    from nvfp4quant_test_b200.host_pipeline import chunk_plan
+
+    assert chunk_plan(8192, 1024) == [(i * 1024, (i + 1) * 1024) for i in range(8)]
+    assert chunk_plan(300, 128) == [(0, 128), (128, 256), (256, 300)]
+    assert chunk_plan(1, 1024) == [(0, 1)]
+    for bad in (0, 100, 129):
+        with pytest.raises(ValueError):
+            chunk_plan(1024, bad)
