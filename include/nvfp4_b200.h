@@ -89,6 +89,13 @@ int nvfp4_global_scale_launch(const void* x, int x_dtype, int64_t numel, float f
                               uint32_t* scratch, void* stream);
 
 /*
+ * out[j] = sum_i x[i, j]^2 in fp32 for x[m, n] (n % 4 == 0, x 16-byte aligned): the per-input-channel squared
+ * norm the reference uses as importance for the operand it multiplies with (README.md:11; the reference's
+ * driver computes it with torch, no dedicated kernel).  Fixed summation order: reproducible run to run.
+ */
+int nvfp4_channel_sqnorm_launch(const void* x, int x_dtype, int64_t m, int64_t n, float* out, void* stream);
+
+/*
  * The same result as nvfp4_global_scale_launch for callers that cannot allocate device memory
  * (this entry point has no counterpart in the reference).  Typical callers: a plugin that only
  * receives raw device pointers from a runtime which owns all allocations, a serving process whose

@@ -15,7 +15,7 @@ CSRC = PKG / "csrc"
 INCLUDE = PKG.parent / "include"
 LIB = PKG / "libnvfp4_b200.so"
 
-SOURCES = ["quant.cu", "global_scale.cu", "global_scale_static.cu", "gemm.cu", "probe.cu"]
+SOURCES = ["quant.cu", "global_scale.cu", "global_scale_static.cu", "importance.cu", "gemm.cu", "probe.cu"]
 NVCC_FLAGS = [
     "-gencode", "arch=compute_100a,code=sm_100a", "-lineinfo", "-O3", "-std=c++17",
     "-fmad=false",  # every fused multiply-add in the kernels is written explicitly

@@ -1,0 +1,83 @@
+// Per-input-channel squared L2 norm of an activation batch: out[j] = sum_i x[i, j]^2 (fp32).
+//
+// This is the importance vector the reference feeds to the weighted quantizer ("the importance scores for
+// weight tensors are based on the activation input-channel square norm, and vice versa", README.md:11 of
+// efsotr/nvfp4quant_test; its driver script is not published, torch's `(x.float() ** 2).sum(0)` is the
+// obvious spelling).  One pass over x; the summation order is fixed (rows strided by 8 per thread, then a
+// fixed tree over the 8 row groups), so the result is reproducible run to run.
+#include <cuda_bf16.h>
+#include <cuda_fp16.h>
+
+#include "common.cuh"
+
+namespace nvfp4 {
+namespace {
+
+constexpr int kSqThreads = 256;   // 8 row groups x 32 lanes
+constexpr int kSqCols = 128;      // columns per CTA: 4 per lane
+
+template <int DT>
+__device__ __forceinline__ void load4(const void* x, int64_t elem, float v[4]) {
+    if (DT == NVFP4_DT_F32) {
+        const float4 f = __ldg(reinterpret_cast<const float4*>(static_cast<const float*>(x) + elem));
+        v[0] = f.x; v[1] = f.y; v[2] = f.z; v[3] = f.w;
+    } else {
+        const uint2 u = __ldg(reinterpret_cast<const uint2*>(static_cast<const uint16_t*>(x) + elem));
+        if (DT == NVFP4_DT_BF16) {
+            v[0] = __uint_as_float(u.x << 16); v[1] = __uint_as_float(u.x & 0xffff0000u);
+            v[2] = __uint_as_float(u.y << 16); v[3] = __uint_as_float(u.y & 0xffff0000u);
+        } else {
+            const float2 a = __half22float2(*reinterpret_cast<const __half2*>(&u.x));
+            const float2 b = __half22float2(*reinterpret_cast<const __half2*>(&u.y));
+            v[0] = a.x; v[1] = a.y; v[2] = b.x; v[3] = b.y;
+        }
+    }
+}
+
+template <int DT>
+__global__ void __launch_bounds__(kSqThreads) channel_sqnorm_kernel(const void* x, int64_t m, int64_t n, float* out) {
+    const int lane = threadIdx.x & 31, rg = threadIdx.x >> 5;
+    const int64_t col = static_cast<int64_t>(blockIdx.x) * kSqCols + lane * 4;
+    float acc[4] = {0.0f, 0.0f, 0.0f, 0.0f};
+    if (col < n) {   // n % 4 == 0 is required, so a lane's 4 columns are all inside or all outside
+        for (int64_t r = rg; r < m; r += 8) {
+            float v[4];
+            load4<DT>(x, r * n + col, v);
+#pragma unroll
+            for (int k = 0; k < 4; ++k) acc[k] = __fmaf_rn(v[k], v[k], acc[k]);
+        }
+    }
+    __shared__ float part[8][kSqCols];
+#pragma unroll
+    for (int k = 0; k < 4; ++k) part[rg][lane * 4 + k] = acc[k];
+    __syncthreads();
+    if (threadIdx.x < kSqCols) {
+        const int c = threadIdx.x;
+        const float s = __fadd_rn(__fadd_rn(__fadd_rn(part[0][c], part[1][c]), __fadd_rn(part[2][c], part[3][c])),
+                                  __fadd_rn(__fadd_rn(part[4][c], part[5][c]), __fadd_rn(part[6][c], part[7][c])));
+        const int64_t oc = static_cast<int64_t>(blockIdx.x) * kSqCols + c;
+        if (oc < n) out[oc] = s;
+    }
+}
+
+}  // namespace
+}  // namespace nvfp4
+
+extern "C" int nvfp4_channel_sqnorm_launch(const void* x, int x_dtype, int64_t m, int64_t n, float* out, void* stream) {
+    using namespace nvfp4;
+    if (x_dtype < NVFP4_DT_BF16 || x_dtype > NVFP4_DT_F32) return NVFP4_ERR_BAD_ENUM;
+    if (m < 0 || n < 0 || (n % 4) != 0) return NVFP4_ERR_BAD_SHAPE;
+    if (n == 0) return NVFP4_OK;
+    if (!out || (!x && m > 0)) return NVFP4_ERR_NULL_POINTER;
+    if ((reinterpret_cast<uintptr_t>(x) & 15) || (reinterpret_cast<uintptr_t>(out) & 3)) return NVFP4_ERR_MISALIGNED;
+    const int64_t blocks = (n + kSqCols - 1) / kSqCols;
+    if (blocks > 0x7fffffffLL) return NVFP4_ERR_TOO_LARGE;
+    cudaStream_t s = static_cast<cudaStream_t>(stream);
+    const unsigned g = static_cast<unsigned>(blocks);
+    switch (x_dtype) {
+        case NVFP4_DT_BF16: channel_sqnorm_kernel<NVFP4_DT_BF16><<<g, kSqThreads, 0, s>>>(x, m, n, out); break;
+        case NVFP4_DT_F16: channel_sqnorm_kernel<NVFP4_DT_F16><<<g, kSqThreads, 0, s>>>(x, m, n, out); break;
+        default: channel_sqnorm_kernel<NVFP4_DT_F32><<<g, kSqThreads, 0, s>>>(x, m, n, out); break;
+    }
+    return static_cast<int>(cudaGetLastError());
+}

@@ -34,6 +34,22 @@ def get_nvfp4_global_scale(x: torch.Tensor, FP8_MAX: float = FP8_E4M3_MAX_NVFP4)
     return out[0], out[1]
 
 
+def channel_square_norm(x: torch.Tensor) -> torch.Tensor:
+    """fp32 [1, dim]: squared L2 norm of every input channel (column) of the 2-D batch x - the importance
+    vector for the operand x is multiplied with (README.md:11 of the reference)."""
+    if x.ndim != 2 or not x.is_cuda:
+        raise ValueError("x must be a 2D CUDA tensor")
+    if x.shape[1] % 4:
+        raise ValueError("x.shape[1] must be divisible by 4")
+    x = x.contiguous()
+    out = torch.empty((1, x.shape[1]), dtype=torch.float32, device=x.device)
+    with torch.cuda.device(x.device):
+        st = _lib.lib().nvfp4_channel_sqnorm_launch(x.data_ptr(), _lib.dtype_code(x.dtype), x.shape[0], x.shape[1],
+                                                    out.data_ptr(), _lib.current_stream_ptr(x.device))
+    _lib.check(st, "nvfp4_channel_sqnorm_launch")
+    return out
+
+
 def error_stats(ref, pred):
     diff = pred.float() - ref.float()
     return torch.mean(diff * diff).item(), torch.max(torch.abs(diff)).item()

@@ -1,0 +1,169 @@
+"""Whole-model weight quantization and per-layer NVFP4 GEMMs for a Llama-3-8B-shaped linear stack.
+
+32 decoder layers, each with q 4096x4096, k/v 1024x4096, o 4096x4096, gate/up 14336x4096 and down 4096x14336
+(rows = output features N, columns = input features K).  Weights are random bf16 N(0, 0.02); the importance of a
+weight's input channels is the squared norm of synthetic N(0,1) calibration activations [2048, K] (K = 4096, or
+14336 for `down`, whose input is the MLP's hidden activation).  Layers are partitioned contiguously across ranks
+(4 per GPU on 8 GPUs); nothing is communicated while quantizing, and each layer's GEMMs run where the layer lives.
+
+  python -m nvfp4quant_test_b200.llama_stack --layers 32 --batches 1 32 256 4096
+  python -m torch.distributed.run --nproc-per-node 8 --master-addr 127.0.0.1 -m nvfp4quant_test_b200.llama_stack
+
+Prints one JSON line per rank-0 run with per-phase device times (CUDA events, max over ranks).
+"""
+from __future__ import annotations
+
+import argparse
+import json
+import os
+
+import torch
+
+from . import helper as H
+from . import kernels as K
+
+# name -> (N = out features, K = in features)
+LAYER_SHAPES = {
+    "q": (4096, 4096), "k": (1024, 4096), "v": (1024, 4096), "o": (4096, 4096),
+    "gate": (14336, 4096), "up": (14336, 4096), "down": (4096, 14336),
+}
+CALIB_ROWS = 2048
+
+
+def layers_for_rank(n_layers: int, rank: int, world: int) -> range:
+    """Contiguous block of layers owned by `rank`; sizes differ by at most one."""
+    base, extra = divmod(n_layers, world)
+    start = rank * base + min(rank, extra)
+    return range(start, start + base + (1 if rank < extra else 0))
+
+
+def weights_per_layer() -> int:
+    return sum(n * k for n, k in LAYER_SHAPES.values())
+
+
+def make_layer(layer: int, device, seed: int = 0) -> dict[str, torch.Tensor]:
+    gen = torch.Generator(device=device)
+    gen.manual_seed(seed * 100003 + layer)
+    return {name: torch.normal(0.0, 0.02, size=shape, generator=gen, device=device, dtype=torch.bfloat16)
+            for name, shape in LAYER_SHAPES.items()}
+
+
+def make_calibration(device, seed: int = 0) -> dict[int, torch.Tensor]:
+    """One activation batch per distinct input width, shared by all layers."""
+    gen = torch.Generator(device=device)
+    gen.manual_seed(seed + 7)
+    return {k: torch.normal(0.0, 1.0, size=(CALIB_ROWS, k), generator=gen, device=device, dtype=torch.bfloat16)
+            for k in sorted({k for _, k in LAYER_SHAPES.values()})}
+
+
+def quantize_weight(w: torch.Tensor, importance: torch.Tensor, fp8_max: float = H.FP8_E4M3_MAX_4OVER6):
+    """(codes, swizzled scales, global_scale) with the importance-weighted ScaleSweep quantizer."""
+    gs, gs_inv = H.get_nvfp4_global_scale(w, fp8_max)
+    codes, scales = K.scalesweep_weighted_mse_nvfp4_quant_impl(w, importance, gs_inv)
+    return codes, scales, gs
+
+
+def quantize_layer(weights: dict[str, torch.Tensor], importance: dict[int, torch.Tensor]):
+    return {name: quantize_weight(w, importance[w.shape[1]]) for name, w in weights.items()}
+
+
+def layer_gemms(qlayer: dict, acts: dict[int, torch.Tensor], act_importance: dict[str, torch.Tensor]):
+    """y = x @ W.T for every matrix of the layer with NVFP4 operands; activations quantized with the unweighted sweep
+    unless an importance vector for them is given.  Returns {name: bf16 [tokens, N]}."""
+    out = {}
+    qact: dict[int, tuple] = {}
+    for name, (codes, scales, gs_w) in qlayer.items():
+        k = codes.shape[1] * 2
+        if k not in qact:
+            x = acts[k]
+            gs_x, gs_x_inv = H.get_nvfp4_global_scale(x, H.FP8_E4M3_MAX_4OVER6)
+            imp = act_importance.get(name)
+            if imp is None:
+                qa, sa = K.scalesweep_mse_nvfp4_quant_impl(x, gs_x_inv)
+            else:
+                qa, sa = K.scalesweep_weighted_mse_nvfp4_quant_impl(x, imp, gs_x_inv)
+            qact[k] = (qa, sa, gs_x)
+        qa, sa, gs_x = qact[k]
+        alpha = (gs_x * gs_w).reshape(1).float()
+        out[name] = K.nvfp4_scaled_mm(qa, codes, sa, scales, alpha, torch.bfloat16)
+    return out
+
+
+def run(n_layers: int, token_batches: list[int], seed: int = 0) -> dict:
+    import torch.distributed as dist
+
+    rank = int(os.environ.get("RANK", "0"))
+    local_rank = int(os.environ.get("LOCAL_RANK", "0"))
+    world = int(os.environ.get("WORLD_SIZE", "1"))
+    torch.cuda.set_device(local_rank)
+    dev = torch.device("cuda", local_rank)
+    if world > 1 and not dist.is_initialized():
+        dist.init_process_group("nccl", device_id=dev)
+
+    def sync():
+        if world > 1:
+            dist.barrier()
+        torch.cuda.synchronize()
+
+    def max_ms(ms: float) -> float:
+        if world == 1:
+            return ms
+        t = torch.tensor([ms], dtype=torch.float64, device=dev)
+        dist.all_reduce(t, op=dist.ReduceOp.MAX)
+        return float(t.item())
+
+    mine = layers_for_rank(n_layers, rank, world)
+    calib = make_calibration(dev, seed)
+    importance = {k: H.channel_square_norm(x) for k, x in calib.items()}
+    layers = [make_layer(i, dev, seed) for i in mine]
+    # warm-up (first launches pay module loading), then the timed quantization of all owned layers
+    if layers:
+        quantize_weight(layers[0]["k"], importance[4096])
+    sync()
+    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    e0.record()
+    qlayers = [quantize_layer(w, importance) for w in layers]
+    e1.record()
+    sync()
+    quant_ms = max_ms(e0.elapsed_time(e1))
+    n_weights = n_layers * weights_per_layer()
+    result = {
+        "layers": n_layers, "n_gpus": world, "weights": n_weights,
+        "quantize_ms": quant_ms, "quantize_gweights_per_s": n_weights / (quant_ms * 1e-3) / 1e9,
+        "gemm": [],
+    }
+    for tokens in token_batches:
+        gen = torch.Generator(device=dev)
+        gen.manual_seed(seed + 1000 + tokens)
+        acts = {k: torch.normal(0.0, 1.0, size=(tokens, k), generator=gen, device=dev, dtype=torch.bfloat16)
+                for k in calib}
+        for q in qlayers[:1]:
+            layer_gemms(q, acts, {})
+        sync()
+        e0.record()
+        for q in qlayers:
+            layer_gemms(q, acts, {})
+        e1.record()
+        sync()
+        ms = max_ms(e0.elapsed_time(e1))
+        flops = 2.0 * tokens * weights_per_layer() * n_layers
+        result["gemm"].append({"tokens": tokens, "ms_all_layers": ms, "tflops": flops / (ms * 1e-3) / 1e12,
+                               "includes": "activation global scale + quantization + 7 GEMMs per layer"})
+    if world > 1:
+        dist.destroy_process_group()
+    return result if rank == 0 else {}
+
+
+def main() -> None:
+    ap = argparse.ArgumentParser()
+    ap.add_argument("--layers", type=int, default=32)
+    ap.add_argument("--batches", type=int, nargs="*", default=[1, 32, 256, 4096])
+    ap.add_argument("--seed", type=int, default=0)
+    args = ap.parse_args()
+    res = run(args.layers, args.batches, args.seed)
+    if res:
+        print(json.dumps(res))
+
+
+if __name__ == "__main__":
+    main()

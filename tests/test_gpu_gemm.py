@@ -161,3 +161,58 @@ def test_gemm_full_size_sampled(cuda_lib, oracle):
         part = K.nvfp4_scaled_mm(qa, qb[n0:n0 + 1024], sa, sb.view(torch.uint8).reshape(-1)[n0 * 512:(n0 + 1024) * 512],
                                  alpha, torch.bfloat16)
         assert torch.equal(part, out[:, n0:n0 + 1024])
+
+
+def test_channel_square_norm_kernel(cuda_lib):
+    from nvfp4quant_test_b200 import helper as H
+
+    for shape, dt in (((2048, 4096), torch.bfloat16), ((300, 520), torch.float16), ((77, 132), torch.float32),
+                      ((1, 8), torch.bfloat16)):
+        x = C._laplace(shape, 17, dt if dt != torch.float32 else torch.float32).cuda()
+        got = H.channel_square_norm(x)
+        want = (x.double() ** 2).sum(0, keepdim=True)
+        assert got.shape == (1, shape[1]) and got.dtype == torch.float32
+        assert torch.allclose(got.double(), want, rtol=2e-5, atol=0)
+        assert torch.equal(got, H.channel_square_norm(x))       # fixed summation order
+
+
+def test_llama_stack_layer_shapes(cuda_lib, oracle):
+    """Config-5 shapes: one Llama-3-8B-shaped layer, importance = squared norms of a calibration batch.
+    Weight bytes checked against the oracle on the two narrow matrices in full and on row samples of the rest;
+    the layer's GEMMs at a token batch of 32 against fp64 dot products on sampled outputs."""
+    import nvfp4quant_test_b200.kernels as K
+    from nvfp4quant_test_b200 import helper as H
+    from nvfp4quant_test_b200 import llama_stack as LS
+
+    dev = torch.device("cuda")
+    calib = LS.make_calibration(dev)
+    importance = {k: H.channel_square_norm(x) for k, x in calib.items()}
+    weights = LS.make_layer(0, dev)
+    q = LS.quantize_layer(weights, importance)
+    for name, (codes, scales, gs) in q.items():
+        n, k = LS.LAYER_SHAPES[name]
+        assert codes.shape == (n, k // 2)
+        rows = slice(0, n) if n <= 1024 else slice(n // 2, n // 2 + 256)
+        w = weights[name][rows].contiguous()
+        _, gs_inv_t = H.get_nvfp4_global_scale(weights[name], 256.0)
+        want_codes, want_scales = oracle.quant(1, oracle.bf16_bits(w.cpu()), float(gs_inv_t),
+                                               importance[k].cpu().numpy(), swizzled=False, lower=-8, upper=7)
+        assert np.array_equal(codes[rows].cpu().numpy(), want_codes), name
+        lin = K.unswizzle_vllm_fp4_scale(scales, n, k).view(torch.uint8)[rows]
+        assert np.array_equal(lin.cpu().numpy(), want_scales), name
+    gen = torch.Generator(device=dev)
+    gen.manual_seed(5)
+    acts = {kk: torch.normal(0.0, 1.0, size=(32, kk), generator=gen, device=dev, dtype=torch.bfloat16) for kk in calib}
+    outs = LS.layer_gemms(q, acts, {})
+    for name in ("k", "down", "gate"):
+        n, k = LS.LAYER_SHAPES[name]
+        codes, scales, gs_w = q[name]
+        gs_x, gs_x_inv = H.get_nvfp4_global_scale(acts[k], 256.0)
+        qa, sa = K.scalesweep_mse_nvfp4_quant_impl(acts[k], gs_x_inv)
+        cols = list(range(0, n, max(1, n // 61)))
+        da = H.dequantize_base(qa, K.unswizzle_vllm_fp4_scale(sa, 32, k), torch.tensor(1.0)).double()
+        db = H.dequantize_base(codes[cols], K.unswizzle_vllm_fp4_scale(scales, n, k)[cols], torch.tensor(1.0)).double()
+        ref = (da @ db.T * float(gs_x * gs_w)).cpu().numpy()
+        got = outs[name][:, cols].float().cpu().numpy()
+        tol = np.maximum(np.abs(ref) * 2.0 ** -7, np.abs(ref).max() * 2.0 ** -16)
+        assert outs[name].shape == (32, n) and (np.abs(got - ref) <= tol).all(), name

@@ -103,3 +103,15 @@ def test_host_pipeline_chunk_plan():
     for bad in (0, 100, 129):
         with pytest.raises(ValueError):
             chunk_plan(1024, bad)
+
+
+def test_llama_stack_layer_partition():
+    from nvfp4quant_test_b200.llama_stack import LAYER_SHAPES, layers_for_rank, weights_per_layer
+
+    assert weights_per_layer() == 218_103_808          # 218.1 M weights per layer, 6.98 G for 32 layers
+    assert LAYER_SHAPES["down"] == (4096, 14336) and LAYER_SHAPES["k"] == (1024, 4096)
+    for n_layers, world in ((32, 8), (32, 1), (32, 3), (2, 4)):
+        got = [list(layers_for_rank(n_layers, r, world)) for r in range(world)]
+        assert sum(got, []) == list(range(n_layers))
+        assert max(map(len, got)) - min(map(len, got)) <= 1
+    assert list(layers_for_rank(32, 5, 8)) == [20, 21, 22, 23]
