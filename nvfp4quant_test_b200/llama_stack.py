@@ -89,7 +89,7 @@ def layer_gemms(qlayer: dict, acts: dict[int, torch.Tensor], act_importance: dic
     return out
 
 
-def run(n_layers: int, token_batches: list[int], seed: int = 0) -> dict:
+def run(n_layers: int, token_batches: list[int], seed: int = 0, use_graph: bool = True) -> dict:
     import torch.distributed as dist
 
     rank = int(os.environ.get("RANK", "0"))
@@ -140,14 +140,28 @@ def run(n_layers: int, token_batches: list[int], seed: int = 0) -> dict:
         for q in qlayers[:1]:
             layer_gemms(q, acts, {})
         sync()
+        graph = None
+        if use_graph and qlayers:
+            # every launch is asynchronous and allocation-free at the C ABI, so the whole per-rank layer stack
+            # records into one CUDA graph; replaying it removes the per-launch host cost that dominates small batches
+            graph = torch.cuda.CUDAGraph()
+            with torch.cuda.graph(graph):
+                for q in qlayers:
+                    layer_gemms(q, acts, {})
+            graph.replay()
+            sync()
         e0.record()
-        for q in qlayers:
-            layer_gemms(q, acts, {})
+        if graph is not None:
+            graph.replay()
+        else:
+            for q in qlayers:
+                layer_gemms(q, acts, {})
         e1.record()
         sync()
         ms = max_ms(e0.elapsed_time(e1))
         flops = 2.0 * tokens * weights_per_layer() * n_layers
         result["gemm"].append({"tokens": tokens, "ms_all_layers": ms, "tflops": flops / (ms * 1e-3) / 1e12,
+                               "cuda_graph": graph is not None,
                                "includes": "activation global scale + quantization + 7 GEMMs per layer"})
     if world > 1:
         dist.destroy_process_group()
@@ -159,8 +173,9 @@ def main() -> None:
     ap.add_argument("--layers", type=int, default=32)
     ap.add_argument("--batches", type=int, nargs="*", default=[1, 32, 256, 4096])
     ap.add_argument("--seed", type=int, default=0)
+    ap.add_argument("--no-graph", action="store_true", help="launch the GEMM phase eagerly instead of replaying a CUDA graph")
     args = ap.parse_args()
-    res = run(args.layers, args.batches, args.seed)
+    res = run(args.layers, args.batches, args.seed, use_graph=not args.no_graph)
     if res:
         print(json.dumps(res))
 
