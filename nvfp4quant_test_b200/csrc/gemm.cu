@@ -991,12 +991,12 @@ extern "C" int nvfp4_gemm_launch(const uint8_t* a, const uint8_t* b, const uint8
     }
     cudaStream_t s = static_cast<cudaStream_t>(stream);
     // Kernel choice by a small cost model fitted to measurements on B200: time ~ waves x cost of one tile, where a
-    // wave is 148 single-CTA tiles or 74 CTA-pair tiles.  Relative tile costs: 128x128 -> 0.55, 128x256 -> 1.0,
+    // wave is 148 single-CTA tiles or 74 CTA-pair tiles.  Relative tile costs: 128x128 -> 0.7, 128x256 -> 1.0,
     // pair 256x192 -> 0.68 (0.75 of the MMA work per SM, and its epilogue overlaps the next tile).
     int path = g_gemm_force_path;   // 0 = choose by shape
     if (path == 0) {
         const int64_t mt = (M + 127) / 128;
-        const double c1 = static_cast<double>((mt * ((N + 127) / 128) + 147) / 148) * 0.55;
+        const double c1 = static_cast<double>((mt * ((N + 127) / 128) + 147) / 148) * 0.7;
         const double c2 = static_cast<double>((mt * ((N + 255) / 256) + 147) / 148) * 1.0;
         const double c4 = static_cast<double>((((M + 255) / 256) * ((N + 191) / 192) + 73) / 74) * 0.68;
         path = (c1 <= c2) ? 1 : 2;

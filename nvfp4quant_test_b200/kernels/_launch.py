@@ -70,11 +70,14 @@ def quant_out(variant: int, input: torch.Tensor, importance: torch.Tensor | None
         imp_ptr = importance.data_ptr()
     if m == 0 or physical_n == 0:
         return
-    with torch.cuda.device(input.device):
-        st = _lib.lib().nvfp4_quant_launch_impl(
-            impl, variant, input.data_ptr(), _lib.dtype_code(input.dtype), imp_ptr, input_scale.data_ptr(),
+    args = (impl, variant, input.data_ptr(), _lib.dtype_code(input.dtype), imp_ptr, input_scale.data_ptr(),
             output.data_ptr(), output_scale.data_ptr(), m, n, physical_n, lower, upper,
             1 if is_sf_swizzled_layout else 0, _lib.current_stream_ptr(input.device))
+    if input.device.index == torch.cuda.current_device():
+        st = _lib.lib().nvfp4_quant_launch_impl(*args)
+    else:  # launch with the tensor's device current
+        with torch.cuda.device(input.device):
+            st = _lib.lib().nvfp4_quant_launch_impl(*args)
     if st < 0 and st in (-2, -5):
         raise ValueError(_lib.status_string(st))
     _lib.check(st, "nvfp4_quant_launch")

@@ -247,3 +247,39 @@ def test_host_pipeline_equals_single_launch(cuda_lib, rows, dim, chunk):
         torch.cuda.synchronize()
         assert torch.equal(codes_host, want_codes.cpu())
         assert torch.equal(scales_host, want_scales.view(torch.uint8).reshape(-1).cpu())
+
+
+def test_entry_points_record_into_a_cuda_graph(cuda_lib):
+    """Launches are asynchronous and never synchronise or copy to the host (reference contract: the kernels read
+    `input_scale` on the device), so global scale -> quantize -> GEMM records into one CUDA graph and replays."""
+    import nvfp4quant_test_b200.kernels as K
+    from nvfp4quant_test_b200 import helper as H
+
+    a = C._gauss((256, 1024), 41).cuda()
+    b = C._gauss((512, 1024), 42).cuda()
+
+    def pipeline():
+        gsa, gsa_inv = H.get_nvfp4_global_scale(a, 256.0)
+        gsb, gsb_inv = H.get_nvfp4_global_scale(b, 256.0)
+        qa, sa = K.scalesweep_mse_nvfp4_quant_impl(a, gsa_inv)
+        qb, sb = K.scalesweep_weighted_mse_nvfp4_quant_impl(b, H.channel_square_norm(a), gsb_inv)
+        return K.nvfp4_scaled_mm(qa, qb, sa, sb, (gsa * gsb).reshape(1), torch.bfloat16)
+
+    want = pipeline()
+    torch.cuda.synchronize()
+    side = torch.cuda.Stream()
+    side.wait_stream(torch.cuda.current_stream())
+    with torch.cuda.stream(side):
+        pipeline()                      # warm-up on the capture stream
+    torch.cuda.current_stream().wait_stream(side)
+    graph = torch.cuda.CUDAGraph()
+    with torch.cuda.graph(graph):
+        out = pipeline()
+    out.zero_()
+    graph.replay()
+    torch.cuda.synchronize()
+    assert torch.equal(out, want)
+    a.mul_(2.0)                          # new input values in the same buffers: replay sees them
+    graph.replay()
+    torch.cuda.synchronize()
+    assert torch.equal(out, pipeline())

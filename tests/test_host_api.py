@@ -115,3 +115,31 @@ def test_llama_stack_layer_partition():
         assert sum(got, []) == list(range(n_layers))
         assert max(map(len, got)) - min(map(len, got)) <= 1
     assert list(layers_for_rank(32, 5, 8)) == [20, 21, 22, 23]
+
+
+def test_storage_round_trip(tmp_path):
+    """codes + tiled scales + global scale survive save/load bit for bit; linear <-> tiled converters invert."""
+    from nvfp4quant_test_b200 import storage
+
+    g = torch.Generator().manual_seed(1)
+    tensors = {}
+    for name, (rows, cols) in {"q": (130, 208), "down": (256, 64)}.items():
+        codes = torch.randint(0, 256, (rows, cols // 2), dtype=torch.uint8, generator=g)
+        lin = torch.randint(0, 127, (rows, cols // 16), dtype=torch.uint8, generator=g)
+        tiled = storage.as_tiled_scales(lin, rows, cols)
+        tensors[name] = (codes, tiled, 0.0123 * (1 + len(name)))
+    path = tmp_path / "w.nvfp4"
+    storage.save(path, tensors)
+    back = storage.load(path)
+    for name, (codes, tiled, gs) in tensors.items():
+        c2, s2, g2 = back[name]
+        rows, cols = codes.shape[0], codes.shape[1] * 2
+        assert torch.equal(c2, codes) and torch.equal(s2.view(torch.uint8).reshape(-1), tiled)
+        assert s2.dtype == torch.float8_e4m3fn and float(g2) == float(torch.tensor(gs, dtype=torch.float32))
+        assert torch.equal(storage.as_tiled_scales(storage.as_linear_scales(s2, rows, cols), rows, cols).view(torch.uint8),
+                           tiled)
+    with pytest.raises(ValueError):
+        storage.save(tmp_path / "bad.nvfp4", {"x": (tensors["q"][0], tensors["q"][1][:10], 1.0)})
+    (tmp_path / "junk").write_bytes(b"not a file of ours")
+    with pytest.raises(ValueError):
+        storage.load(tmp_path / "junk")
