@@ -98,6 +98,8 @@ def run(n_layers: int, token_batches: list[int], seed: int = 0, use_graph: bool 
     torch.cuda.set_device(local_rank)
     dev = torch.device("cuda", local_rank)
     if world > 1 and not dist.is_initialized():
+        if os.environ.get("NCCL_DEBUG", "").upper() in ("", "VERSION"):
+            os.environ["NCCL_DEBUG"] = "WARN"      # keep stdout to the JSON line
         dist.init_process_group("nccl", device_id=dev)
 
     def sync():
