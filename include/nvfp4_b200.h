@@ -70,10 +70,10 @@ int nvfp4_quant_launch(int variant, const void* x, int x_dtype, const float* imp
                        const float* gs_inv, uint8_t* codes, uint8_t* scales, int64_t m, int64_t n,
                        int64_t padded_n, int lower, int upper, int swizzled, void* stream);
 
-/* Same, choosing the kernel body: 0 = default (= 3), 1 = scalar (one candidate at a time, the
- * plainest transcription), 2 = f32x2 lanes hold two candidates, 3 = two candidates per trip with
- * element pairs sharing multiply and conversions, 4 = as 2 with the mixed-precision subtract,
- * 5 = one candidate per trip.  All give identical bytes; exposed for testing and timing. */
+/* Same, choosing the kernel body: 0 = default (= 3), 1 = scalar (one candidate at a time, the plainest
+ * transcription), 2 = one candidate per trip with packed multiplies and the mixed-precision subtract,
+ * 3 = two candidates per trip sharing one f32x2 FMA chain.  All give identical bytes; exposed for testing
+ * and timing. */
 int nvfp4_quant_launch_impl(int impl, int variant, const void* x, int x_dtype, const float* importance,
                             const float* gs_inv, uint8_t* codes, uint8_t* scales, int64_t m, int64_t n,
                             int64_t padded_n, int lower, int upper, int swizzled, void* stream);

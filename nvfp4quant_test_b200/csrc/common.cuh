@@ -42,15 +42,6 @@ __device__ __forceinline__ uint32_t f32_to_e4m3(float x) {
     return r & 0xffu;
 }
 
-// Two fp32 -> one byte of E2M1 nibbles (lo -> bits 0-3, hi -> bits 4-7), RNE, saturating.
-__device__ __forceinline__ uint32_t f32x2_to_e2m1x2(float lo, float hi) {
-    uint32_t out;
-    asm("{ .reg .b8 b; cvt.rn.satfinite.e2m1x2.f32 b, %2, %1; cvt.u32.u8 %0, b; }"
-        : "=r"(out)
-        : "f"(lo), "f"(hi));
-    return out;
-}
-
 // Eight fp32 -> 32 bits of E2M1 nibbles, element 0 in the lowest nibble.
 __device__ __forceinline__ uint32_t f32x8_to_e2m1x8(float x0, float x1, float x2, float x3, float x4,
                                                     float x5, float x6, float x7) {
@@ -90,11 +81,6 @@ __device__ __forceinline__ void unpack_f32x2(uint64_t v, float& lo, float& hi) {
 __device__ __forceinline__ uint64_t mul_f32x2(uint64_t a, uint64_t b) {
     uint64_t r;
     asm("mul.rn.f32x2 %0, %1, %2;" : "=l"(r) : "l"(a), "l"(b));
-    return r;
-}
-__device__ __forceinline__ uint64_t sub_f32x2(uint64_t a, uint64_t b) {
-    uint64_t r;
-    asm("sub.rn.f32x2 %0, %1, %2;" : "=l"(r) : "l"(a), "l"(b));
     return r;
 }
 __device__ __forceinline__ uint64_t add_f32x2(uint64_t a, uint64_t b) {

@@ -31,10 +31,6 @@ constexpr int kTmemCols = 512;
 constexpr uint64_t kWaitLimitNs = 2000000000ull;  // 2 s: far above any legitimate wait
 
 __device__ uint32_t g_gemm_status;  // 0 = ok; else (role << 24) | detail of the wait that expired
-// Per-CTA cycle counters of the last launch (diagnostics): [cta][0] MMA loop total, [1] MMA waiting for data,
-// [2] MMA waiting for a free accumulator, [3] producer waiting for a free slot, [4] epilogue waiting for the
-// accumulator, [5] epilogue draining it, [6] tiles done by this CTA.
-__device__ unsigned long long g_gemm_cycles[160][8];
 
 template <int BN>
 struct Cfg {
@@ -115,17 +111,6 @@ __device__ __forceinline__ void tc_fence_after() { asm volatile("tcgen05.fence::
 __device__ __forceinline__ void tc_commit(uint32_t bar) {
     asm volatile("tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%0];" ::"r"(bar) : "memory");
 }
-__device__ __forceinline__ void tc_cp_32x128b_warpx4(uint32_t taddr, uint64_t sdesc) {
-    asm volatile("tcgen05.cp.cta_group::1.32x128b.warpx4 [%0], %1;" ::"r"(taddr), "l"(sdesc) : "memory");
-}
-__device__ __forceinline__ void tc_mma_nvf4(uint32_t d_tmem, uint64_t adesc, uint64_t bdesc, uint32_t idesc,
-                                            uint32_t sfa_tmem, uint32_t sfb_tmem, uint32_t accumulate) {
-    asm volatile(
-        "{ .reg .pred p; setp.ne.b32 p, %4, 0;\n"
-        "  tcgen05.mma.cta_group::1.kind::mxf4nvf4.block_scale.block16 [%0], %1, %2, %3, [%5], [%6], p; }" ::"r"(d_tmem),
-        "l"(adesc), "l"(bdesc), "r"(idesc), "r"(accumulate), "r"(sfa_tmem), "r"(sfb_tmem)
-        : "memory");
-}
 __device__ __forceinline__ void tc_ld_32x32b_x32(uint32_t taddr, uint32_t v[32]) {
     asm volatile(
         "tcgen05.ld.sync.aligned.32x32b.x32.b32 "
@@ -170,16 +155,6 @@ __device__ __forceinline__ void tc_mma_lohi(uint32_t d_tmem, uint32_t a_lo, uint
         "  tcgen05.mma.cta_group::1.kind::mxf4nvf4.block_scale.block16 [%0], da, db, %3, [%5], [%6], p; }" ::"r"(d_tmem),
         "r"(a_lo), "r"(b_lo), "r"(idesc), "r"(accumulate), "r"(sfa_tmem), "r"(sfb_tmem), "r"(kDescHiSw128)
         : "memory");
-}
-
-// K-major operand tile, 128-byte swizzle: rows are 128 B apart, 8-row groups 1024 B apart.
-__device__ __forceinline__ uint64_t smem_desc_sw128(uint32_t addr) {
-    return static_cast<uint64_t>((addr & 0x3ffffu) >> 4) | (1ull << 16) | (static_cast<uint64_t>(1024 >> 4) << 32) |
-           (1ull << 46) | (2ull << 61);
-}
-// Scale tile: 32 rows x 16 B, unswizzled; 8-row core matrices 128 B apart.
-__device__ __forceinline__ uint64_t smem_desc_sf(uint32_t addr) {
-    return static_cast<uint64_t>((addr & 0x3ffffu) >> 4) | (static_cast<uint64_t>(128 >> 4) << 32) | (1ull << 46);
 }
 
 // Instruction descriptor: E2M1 x E2M1, UE4M3 scales, K-major A and B, M = 128, N = BN, K = 64.
@@ -267,7 +242,6 @@ gemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant__ 
             int stage = 0;
             uint32_t phase = 0;
             bool ok = true;
-            long long w_empty = 0;
             for (int tile = blockIdx.x; ok && tile < total_tiles; tile += gridDim.x) {
                 const int ks = tile / mn_tiles, t2 = tile - ks * mn_tiles;
                 const int mt = t2 % m_tiles, nt = t2 / m_tiles;
@@ -276,9 +250,7 @@ gemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant__ 
                 const int rot = p.k_rotate ? (t2 * 5) % kcount : 0;
                 for (int i = 0; i < kcount; ++i) {
                     const int kt = kt_begin + (i + rot) % kcount;
-                    const long long c0 = clock64();
                     if (!(ok = mbar_wait_warp(empty_bar(stage), phase ^ 1u, abort_flag, (1u << 24) | kt))) break;
-                    w_empty += clock64() - c0;
                     const int kb_count = min(4, (p.K - kt * kBK + 63) / 64);  // 64-element K blocks in this stage
                     const uint32_t sf_bytes = 512u * kb_count;
                     int sfb_present = 0;
@@ -308,7 +280,6 @@ gemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant__ 
                     }
                 }
             }
-            if (issuer && blockIdx.x < 160) g_gemm_cycles[blockIdx.x][3] = w_empty;
         }
     } else if (warp == 1) {
         // ------------------------------------------------------------------ MMA issuer
@@ -320,13 +291,8 @@ gemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant__ 
             int acc = 0;
             uint32_t acc_phase = 0;
             bool ok = true;
-            long long w_full = 0, w_acc = 0, ntile = 0;
-            const long long t_begin = clock64();
             for (int tile = blockIdx.x; ok && tile < total_tiles; tile += gridDim.x) {
-                long long c0 = clock64();
                 if (!(ok = mbar_wait_warp(tempty_bar(acc), acc_phase ^ 1u, abort_flag, (2u << 24) | 0xffff))) break;
-                w_acc += clock64() - c0;
-                ++ntile;
                 tc_fence_after();
                 const uint32_t d_tmem = tmem_base + acc * BN;
                 const int ks = tile / mn_tiles, t2 = tile - ks * mn_tiles;
@@ -335,9 +301,7 @@ gemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant__ 
                 const int rot = p.k_rotate ? (t2 * 5) % kcount : 0;
                 for (int i = 0; i < kcount; ++i) {
                     const int kt = kt_begin + (i + rot) % kcount;
-                    c0 = clock64();
                     if (!(ok = mbar_wait_warp(full_bar(stage), phase, abort_flag, (2u << 24) | kt))) break;
-                    w_full += clock64() - c0;
                     tc_fence_after();
                     const int kb_count = min(4, (p.K - kt * kBK + 63) / 64);
                     const uint32_t sbase = base + stage * C::kStageBytes;
@@ -388,12 +352,6 @@ gemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant__ 
                     acc_phase ^= 1u;
                 }
             }
-            if (issuer && blockIdx.x < 160) {
-                g_gemm_cycles[blockIdx.x][0] = clock64() - t_begin;
-                g_gemm_cycles[blockIdx.x][1] = w_full;
-                g_gemm_cycles[blockIdx.x][2] = w_acc;
-                g_gemm_cycles[blockIdx.x][6] = ntile;
-            }
         }
     } else {
         // ------------------------------------------------------------------ epilogue (warps 2..5)
@@ -403,16 +361,12 @@ gemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant__ 
         uint32_t acc_phase = 0;
         bool ok = true;
         const bool vec_ok = (p.N % 8) == 0;
-        long long w_tfull = 0, t_drain = 0;
         for (int tile = blockIdx.x; ok && tile < total_tiles; tile += gridDim.x) {
             const int ks = tile / mn_tiles, t2 = tile - ks * mn_tiles;
             const int mt = t2 % m_tiles, nt = t2 / m_tiles;
-            const long long c0 = clock64();
             ok = mbar_wait(tfull_bar(acc), acc_phase, abort_flag, (3u << 24) | (tile & 0xffff));
             ok = __shfl_sync(0xffffffffu, ok ? 1 : 0, 0) != 0;
             if (!ok) break;
-            const long long c1 = clock64();
-            w_tfull += c1 - c0;
             tc_fence_after();
             const int row = mt * kBM + sp * 32 + lane;
             __nv_bfloat16* orow = p.out + static_cast<int64_t>(row) * p.N;
@@ -458,15 +412,10 @@ gemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant__ 
             tc_fence_before();
             __syncwarp();
             if (lane == 0) mbar_arrive(tempty_bar(acc));
-            t_drain += clock64() - c1;
             if (++acc == C::kAcc) {
                 acc = 0;
                 acc_phase ^= 1u;
             }
-        }
-        if (warp == 2 && lane == 0 && blockIdx.x < 160) {
-            g_gemm_cycles[blockIdx.x][4] = w_tfull;
-            g_gemm_cycles[blockIdx.x][5] = t_drain;
         }
     }
 
@@ -731,21 +680,14 @@ gemm_pair_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_consta
             uint32_t phase = 0, acc_phase = 0;
             int acc = 0;
             bool ok = true;
-            long long w_full = 0, w_acc = 0, ntile = 0, c0;
-            const long long t_begin = clock64();
             for (int tile = pair_id; ok && tile < total_tiles; tile += num_pairs) {
-                c0 = clock64();
                 if (!(ok = mbar_wait_warp(tempty_bar(acc), acc_phase ^ 1u, abort_flag, (2u << 24) | 0xffff))) break;
-                w_acc += clock64() - c0;
-                ++ntile;
                 tc_fence_after();
                 const uint32_t d_tmem = tmem_base + acc * BN;
                 // a 192-wide tile starts 0 or 64 rows into its first scale group: 64 rows = 2 TMEM columns
                 const uint32_t sfb_shift = ((tile / m_tiles) * BN % 128) / 32;
                 for (int kt = 0; kt < k_tiles; ++kt) {
-                    c0 = clock64();
                     if (!(ok = mbar_wait_warp(full_bar(stage), phase, abort_flag, (2u << 24) | kt))) break;
-                    w_full += clock64() - c0;
                     tc_fence_after();
                     const int kb_count = min(4, (p.K - kt * kBK + 63) / 64);
                     const uint32_t sbase = base + stage * C::kStageBytes;
@@ -794,12 +736,6 @@ gemm_pair_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_consta
                     acc = 0;
                     acc_phase ^= 1u;
                 }
-            }
-            if (issuer && pair_id < 160) {
-                g_gemm_cycles[pair_id][0] = clock64() - t_begin;
-                g_gemm_cycles[pair_id][1] = w_full;
-                g_gemm_cycles[pair_id][2] = w_acc;
-                g_gemm_cycles[pair_id][6] = ntile;
             }
         }
     } else {
@@ -1008,14 +944,6 @@ extern "C" int nvfp4_gemm_launch(const uint8_t* a, const uint8_t* b, const uint8
     if (path == 4) return gemm::pair::launch_pair<192>(a, b, p, s);
     if (path == 2) return gemm::launch<256>(a, b, p, s);
     return gemm::launch<128>(a, b, p, s);
-}
-
-// Diagnostics: copies the per-CTA cycle counters of the last 1-CTA GEMM launch (160 x 8 uint64) to the host.
-extern "C" int nvfp4_gemm_debug_cycles(unsigned long long* host_160x8) {
-    if (!host_160x8) return NVFP4_ERR_NULL_POINTER;
-    cudaError_t e = cudaDeviceSynchronize();
-    if (e != cudaSuccess) return static_cast<int>(e);
-    return static_cast<int>(cudaMemcpyFromSymbol(host_160x8, nvfp4::gemm::g_gemm_cycles, sizeof(unsigned long long) * 160 * 8));
 }
 
 extern "C" int nvfp4_gemm_last_status(void* stream, uint32_t* status_host) {

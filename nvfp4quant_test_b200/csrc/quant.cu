@@ -13,9 +13,11 @@
 // a strict `<`, so the lowest raw code wins ties.
 //
 // Mapping: one 16-element block per thread; a warp covers 32 consecutive blocks
-// of one row (1 KiB of bf16).  Two candidates are evaluated per instruction with
-// the packed f32x2 forms (each lane is an independent IEEE operation, so the
-// result is the same as the scalar transcription kept beside it).
+// of one row (1 KiB of bf16).  Three interchangeable loop bodies give identical
+// bytes: the scalar transcription (1), one candidate per trip with packed
+// multiplies and the mixed-precision subtract (2), and the default (3): two
+// candidates per trip whose FMA chains share one f32x2 instruction (each lane of
+// a packed instruction is an independent IEEE operation).
 #include <cuda_bf16.h>
 #include <cuda_fp16.h>
 
@@ -135,67 +137,6 @@ __device__ __forceinline__ uint32_t sweep_scalar(const float v[16], const float 
     return best_raw;
 }
 
-// ---- packed: candidates i and i+1 share every instruction ---------------------------------
-template <bool WEIGHTED>
-__device__ __forceinline__ uint32_t sweep_packed(const float v[16], const float w[16], int first_raw, int ncand,
-                                                 const float2* tab) {
-    uint64_t vv[16];
-#pragma unroll
-    for (int j = 0; j < 16; ++j) vv[j] = pack_f32x2(v[j], v[j]);
-    float best = __int_as_float(0x7f800000);
-    uint32_t best_raw = 0;
-#pragma unroll 1
-    for (int i = 0; i < ncand; i += 2) {
-        const int raw_a = clamp_raw(first_raw + i);
-        const int raw_b = clamp_raw(first_raw + min(i + 1, ncand - 1));
-        const float2 ea = tab[raw_a], eb = tab[raw_b];
-        const uint64_t inv2 = pack_f32x2(ea.x, eb.x);
-        uint64_t tot2;
-        if (!WEIGHTED) {
-            uint64_t acc2 = 0;  // (+0, +0)
-#pragma unroll
-            for (int j = 0; j < 16; ++j) {
-                uint64_t x2 = mul_f32x2(vv[j], inv2);
-                float xa, xb, qa, qb;
-                unpack_f32x2(x2, xa, xb);
-                e2m1_round_pair(xa, xb, qa, qb);
-                uint64_t d2 = sub_f32x2(pack_f32x2(qa, qb), x2);
-                acc2 = fma_f32x2(d2, d2, acc2);
-            }
-            tot2 = acc2;
-        } else {
-            uint64_t pe[8];
-#pragma unroll
-            for (int p = 0; p < 8; ++p) {
-                uint64_t d2[2];
-#pragma unroll
-                for (int h = 0; h < 2; ++h) {
-                    uint64_t x2 = mul_f32x2(vv[2 * p + h], inv2);
-                    float xa, xb, qa, qb;
-                    unpack_f32x2(x2, xa, xb);
-                    e2m1_round_pair(xa, xb, qa, qb);
-                    d2[h] = sub_f32x2(pack_f32x2(qa, qb), x2);
-                }
-                uint64_t a = mul_f32x2(mul_f32x2(d2[0], d2[0]), pack_f32x2(w[2 * p], w[2 * p]));
-                pe[p] = fma_f32x2(mul_f32x2(d2[1], d2[1]), pack_f32x2(w[2 * p + 1], w[2 * p + 1]), a);
-            }
-            tot2 = add_f32x2(add_f32x2(add_f32x2(pe[0], pe[1]), add_f32x2(pe[2], pe[3])),
-                             add_f32x2(add_f32x2(pe[4], pe[5]), add_f32x2(pe[6], pe[7])));
-        }
-        float err_a, err_b;
-        unpack_f32x2(mul_f32x2(tot2, pack_f32x2(ea.y, eb.y)), err_a, err_b);
-        if (err_a < best) {
-            best = err_a;
-            best_raw = raw_a;
-        }
-        if (err_b < best) {  // for an odd count the last lane repeats candidate a: never "better"
-            best = err_b;
-            best_raw = raw_b;
-        }
-    }
-    return best_raw;
-}
-
 // ---- paired: two candidates per loop trip; element pairs share the multiply and both
 // conversions, the difference uses the mixed-precision subtract (f16 grid value minus fp32 x,
 // one full-rate instruction, exact like cvt + sub), and the two candidates' accumulations
@@ -295,72 +236,6 @@ __device__ __forceinline__ uint32_t sweep_paired(const float v[16], const float 
         if (err < best) {
             best = err;
             best_raw = raw;
-        }
-    }
-    return best_raw;
-}
-
-// ---- candidate-packed with the mixed-precision subtract: lanes of every packed register are
-// (candidate a, candidate b) for one element, so no value ever changes lanes -------------------
-__device__ __forceinline__ uint64_t e2m1_diff_lanes(uint64_t x2) {
-    uint64_t d2;
-    asm("{ .reg .b8 b; .reg .b32 h; .reg .b16 lo, hi; .reg .f32 x0, x1, d0, d1;\n"
-        "  mov.b64 {x0, x1}, %1;\n"
-        "  cvt.rn.satfinite.e2m1x2.f32 b, x1, x0;\n"
-        "  cvt.rn.f16x2.e2m1x2 h, b;\n"
-        "  mov.b32 {lo, hi}, h;\n"
-        "  sub.rn.f32.f16 d0, lo, x0;\n"
-        "  sub.rn.f32.f16 d1, hi, x1;\n"
-        "  mov.b64 %0, {d0, d1}; }"
-        : "=l"(d2)
-        : "l"(x2));
-    return d2;
-}
-
-template <bool WEIGHTED>
-__device__ __forceinline__ uint32_t sweep_lanes(const float v[16], const float w[16], int first_raw, int ncand,
-                                                const float2* tab) {
-    uint64_t vv[16];
-#pragma unroll
-    for (int j = 0; j < 16; ++j) vv[j] = pack_f32x2(v[j], v[j]);
-    float best = __int_as_float(0x7f800000);
-    uint32_t best_raw = 0;
-#pragma unroll 1
-    for (int i = 0; i < ncand; i += 2) {
-        const int raw_a = clamp_raw(first_raw + i);
-        const int raw_b = clamp_raw(first_raw + min(i + 1, ncand - 1));
-        const float2 ea = tab[raw_a], eb = tab[raw_b];
-        const uint64_t inv2 = pack_f32x2(ea.x, eb.x);
-        uint64_t tot2;
-        if (!WEIGHTED) {
-            uint64_t acc2 = 0;
-#pragma unroll
-            for (int j = 0; j < 16; ++j) {
-                const uint64_t d2 = e2m1_diff_lanes(mul_f32x2(vv[j], inv2));
-                acc2 = fma_f32x2(d2, d2, acc2);
-            }
-            tot2 = acc2;
-        } else {
-            uint64_t pe[8];
-#pragma unroll
-            for (int p = 0; p < 8; ++p) {
-                const uint64_t d0 = e2m1_diff_lanes(mul_f32x2(vv[2 * p], inv2));
-                const uint64_t d1 = e2m1_diff_lanes(mul_f32x2(vv[2 * p + 1], inv2));
-                const uint64_t t = mul_f32x2(mul_f32x2(d0, d0), pack_f32x2(w[2 * p], w[2 * p]));
-                pe[p] = fma_f32x2(mul_f32x2(d1, d1), pack_f32x2(w[2 * p + 1], w[2 * p + 1]), t);
-            }
-            tot2 = add_f32x2(add_f32x2(add_f32x2(pe[0], pe[1]), add_f32x2(pe[2], pe[3])),
-                             add_f32x2(add_f32x2(pe[4], pe[5]), add_f32x2(pe[6], pe[7])));
-        }
-        float err_a, err_b;
-        unpack_f32x2(mul_f32x2(tot2, pack_f32x2(ea.y, eb.y)), err_a, err_b);
-        if (err_a < best) {
-            best = err_a;
-            best_raw = raw_a;
-        }
-        if (err_b < best) {
-            best = err_b;
-            best_raw = raw_b;
         }
     }
     return best_raw;
@@ -475,9 +350,7 @@ __global__ void __launch_bounds__(kThreads) quant_kernel(const QuantParams p) {
         if (VARIANT == NVFP4_VARIANT_WEIGHTED) base_raw -= (e4m3_to_f32(base_fp8) > base_scale) ? 1 : 0;
         constexpr bool W = VARIANT == NVFP4_VARIANT_WEIGHTED;
         sbyte = (IMPL == 1)   ? sweep_scalar<W>(v, w, base_raw + p.lower, p.ncand, tab)
-                : (IMPL == 2) ? sweep_packed<W>(v, w, base_raw + p.lower, p.ncand, tab)
-                : (IMPL == 4) ? sweep_lanes<W>(v, w, base_raw + p.lower, p.ncand, tab)
-                : (IMPL == 5) ? sweep_single<W>(v, w, base_raw + p.lower, p.ncand, tab)
+                : (IMPL == 2) ? sweep_single<W>(v, w, base_raw + p.lower, p.ncand, tab)
                               : sweep_paired<W>(v, w, base_raw + p.lower, p.ncand, tab);
         inv = tab[sbyte].x;
     }
@@ -517,10 +390,6 @@ cudaError_t launch_impl(int impl, const QuantParams& p, cudaStream_t stream) {
         quant_kernel<DT, VARIANT, 1><<<static_cast<unsigned>(grid), kThreads, 0, stream>>>(p);
     else if (impl == 2)
         quant_kernel<DT, VARIANT, 2><<<static_cast<unsigned>(grid), kThreads, 0, stream>>>(p);
-    else if (impl == 4)
-        quant_kernel<DT, VARIANT, 4><<<static_cast<unsigned>(grid), kThreads, 0, stream>>>(p);
-    else if (impl == 5)
-        quant_kernel<DT, VARIANT, 5><<<static_cast<unsigned>(grid), kThreads, 0, stream>>>(p);
     else
         quant_kernel<DT, VARIANT, 3><<<static_cast<unsigned>(grid), kThreads, 0, stream>>>(p);
     return cudaGetLastError();
@@ -544,7 +413,7 @@ extern "C" int nvfp4_quant_launch_impl(int impl, int variant, const void* x, int
     using namespace nvfp4;
     if (variant < NVFP4_VARIANT_MSE || variant > NVFP4_VARIANT_AMAX) return NVFP4_ERR_BAD_ENUM;
     if (x_dtype < NVFP4_DT_BF16 || x_dtype > NVFP4_DT_F32) return NVFP4_ERR_BAD_ENUM;
-    if (impl < 0 || impl > 5) return NVFP4_ERR_BAD_ENUM;
+    if (impl < 0 || impl > 3) return NVFP4_ERR_BAD_ENUM;
     if (m < 0 || n < 0 || (n % kBlock) != 0 || (padded_n % kBlock) != 0 || padded_n < n) return NVFP4_ERR_BAD_SHAPE;
     if (variant != NVFP4_VARIANT_AMAX && (upper < lower || upper - lower + 1 > 64)) return NVFP4_ERR_BAD_RANGE;
     QuantParams p;
