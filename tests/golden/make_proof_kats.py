@@ -16,7 +16,9 @@ import numpy as np
 
 
 def main() -> None:
-    ref = pathlib.Path(sys.argv[1] if len(sys.argv) > 1 else "/root/reference")
+    if len(sys.argv) < 2:
+        raise SystemExit("usage: make_proof_kats.py /path/to/nvfp4quant_test")
+    ref = pathlib.Path(sys.argv[1])
     sys.path.insert(0, str(ref / "proof"))
     import nvfp4_bound_example as ex  # noqa: E402
 
