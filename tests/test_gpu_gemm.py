@@ -216,3 +216,38 @@ def test_llama_stack_layer_shapes(cuda_lib, oracle):
         got = outs[name][:, cols].float().cpu().numpy()
         tol = np.maximum(np.abs(ref) * 2.0 ** -7, np.abs(ref).max() * 2.0 ** -16)
         assert outs[name].shape == (32, n) and (np.abs(got - ref) <= tol).all(), name
+
+
+@pytest.mark.parametrize("N", [8192, 28672])
+def test_config4_gemm_shapes(cuda_lib, N):
+    """Activation [M, 8192] and weight [N, 8192] ~ Laplace(0,1), each quantized with importance from the other
+    operand's channel square norms; M in {1, 16, 128, 2048, 8192}.  Sampled outputs against fp64 dot products of
+    the dequantized operands."""
+    import nvfp4quant_test_b200.kernels as K
+    from nvfp4quant_test_b200 import helper as H
+    from nvfp4quant_test_b200.kernels.kernel_gemm import gemm_last_status
+
+    lap = torch.distributions.Laplace(torch.tensor(0.0, device="cuda"), torch.tensor(1.0, device="cuda"))
+    torch.manual_seed(N)
+    w = lap.sample((N, 8192)).bfloat16()
+    a_full = lap.sample((8192, 8192)).bfloat16()
+    gs_w, gs_w_inv = H.get_nvfp4_global_scale(w, 256.0)
+    qw, sw = K.scalesweep_weighted_mse_nvfp4_quant_impl(w, H.channel_square_norm(a_full), gs_w_inv)
+    imp_a = H.channel_square_norm(w)
+    sw_lin = K.unswizzle_vllm_fp4_scale(sw, N, 8192)
+    cols = list(range(0, N, N // 53)) + [N - 1]
+    db = H.dequantize_base(qw[cols], sw_lin[cols], torch.tensor(1.0)).double()
+    for M in (1, 16, 128, 2048, 8192):
+        a = a_full[:M].contiguous()
+        gs_a, gs_a_inv = H.get_nvfp4_global_scale(a, 256.0)
+        qa, sa = K.scalesweep_weighted_mse_nvfp4_quant_impl(a, imp_a, gs_a_inv)
+        alpha = (gs_a * gs_w).reshape(1).float()
+        out = K.nvfp4_scaled_mm(qa, qw, sa, sw, alpha, torch.bfloat16)
+        assert gemm_last_status() == 0 and out.shape == (M, N)
+        rows = sorted(set([0, M - 1, M // 2] + list(range(0, M, max(1, M // 7)))))
+        da = H.dequantize_base(qa[rows], K.unswizzle_vllm_fp4_scale(sa, M, 8192)[rows], torch.tensor(1.0)).double()
+        ref = (da @ db.T * float(alpha)).cpu().numpy()
+        got = out[rows][:, cols].float().cpu().numpy()
+        tol = np.maximum(np.abs(ref) * 2.0 ** -7, np.abs(ref).max() * 2.0 ** -16)
+        assert (np.abs(got - ref) <= tol).all(), (M, N, float(np.abs(got - ref).max()))
+        del out

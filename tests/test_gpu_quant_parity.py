@@ -283,3 +283,36 @@ def test_entry_points_record_into_a_cuda_graph(cuda_lib):
     graph.replay()
     torch.cuda.synchronize()
     assert torch.equal(out, pipeline())
+
+
+def test_config3_weighted_weight_quantization_sharded(cuda_lib, oracle):
+    """bf16 weight [8192, 8192] ~ Laplace(0,1), importance = per-input-channel squared norm of a Laplace(0,1)
+    activation batch [4096, 8192]; rows split across 1 / 2 / 4 / 8 shards (one per GPU) must give the bytes of
+    the unsharded call, which must equal the oracle's."""
+    import nvfp4quant_test_b200.kernels as K
+    from nvfp4quant_test_b200 import helper as H
+    from nvfp4quant_test_b200.sharding import row_shards, scale_slab
+
+    lap = torch.distributions.Laplace(torch.tensor(0.0, device="cuda"), torch.tensor(1.0, device="cuda"))
+    torch.manual_seed(0)
+    w = lap.sample((8192, 8192)).bfloat16()
+    act = lap.sample((4096, 8192)).bfloat16()
+    imp = H.channel_square_norm(act)
+    assert torch.allclose(imp, (act.float() ** 2).sum(0, keepdim=True), rtol=1e-4)
+    gs, gs_inv = H.get_nvfp4_global_scale(w, 256.0)
+    codes, scales = K.scalesweep_weighted_mse_nvfp4_quant_impl(w, imp, gs_inv)
+    want_codes, want_scales = oracle.quant(1, oracle.bf16_bits(w.cpu()), float(gs_inv), imp.cpu().numpy(),
+                                           lower=-8, upper=7)
+    assert np.array_equal(codes.cpu().numpy(), want_codes)
+    flat = scales.view(torch.uint8).reshape(-1)
+    assert np.array_equal(flat.cpu().numpy(), want_scales.reshape(-1))
+    for world in (2, 4, 8):
+        for a, b in row_shards(8192, world):
+            c_, s_ = K.scalesweep_weighted_mse_nvfp4_quant_impl(w[a:b], imp, gs_inv)
+            lo, hi = scale_slab(a, b, 512)
+            assert torch.equal(c_, codes[a:b]) and torch.equal(s_.view(torch.uint8).reshape(-1), flat[lo:hi])
+    # the weighted objective is what improves: importance-weighted error below the unweighted sweep's
+    mc, ms = K.scalesweep_mse_nvfp4_quant_impl(w, gs_inv)
+    dq_w = H.dequantize_base(codes[:1024], K.unswizzle_vllm_fp4_scale(scales, 8192, 8192)[:1024], gs)
+    dq_m = H.dequantize_base(mc[:1024], K.unswizzle_vllm_fp4_scale(ms, 8192, 8192)[:1024], gs)
+    assert H.weighted_error_stats(w[:1024], dq_w, imp)[0] <= H.weighted_error_stats(w[:1024], dq_m, imp)[0]
