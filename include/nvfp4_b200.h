@@ -137,6 +137,8 @@ int nvfp4_gemm_force_path(int path);
 /* Testing hook (process-wide) for the single-CTA kernel: number of K ranges (0 = by shape) and K-loop
  * rotation (-1 = by shape, 0 = off, 1 = on).  nvfp4_gemm_workspace_bytes reflects the current setting. */
 int nvfp4_gemm_tune(int k_splits, int k_rotate);
+/* Testing hook (process-wide): m-tiles per band of the persistent kernels' tile numbering (0 = default). */
+int nvfp4_gemm_tune_raster(int group);
 
 /* Device status word of the last GEMM on this device: 0 = ok, else a bounded
  * wait inside the kernel gave up (the kernel returned without hanging).

@@ -16,7 +16,7 @@ DT_BF16, DT_F16, DT_F32 = 0, 1, 2
 
 EXPORTS = (
     "nvfp4_quant_launch", "nvfp4_quant_launch_impl", "nvfp4_global_scale_launch", "nvfp4_channel_sqnorm_launch",
-    "nvfp4_gemm_launch", "nvfp4_gemm_workspace_bytes", "nvfp4_gemm_last_status", "nvfp4_gemm_force_path", "nvfp4_gemm_tune",
+    "nvfp4_gemm_launch", "nvfp4_gemm_workspace_bytes", "nvfp4_gemm_last_status", "nvfp4_gemm_force_path", "nvfp4_gemm_tune", "nvfp4_gemm_tune_raster",
     "nvfp4_probe_div_full_table", "nvfp4_probe_amax_out_scale_table",
     "nvfp4_status_string", "nvfp4_abi_version",
 )
@@ -55,6 +55,8 @@ def lib() -> ctypes.CDLL:
         L.nvfp4_gemm_workspace_bytes.argtypes = [i64, i64, i64]
         L.nvfp4_gemm_last_status.restype = ci
         L.nvfp4_gemm_last_status.argtypes = [vp, vp]
+        L.nvfp4_gemm_tune_raster.restype = ci
+        L.nvfp4_gemm_tune_raster.argtypes = [ci]
         L.nvfp4_gemm_tune.restype = ci
         L.nvfp4_gemm_tune.argtypes = [ci, ci]
         L.nvfp4_gemm_force_path.restype = ci

@@ -177,7 +177,20 @@ struct GemmParams {
     int k_splits, k_tiles_per_split;
     int k_rotate;             // != 0: each tile starts its K loop at a different stage (spreads requests for shared A rows)
     float* partial;
+    int raster_group;         // m-tiles per band of the tile numbering (see tile_to_mn)
 };
+
+// Tile index -> (m tile, n tile).  Tiles are numbered in bands of `group` m-tiles: inside a band the m index runs
+// fastest, then n.  The CTAs that run at the same time then cover a roughly square patch of the output, so every A
+// tile and every B tile is being fetched by a moderate number of CTAs at once instead of one B tile by all of them.
+__device__ __forceinline__ void tile_to_mn(int tile, int m_tiles, int n_tiles, int group, int& mt, int& nt) {
+    const int band = tile / (group * n_tiles);
+    const int first_m = band * group;
+    const int rows = min(group, m_tiles - first_m);
+    const int in_band = tile - band * group * n_tiles;
+    nt = in_band / rows;
+    mt = first_m + in_band - nt * rows;
+}
 
 template <int BN>
 __global__ void __launch_bounds__(kThreads, 1)
@@ -244,7 +257,8 @@ gemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant__ 
             bool ok = true;
             for (int tile = blockIdx.x; ok && tile < total_tiles; tile += gridDim.x) {
                 const int ks = tile / mn_tiles, t2 = tile - ks * mn_tiles;
-                const int mt = t2 % m_tiles, nt = t2 / m_tiles;
+                int mt, nt;
+                tile_to_mn(t2, m_tiles, n_tiles, p.raster_group, mt, nt);
                 const int kt_begin = ks * p.k_tiles_per_split;
                 const int kcount = min(k_tiles, kt_begin + p.k_tiles_per_split) - kt_begin;
                 const int rot = p.k_rotate ? (t2 * 5) % kcount : 0;
@@ -363,7 +377,8 @@ gemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant__ 
         const bool vec_ok = (p.N % 8) == 0;
         for (int tile = blockIdx.x; ok && tile < total_tiles; tile += gridDim.x) {
             const int ks = tile / mn_tiles, t2 = tile - ks * mn_tiles;
-            const int mt = t2 % m_tiles, nt = t2 / m_tiles;
+            int mt, nt;
+            tile_to_mn(t2, m_tiles, n_tiles, p.raster_group, mt, nt);
             ok = mbar_wait(tfull_bar(acc), acc_phase, abort_flag, (3u << 24) | (tile & 0xffff));
             ok = __shfl_sync(0xffffffffu, ok ? 1 : 0, 0) != 0;
             if (!ok) break;
@@ -648,7 +663,8 @@ gemm_pair_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_consta
             uint32_t phase = 0;
             bool ok = true;
             for (int tile = pair_id; ok && tile < total_tiles; tile += num_pairs) {
-                const int mt = tile % m_tiles, nt = tile / m_tiles;
+                int mt, nt;
+                tile_to_mn(tile, m_tiles, n_tiles, p.raster_group, mt, nt);
                 for (int kt = 0; kt < k_tiles; ++kt) {
                     if (!(ok = mbar_wait_warp(empty_bar(stage), phase ^ 1u, abort_flag, (1u << 24) | kt))) break;
                     if (issuer) {
@@ -685,7 +701,9 @@ gemm_pair_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_consta
                 tc_fence_after();
                 const uint32_t d_tmem = tmem_base + acc * BN;
                 // a 192-wide tile starts 0 or 64 rows into its first scale group: 64 rows = 2 TMEM columns
-                const uint32_t sfb_shift = ((tile / m_tiles) * BN % 128) / 32;
+                int mt_unused, nt_of_tile;
+                tile_to_mn(tile, m_tiles, n_tiles, p.raster_group, mt_unused, nt_of_tile);
+                const uint32_t sfb_shift = (nt_of_tile * BN % 128) / 32;
                 for (int kt = 0; kt < k_tiles; ++kt) {
                     if (!(ok = mbar_wait_warp(full_bar(stage), phase, abort_flag, (2u << 24) | kt))) break;
                     tc_fence_after();
@@ -747,7 +765,8 @@ gemm_pair_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_consta
         bool ok = true;
         const bool vec_ok = (p.N % 8) == 0;
         for (int tile = pair_id; ok && tile < total_tiles; tile += num_pairs) {
-            const int mt = tile % m_tiles, nt = tile / m_tiles;
+            int mt, nt;
+            tile_to_mn(tile, m_tiles, n_tiles, p.raster_group, mt, nt);
             ok = mbar_wait(tfull_bar(acc), acc_phase, abort_flag, (3u << 24) | (tile & 0xffff));
             ok = __shfl_sync(0xffffffffu, ok ? 1 : 0, 0) != 0;
             if (!ok) break;
@@ -858,6 +877,7 @@ static int launch_pair(const uint8_t* a, const uint8_t* b, const GemmParams& p, 
 static int g_gemm_force_path = 0;
 static int g_gemm_force_splits = 0;    // 0 = by shape
 static int g_gemm_force_rotate = -1;   // -1 = by shape
+static int g_gemm_raster_group = 0;    // 0 = default
 
 // K ranges for the single-CTA kernel.  Measured on B200 (M <= 128, K = 8192): cutting K never paid, the fixed
 // cost of a second kernel and of the partial tiles outweighs the extra SMs, so the default is one range and the
@@ -875,6 +895,13 @@ extern "C" size_t nvfp4_gemm_workspace_bytes(int64_t M, int64_t N, int64_t K) {
 }
 
 // Testing hook: K ranges (0 = by shape) and K-loop rotation (-1 = by shape, 0 = off, 1 = on) of the single-CTA kernel.
+// Testing hook: m-tiles per band of the tile numbering (0 = default).
+extern "C" int nvfp4_gemm_tune_raster(int group) {
+    if (group < 0 || group > 4096) return NVFP4_ERR_BAD_ENUM;
+    g_gemm_raster_group = group;
+    return NVFP4_OK;
+}
+
 extern "C" int nvfp4_gemm_tune(int k_splits, int k_rotate) {
     if (k_splits < 0 || k_splits > 16 || k_rotate < -1 || k_rotate > 1) return NVFP4_ERR_BAD_ENUM;
     g_gemm_force_splits = k_splits;
@@ -920,6 +947,8 @@ extern "C" int nvfp4_gemm_launch(const uint8_t* a, const uint8_t* b, const uint8
     p.k_splits = (k_tiles_total + p.k_tiles_per_split - 1) / p.k_tiles_per_split;   // no empty range
     p.k_rotate = g_gemm_force_rotate > 0 ? 1 : 0;
     p.partial = static_cast<float*>(workspace);
+    // default: one band over all m-tiles (band sizes 1..16 measured within noise of it on B200)
+    p.raster_group = g_gemm_raster_group > 0 ? g_gemm_raster_group : (1 << 20);
     if (p.k_splits > 1) {
         const size_t need = static_cast<size_t>(p.k_splits) * static_cast<size_t>(M) * static_cast<size_t>(N) * sizeof(float);
         if (!workspace || workspace_bytes < need) return NVFP4_ERR_WORKSPACE;

@@ -316,3 +316,48 @@ def test_config3_weighted_weight_quantization_sharded(cuda_lib, oracle):
     dq_w = H.dequantize_base(codes[:1024], K.unswizzle_vllm_fp4_scale(scales, 8192, 8192)[:1024], gs)
     dq_m = H.dequantize_base(mc[:1024], K.unswizzle_vllm_fp4_scale(ms, 8192, 8192)[:1024], gs)
     assert H.weighted_error_stats(w[:1024], dq_w, imp)[0] <= H.weighted_error_stats(w[:1024], dq_m, imp)[0]
+
+
+def test_randomized_differential_against_oracle(cuda_lib, oracle):
+    """Seeded random sweep over shapes, dtypes, layouts, K padding, candidate windows, scale magnitudes and
+    importance vectors (including zeros and huge weights): every byte must equal the oracle's."""
+    rng = np.random.default_rng(20240607)
+    for trial in range(60):
+        m = int(rng.choice([1, 3, 31, 64, 128, 129, 200, 257, 400]))
+        n = 16 * int(rng.integers(1, 40))
+        dtype = [torch.bfloat16, torch.float16, torch.float32][int(rng.integers(0, 3))]
+        variant = ["mse", "weighted", "amax"][int(rng.integers(0, 3))]
+        swizzled = bool(rng.integers(0, 2))
+        padded_n = n + 16 * int(rng.integers(0, 4)) if rng.integers(0, 3) == 0 else None
+        dist = int(rng.integers(0, 4))
+        g = torch.Generator().manual_seed(1000 + trial)
+        if dist == 0:
+            x = torch.randn((m, n), generator=g)
+        elif dist == 1:
+            x = torch.randn((m, n), generator=g) * torch.exp(4 * torch.randn((m, 1), generator=g))    # rows of very different size
+        elif dist == 2:
+            x = torch.randn((m, n), generator=g) * (torch.rand((m, n), generator=g) < 0.15)               # sparse
+        else:
+            x = torch.round(torch.randn((m, n), generator=g) * 4) / 4                                     # many exact ties
+        x = x.to(dtype)
+        if variant == "amax" and dtype == torch.float32:
+            dtype, x = torch.bfloat16, x.to(torch.bfloat16)
+        gs_inv = float(np.float32(rng.choice([1.0, 37.5, 565.9, 1e-3, 3000.0])))
+        imp = None
+        lower = upper = None
+        if variant == "weighted":
+            imp = torch.rand((1, n), generator=g) * 3
+            if trial % 4 == 0:
+                imp[0, ::5] = 0.0
+            if trial % 7 == 0:
+                imp[0, 1::9] = 1e20
+            lower, upper = int(rng.integers(-10, 1)), int(rng.integers(0, 9))
+        c = dict(x=x, variant=variant, importance=imp, swizzled=swizzled, padded_n=padded_n, lower=lower, upper=upper)
+        table = _amax_table(cuda_lib, gs_inv) if variant == "amax" else None
+        want_codes, want_scales = util.oracle_quant_case(oracle, c, gs_inv, table)
+        codes, scales, intact = _run_cuda(c, gs_inv)
+        idx = util.logical_scale_index(m, (padded_n or n) // 16, swizzled)
+        tag = (trial, m, n, str(dtype), variant, swizzled, padded_n, lower, upper, gs_inv)
+        assert intact, tag
+        assert np.array_equal(codes, want_codes), tag
+        assert np.array_equal(scales[idx], want_scales[idx]), tag
