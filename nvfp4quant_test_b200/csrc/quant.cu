@@ -341,8 +341,10 @@ __global__ void __launch_bounds__(kThreads) quant_kernel(const QuantParams p) {
         sbyte = f32_to_e4m3(sf);
         inv = tab[sbyte & 0x7f].x;
     } else {
+        const uint64_t gs2 = pack_f32x2(gs_inv, gs_inv);
 #pragma unroll
-        for (int j = 0; j < 16; ++j) v[j] = __fmul_rn(v[j], gs_inv);
+        for (int q = 0; q < 8; ++q)   // packed multiply: each lane is the same IEEE product as a scalar mul.rn
+            unpack_f32x2(mul_f32x2(pack_f32x2(v[2 * q], v[2 * q + 1]), gs2), v[2 * q], v[2 * q + 1]);
         const float amax = max_abs16(v);
         const float base_scale = __fmul_rn(amax, __uint_as_float(0x3E2AAAABu));  // fp32(1/6)
         const uint32_t base_fp8 = f32_to_e4m3(base_scale);
@@ -356,12 +358,13 @@ __global__ void __launch_bounds__(kThreads) quant_kernel(const QuantParams p) {
     }
 
     if (valid) {
-        const uint32_t lo = f32x8_to_e2m1x8(__fmul_rn(v[0], inv), __fmul_rn(v[1], inv), __fmul_rn(v[2], inv),
-                                            __fmul_rn(v[3], inv), __fmul_rn(v[4], inv), __fmul_rn(v[5], inv),
-                                            __fmul_rn(v[6], inv), __fmul_rn(v[7], inv));
-        const uint32_t hi = f32x8_to_e2m1x8(__fmul_rn(v[8], inv), __fmul_rn(v[9], inv), __fmul_rn(v[10], inv),
-                                            __fmul_rn(v[11], inv), __fmul_rn(v[12], inv), __fmul_rn(v[13], inv),
-                                            __fmul_rn(v[14], inv), __fmul_rn(v[15], inv));
+        const uint64_t inv2 = pack_f32x2(inv, inv);
+        float x[16];
+#pragma unroll
+        for (int q = 0; q < 8; ++q)
+            unpack_f32x2(mul_f32x2(pack_f32x2(v[2 * q], v[2 * q + 1]), inv2), x[2 * q], x[2 * q + 1]);
+        const uint32_t lo = f32x8_to_e2m1x8(x[0], x[1], x[2], x[3], x[4], x[5], x[6], x[7]);
+        const uint32_t hi = f32x8_to_e2m1x8(x[8], x[9], x[10], x[11], x[12], x[13], x[14], x[15]);
         *reinterpret_cast<uint2*>(p.codes + (row * p.bout + col) * 8) = make_uint2(lo, hi);
     } else {
         sbyte = 0;  // padding rows / columns of the scale buffer read as zero scales
