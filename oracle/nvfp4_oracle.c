@@ -326,3 +326,39 @@ int nvfp4_oracle_gemm(const uint8_t* a, const uint8_t* b, const uint8_t* sfa, co
 
 int nvfp4_oracle_div_full_table_is_measured(void) { return NVFP4_DIV_FULL_TABLE_MEASURED; }
 uint32_t nvfp4_oracle_div_full_bits(int raw) { return NVFP4_DIV_FULL_RCP_BITS[raw & 127]; }
+
+/*
+ * For nblocks fp32 blocks (gs_inv = 1): hist[off + 64] += 1 where off = exhaustive optimum raw - base raw,
+ * base = RNE_E4M3(amax/6).  Blocks whose base code is >= 120 (within reach of saturation) or < 16 (window touches
+ * the subnormal codes, where scales are equally spaced and the claim does not apply) are counted in *skipped.
+ * Supports the reference's claim (proof/proof.md) that for normal scales away from saturation a minimiser lies in
+ * [base-3, base+7].
+ */
+void nvfp4_oracle_offset_histogram(const float* x, int64_t nblocks, int64_t hist[128], int64_t* skipped) {
+    int64_t local_skipped = 0;
+#pragma omp parallel
+    {
+        int64_t h[128];
+        int64_t sk = 0;
+        memset(h, 0, sizeof(h));
+#pragma omp for schedule(static)
+        for (int64_t b = 0; b < nblocks; ++b) {
+            const float* v = x + b * 16;
+            float amax = 0.0f;
+            for (int j = 0; j < 16; ++j) amax = fmaxf(amax, fabsf(v[j]));
+            int base = nvfp4_oracle_f32_to_e4m3(amax * bits_to_f32(0x3E2AAAABu));
+            if (amax == 0.0f || base >= 120 || base < 16) { ++sk; continue; }
+            int best = nvfp4_oracle_best_raw_exhaustive(v);
+            int off = best - base;
+            if (off < -64) off = -64;
+            if (off > 63) off = 63;
+            ++h[off + 64];
+        }
+#pragma omp critical
+        {
+            for (int i = 0; i < 128; ++i) hist[i] += h[i];
+            local_skipped += sk;
+        }
+    }
+    *skipped = local_skipped;
+}

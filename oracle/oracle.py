@@ -27,7 +27,7 @@ def build(force: bool = False) -> pathlib.Path:
     """Compile the oracle with the Makefile beside it (gcc only)."""
     if force or not _LIB_PATH.exists() or any(
         (_HERE / f).stat().st_mtime > _LIB_PATH.stat().st_mtime
-        for f in ("nvfp4_oracle.c", "div_full_table.h")
+        for f in ("nvfp4_oracle.c", "div_full_table.h", "oracle.py")
     ):
         subprocess.run(["make", "-C", str(_HERE), "-B"], check=True, capture_output=True)
     return _LIB_PATH
@@ -56,6 +56,8 @@ def lib() -> ctypes.CDLL:
         L.nvfp4_oracle_f32_to_e4m3.argtypes = [f32]
         L.nvfp4_oracle_swizzled_offset.restype = i64
         L.nvfp4_oracle_swizzled_offset.argtypes = [i64, i64, i64]
+        L.nvfp4_oracle_offset_histogram.restype = None
+        L.nvfp4_oracle_offset_histogram.argtypes = [vp, i64, vp, vp]
         L.nvfp4_oracle_div_full_table_is_measured.restype = ci
         L.nvfp4_oracle_div_full_bits.restype = ctypes.c_uint32
         L.nvfp4_oracle_div_full_bits.argtypes = [ci]
@@ -146,6 +148,16 @@ def sweep_block(variant: int, v16: np.ndarray, w16: np.ndarray | None = None, lo
     v = np.ascontiguousarray(v16, dtype=np.float32)
     w = None if w16 is None else np.ascontiguousarray(w16, dtype=np.float32)
     return lib().nvfp4_oracle_sweep_block_f32(variant, _ptr(v), _ptr(w), lower, upper)
+
+
+def offset_histogram(blocks: np.ndarray):
+    """{offset: count} of (exhaustive optimum raw code - RNE base code) over fp32 blocks [n, 16], and the number of
+    blocks skipped (base code outside 16..119: subnormal window or within reach of saturation)."""
+    x = np.ascontiguousarray(blocks, dtype=np.float32).reshape(-1, 16)
+    hist = np.zeros(128, dtype=np.int64)
+    skipped = np.zeros(1, dtype=np.int64)
+    lib().nvfp4_oracle_offset_histogram(_ptr(x), x.shape[0], _ptr(hist), _ptr(skipped))
+    return {i - 64: int(c) for i, c in enumerate(hist) if c}, int(skipped[0])
 
 
 def e4m3_to_f32(raw: int) -> float:

@@ -143,3 +143,19 @@ def test_storage_round_trip(tmp_path):
     (tmp_path / "junk").write_bytes(b"not a file of ours")
     with pytest.raises(ValueError):
         storage.load(tmp_path / "junk")
+
+
+def test_report_tables():
+    from nvfp4quant_test_b200.report import build_report
+
+    def res(name, scale):
+        return {"name": name, "sm_count": 148, "dim": 8192, "environment": {"torch": "2.11", "gpu": "B200"},
+                "results": [{"bsz": b, "dim": 8192, "latency_ms": scale * b / 1000, "mse": 0.0066, "max_abs_error": 0.586,
+                             "weighted_mse": 0.0066} for b in (1, 128, 8192)]}
+
+    text = build_report([res("cuda.ScaleSweep_MSE", 0.0155), res("cuda.vllm", 0.005)])
+    assert "| kernel | 1 | 128 | 8192 |" in text
+    assert "| cuda.ScaleSweep_MSE | 1.55e-05 | 0.001984 | 0.126976 |" in text
+    assert "## Quantization error at bsz = 8192" in text and "| cuda.vllm | 0.0066 | 0.0066 | 0.586 |" in text
+    with pytest.raises(ValueError):
+        build_report([])

@@ -145,3 +145,31 @@ def test_window_clamps_at_both_ends(oracle, variant):
     r_tiny = oracle.sweep_block(variant, tiny, w, lo, up)
     r_huge = oracle.sweep_block(variant, huge, w, lo, up)
     assert 1 <= r_tiny <= 8 and r_huge == 126
+
+
+def test_sweep_window_covers_the_exhaustive_optimum(oracle):
+    """Regression of the reference's range claim (proof/proof.md:16-19,59): for normal scales away from saturation
+    the fp32 exhaustive optimum over all 126 scales lies within base-3 .. base+7, so the 11-candidate sweep loses
+    nothing.  (With subnormal base codes the optimum can sit far outside the window - e.g. +14 for blocks with a
+    single tiny non-zero - and the reference sweeps the same window regardless; those blocks are skipped here.)
+    Checked on 300k blocks from Gaussian, Laplace, sparse, outlier-heavy and near-uniform distributions at several
+    magnitudes, and the observed offsets actually reach both ends of the window region."""
+    rng = np.random.default_rng(7)
+    n = 60000
+    parts = [
+        rng.standard_normal((n, 16)),
+        rng.laplace(size=(n, 16)),
+        rng.standard_normal((n, 16)) * (rng.random((n, 16)) < 0.2),
+        rng.standard_normal((n, 16)) * np.where(rng.random((n, 16)) < 0.07, 12.0, 1.0),
+        rng.uniform(4.0, 6.5, size=(n, 16)) * rng.choice([-1.0, 1.0], size=(n, 16)),
+    ]
+    scales = [1.0, 37.0, 2.5, 3.3, 0.4]
+    total = {}
+    for part, sc in zip(parts, scales):
+        hist, skipped = oracle.offset_histogram((part * sc).astype(np.float32))
+        assert skipped < n // 20          # all-zero sparse blocks
+        for k, v in hist.items():
+            total[k] = total.get(k, 0) + v
+    assert min(total) >= -3 and max(total) <= 7, total
+    assert sum(total.values()) > 285000
+    assert total.get(0, 0) > 0 and max(total) >= 3 and min(total) <= -1, total
