@@ -91,18 +91,23 @@ __device__ __forceinline__ float max_abs16(const float v[16]) {
     return fmaxf(fmaxf(fmaxf(m[0], m[1]), fmaxf(m[2], m[3])), fmaxf(fmaxf(m[4], m[5]), fmaxf(m[6], m[7])));
 }
 
-__device__ __forceinline__ int clamp_raw(int raw) { return min(max(raw, 1), 126); }
+// Candidate table: entry k describes raw code clamp(k - kTabPad, 1, 126), so a sweep that starts at
+// tab[first + kTabPad] reads consecutive entries and needs no per-candidate clamping.
+// .x = .y = 1/s (div.full.f32), .z = s*s, .w = the raw code (bit pattern).
+constexpr int kTabPad = 64;
+constexpr int kTabSize = 256;
 
 // ---- scalar transcription: one candidate at a time --------------------------------------
 template <bool WEIGHTED>
-__device__ __forceinline__ uint32_t sweep_scalar(const float v[16], const float w[16], int first_raw, int ncand,
-                                                 const float2* tab) {
+__device__ __forceinline__ uint32_t sweep_scalar(const float v[16], const float w[16], int first_idx, int ncand,
+                                                 const float4* tab) {
     float best = __int_as_float(0x7f800000);
     uint32_t best_raw = 0;
 #pragma unroll 1
     for (int i = 0; i < ncand; ++i) {
-        const int raw = clamp_raw(first_raw + i);
-        const float2 e = tab[raw];
+        const float4 e4 = tab[first_idx + i];
+        const float2 e = make_float2(e4.x, e4.z);
+        const uint32_t raw = __float_as_uint(e4.w);
         float err;
         if (!WEIGHTED) {
             float acc = 0.0f;
@@ -154,8 +159,8 @@ __device__ __forceinline__ void e2m1_diff_pair(uint64_t x2, float& d0, float& d1
 }
 
 template <bool WEIGHTED>
-__device__ __forceinline__ uint32_t sweep_paired(const float v[16], const float w[16], int first_raw, int ncand,
-                                                 const float2* tab) {
+__device__ __forceinline__ uint32_t sweep_paired(const float v[16], const float w[16], int first_idx, int ncand,
+                                                 const float4* tab) {
     uint64_t vp[8];  // (v[2p], v[2p+1])
 #pragma unroll
     for (int p = 0; p < 8; ++p) vp[p] = pack_f32x2(v[2 * p], v[2 * p + 1]);
@@ -163,10 +168,9 @@ __device__ __forceinline__ uint32_t sweep_paired(const float v[16], const float 
     uint32_t best_raw = 0;
 #pragma unroll 1
     for (int i = 0; i + 1 < ncand; i += 2) {
-        const int raw_a = clamp_raw(first_raw + i);
-        const int raw_b = clamp_raw(first_raw + i + 1);
-        const float2 ea = tab[raw_a], eb = tab[raw_b];
-        const uint64_t inv_a = pack_f32x2(ea.x, ea.x), inv_b = pack_f32x2(eb.x, eb.x);
+        const float4 ea = tab[first_idx + i], eb = tab[first_idx + i + 1];
+        const uint32_t raw_a = __float_as_uint(ea.w), raw_b = __float_as_uint(eb.w);
+        const uint64_t inv_a = pack_f32x2(ea.x, ea.y), inv_b = pack_f32x2(eb.x, eb.y);
         uint64_t tot2;
         if (!WEIGHTED) {
             uint64_t acc2 = 0;  // (+0, +0): candidate a in the low lane, b in the high lane
@@ -195,7 +199,7 @@ __device__ __forceinline__ uint32_t sweep_paired(const float v[16], const float 
                              add_f32x2(add_f32x2(pe[4], pe[5]), add_f32x2(pe[6], pe[7])));
         }
         float err_a, err_b;
-        unpack_f32x2(mul_f32x2(tot2, pack_f32x2(ea.y, eb.y)), err_a, err_b);
+        unpack_f32x2(mul_f32x2(tot2, pack_f32x2(ea.z, eb.z)), err_a, err_b);
         if (err_a < best) {
             best = err_a;
             best_raw = raw_a;
@@ -206,9 +210,10 @@ __device__ __forceinline__ uint32_t sweep_paired(const float v[16], const float 
         }
     }
     if (ncand & 1) {  // odd count: the last candidate alone, scalar chain
-        const int raw = clamp_raw(first_raw + ncand - 1);
-        const float2 e = tab[raw];
-        const uint64_t inv2 = pack_f32x2(e.x, e.x);
+        const float4 e4 = tab[first_idx + ncand - 1];
+        const float2 e = make_float2(e4.x, e4.z);
+        const uint32_t raw = __float_as_uint(e4.w);
+        const uint64_t inv2 = pack_f32x2(e4.x, e4.y);
         float err;
         if (!WEIGHTED) {
             float acc = 0.0f;
@@ -243,8 +248,8 @@ __device__ __forceinline__ uint32_t sweep_paired(const float v[16], const float 
 
 // ---- one candidate per trip, element pairs share the multiply, scalar FMA chain ----------------
 template <bool WEIGHTED>
-__device__ __forceinline__ uint32_t sweep_single(const float v[16], const float w[16], int first_raw, int ncand,
-                                                 const float2* tab) {
+__device__ __forceinline__ uint32_t sweep_single(const float v[16], const float w[16], int first_idx, int ncand,
+                                                 const float4* tab) {
     uint64_t vp[8];
 #pragma unroll
     for (int p = 0; p < 8; ++p) vp[p] = pack_f32x2(v[2 * p], v[2 * p + 1]);
@@ -252,9 +257,10 @@ __device__ __forceinline__ uint32_t sweep_single(const float v[16], const float 
     uint32_t best_raw = 0;
 #pragma unroll 1
     for (int i = 0; i < ncand; ++i) {
-        const int raw = clamp_raw(first_raw + i);
-        const float2 e = tab[raw];
-        const uint64_t inv2 = pack_f32x2(e.x, e.x);
+        const float4 e4 = tab[first_idx + i];
+        const float2 e = make_float2(e4.x, e4.z);
+        const uint32_t raw = __float_as_uint(e4.w);
+        const uint64_t inv2 = pack_f32x2(e4.x, e4.y);
         float err;
         if (!WEIGHTED) {
             float acc = 0.0f;
@@ -289,21 +295,25 @@ __device__ __forceinline__ uint32_t sweep_single(const float v[16], const float 
 
 template <int DT, int VARIANT, int IMPL>
 __global__ void __launch_bounds__(kThreads) quant_kernel(const QuantParams p) {
-    // tab[raw] = (multiplier for the block's elements, scale*scale)
-    __shared__ float2 tab[128];
+    static_assert(kThreads == kTabSize, "one table entry per thread");
+    __shared__ float4 tab[kTabSize];
     const float gs_inv = __ldg(p.gs_inv);
-    if (threadIdx.x < 128) {
-        const uint32_t raw = threadIdx.x;
-        const float s = e4m3_to_f32(raw);
-        float2 e;
-        if (VARIANT == NVFP4_VARIANT_AMAX) {
-            e.x = (raw == 0) ? 0.0f : rcp_approx_ftz(__fmul_rn(s, rcp_approx_ftz(gs_inv)));
-            e.y = 0.0f;
+    {
+        float4 e;
+        if (VARIANT == NVFP4_VARIANT_AMAX) {   // tab[raw].x = multiplier for scale byte raw (entries 0..127 used)
+            const uint32_t raw = threadIdx.x & 127;
+            const float s = e4m3_to_f32(raw);
+            e.x = e.y = (raw == 0) ? 0.0f : rcp_approx_ftz(__fmul_rn(s, rcp_approx_ftz(gs_inv)));
+            e.z = 0.0f;
+            e.w = __uint_as_float(raw);
         } else {
-            e.x = div_full(1.0f, s);
-            e.y = __fmul_rn(s, s);
+            const uint32_t raw = static_cast<uint32_t>(min(max(static_cast<int>(threadIdx.x) - kTabPad, 1), 126));
+            const float s = e4m3_to_f32(raw);
+            e.x = e.y = div_full(1.0f, s);
+            e.z = __fmul_rn(s, s);
+            e.w = __uint_as_float(raw);
         }
-        tab[raw] = e;
+        tab[threadIdx.x] = e;
     }
     __syncthreads();
 
@@ -351,10 +361,13 @@ __global__ void __launch_bounds__(kThreads) quant_kernel(const QuantParams p) {
         int base_raw = static_cast<int>(base_fp8);
         if (VARIANT == NVFP4_VARIANT_WEIGHTED) base_raw -= (e4m3_to_f32(base_fp8) > base_scale) ? 1 : 0;
         constexpr bool W = VARIANT == NVFP4_VARIANT_WEIGHTED;
-        sbyte = (IMPL == 1)   ? sweep_scalar<W>(v, w, base_raw + p.lower, p.ncand, tab)
-                : (IMPL == 2) ? sweep_single<W>(v, w, base_raw + p.lower, p.ncand, tab)
-                              : sweep_paired<W>(v, w, base_raw + p.lower, p.ncand, tab);
-        inv = tab[sbyte].x;
+        // clamping the start once is enough: with it below -kTabPad every candidate is raw 1, above 127 every one 126
+        const int first_idx = min(max(base_raw + p.lower, -kTabPad), 127) + kTabPad;
+        sbyte = (IMPL == 1)   ? sweep_scalar<W>(v, w, first_idx, p.ncand, tab)
+                : (IMPL == 2) ? sweep_single<W>(v, w, first_idx, p.ncand, tab)
+                              : sweep_paired<W>(v, w, first_idx, p.ncand, tab);
+        // sbyte is 0 only when no candidate had a comparable (non-NaN, < inf) error: 1/0 as the reference computes it
+        inv = (sbyte == 0) ? div_full(1.0f, 0.0f) : tab[sbyte + kTabPad].x;
     }
 
     if (valid) {
