@@ -43,7 +43,8 @@ def build(force: bool = False, verbose: bool = False) -> pathlib.Path:
     if not force and not _stale():
         return LIB
     srcs = [str(CSRC / s) for s in SOURCES if (CSRC / s).exists()]
-    cmd = [_nvcc(), *NVCC_FLAGS, f"-I{INCLUDE}", f"-I{CSRC}", "-shared", "-o", str(LIB), *srcs]
+    extra = os.environ.get("NVFP4_EXTRA_NVCC_FLAGS", "").split()   # e.g. -DNVFP4_QUANT_MIN_BLOCKS=6 for experiments
+    cmd = [_nvcc(), *NVCC_FLAGS, *extra, f"-I{INCLUDE}", f"-I{CSRC}", "-shared", "-o", str(LIB), *srcs]
     if verbose:
         cmd.insert(1, "-Xptxas=-v")
     env = dict(os.environ)

@@ -27,6 +27,11 @@ namespace nvfp4 {
 namespace {
 
 constexpr int kThreads = 256;
+// Resident CTAs per SM the register allocation aims for: the unweighted sweep fits 5 (48 registers) without
+// spilling; the weighted one keeps 16 importance weights live and needs 64 registers (4 CTAs).
+#ifndef NVFP4_QUANT_MIN_BLOCKS
+#define NVFP4_QUANT_MIN_BLOCKS 5
+#endif
 
 struct QuantParams {
     const void* x;
@@ -294,7 +299,8 @@ __device__ __forceinline__ uint32_t sweep_single(const float v[16], const float 
 }
 
 template <int DT, int VARIANT, int IMPL>
-__global__ void __launch_bounds__(kThreads) quant_kernel(const QuantParams p) {
+__global__ void __launch_bounds__(kThreads, VARIANT == NVFP4_VARIANT_WEIGHTED ? 4 : NVFP4_QUANT_MIN_BLOCKS)
+quant_kernel(const QuantParams p) {
     static_assert(kThreads == kTabSize, "one table entry per thread");
     __shared__ float4 tab[kTabSize];
     const float gs_inv = __ldg(p.gs_inv);
