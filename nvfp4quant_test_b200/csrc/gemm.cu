@@ -6,7 +6,7 @@
 //
 // Structure (one persistent CTA per SM, 192 threads):
 //   warp 0      producer: TMA tile loads of A / B (128-byte swizzle) and bulk copies of the
-//               scale tiles into a 4-stage shared-memory ring
+//               scale tiles into a shared-memory ring (6 stages with 128-wide tiles, 4 with 256-wide)
 //   warp 1      MMA issuer: tcgen05.cp scale tiles smem -> TMEM, then
 //               tcgen05.mma.kind::mxf4nvf4.block_scale (K = 64 per instruction) into a TMEM
 //               accumulator; tcgen05.commit releases ring slots / publishes the accumulator
@@ -25,7 +25,6 @@ namespace gemm {
 constexpr int kBM = 128;          // rows of A per tile
 constexpr int kBKBytes = 128;     // bytes of K per stage row (= 256 FP4 elements, one swizzle row)
 constexpr int kBK = 256;          // elements of K per stage
-constexpr int kStages = 4;
 constexpr int kThreads = 192;
 constexpr int kTmemCols = 512;
 constexpr uint64_t kWaitLimitNs = 2000000000ull;  // 2 s: far above any legitimate wait
@@ -41,6 +40,9 @@ struct Cfg {
     static constexpr int kSfaBytes = 2048;                  // 128 rows x 16 blocks
     static constexpr int kSfbBytes = 2048 * kNG;
     static constexpr int kStageBytes = kABytes + kBBytes + kSfaBytes + kSfbBytes;
+    // ring depth: as many stages as fit in shared memory (the bytes in flight per SM are what keeps HBM busy when
+    // few CTAs stream a long K)
+    static constexpr int kStages = (BN == 128) ? 6 : 4;
     static constexpr int kSmemBytes = kStages * kStageBytes + 1024 /*align*/ + 256 /*barriers*/;
     // scale factors sit behind the accumulators, in two sets used by alternate K tiles so that the
     // copies for the next K tile do not have to wait for the MMAs still reading the current set
@@ -201,20 +203,20 @@ gemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant__ 
     const uint32_t base = (raw_addr + 1023u) & ~1023u;
     uint8_t* aligned = smem_raw + (base - raw_addr);
     // ring: [stage][A | B | SFA | SFB]; then barriers
-    uint64_t* bars = reinterpret_cast<uint64_t*>(aligned + kStages * C::kStageBytes);
+    uint64_t* bars = reinterpret_cast<uint64_t*>(aligned + C::kStages * C::kStageBytes);
     const uint32_t bar_base = smem_u32(bars);
     auto full_bar = [&](int s) { return bar_base + 8u * s; };
-    auto empty_bar = [&](int s) { return bar_base + 8u * (kStages + s); };
-    auto tfull_bar = [&](int a) { return bar_base + 8u * (2 * kStages + a); };
-    auto tempty_bar = [&](int a) { return bar_base + 8u * (2 * kStages + 2 + a); };
-    volatile uint32_t* tmem_slot = reinterpret_cast<volatile uint32_t*>(bars + 2 * kStages + 4);
+    auto empty_bar = [&](int s) { return bar_base + 8u * (C::kStages + s); };
+    auto tfull_bar = [&](int a) { return bar_base + 8u * (2 * C::kStages + a); };
+    auto tempty_bar = [&](int a) { return bar_base + 8u * (2 * C::kStages + 2 + a); };
+    volatile uint32_t* tmem_slot = reinterpret_cast<volatile uint32_t*>(bars + 2 * C::kStages + 4);
     volatile uint32_t* abort_flag = tmem_slot + 1;
 
     const int warp = __shfl_sync(0xffffffffu, threadIdx.x >> 5, 0);
     const int lane = threadIdx.x & 31;
 
     if (threadIdx.x == 0) {
-        for (int s = 0; s < kStages; ++s) {
+        for (int s = 0; s < C::kStages; ++s) {
             mbar_init(full_bar(s), 1);
             mbar_init(empty_bar(s), 1);
         }
@@ -288,7 +290,7 @@ gemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant__ 
                     }
                     }
                     __syncwarp();
-                    if (++stage == kStages) {
+                    if (++stage == C::kStages) {
                         stage = 0;
                         phase ^= 1u;
                     }
@@ -353,7 +355,7 @@ gemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant__ 
                     }
                     if (issuer) tc_commit(empty_bar(stage));  // slot reusable once these MMAs have read it
                     __syncwarp();
-                    if (++stage == kStages) {
+                    if (++stage == C::kStages) {
                         stage = 0;
                         phase ^= 1u;
                     }
@@ -871,10 +873,324 @@ static int launch_pair(const uint8_t* a, const uint8_t* b, const GemmParams& p, 
 
 }  // namespace pair
 
+// =============================================================================================
+// Skinny variant for decode-sized batches (M <= 64).  The roles of the operands are swapped: the 128 rows of
+// the MMA are WEIGHT rows and its N dimension is the (padded) token count BT = 16 / 32 / 64, so the tensor
+// cores spend BT/128 of the time a 128-row token tile of mostly padding would take and the kernel is a
+// stream of the weights.  One CTA owns 128 weight rows and one K range; the K ranges of a tile are the CTAs
+// of one thread-block cluster (1..8), which lets a shape with few weight tiles still pull from every SM.
+// The partial accumulators of ranks 1.. are written into rank 0's shared memory (st.shared::cluster) and
+// rank 0 adds them in ascending rank order, applies alpha and stores bf16: one kernel, no workspace, and
+// the result does not depend on timing.  Every TMA copy has one destination CTA (no multicast).
+// =============================================================================================
+namespace skinny {
+
+using pair::cluster_ctarank;
+using pair::cluster_sync_all;
+using pair::map_to_cta;
+
+constexpr int kMaxStages = 8;
+// TMEM: accumulator in columns 0..BT-1, then two scale sets of 32 columns
+
+template <int BT>
+struct SkinnyCfg {
+    static constexpr int kWBytes = 128 * kBKBytes;     // 128 weight rows x 256 codes
+    static constexpr int kXBytes = BT * kBKBytes;      // BT token rows x 256 codes
+    static constexpr int kSfBytes = 2048;              // one 128-row scale group x 16 blocks, for each operand
+    static constexpr int kStageBytes = kWBytes + kXBytes + 2 * kSfBytes;
+    static constexpr int kSfCol = BT <= 64 ? 64 : 128; // scale set 0: weights +0..15, tokens +16..31; set 1: +32
+    static constexpr int kTmemCols = BT <= 64 ? 128 : 256;
+    static constexpr int kMaxStages = (BT <= 64) ? 8 : 6;
+    static_assert(kStageBytes % 1024 == 0, "stage alignment for the 128-byte swizzle");
+    static_assert(BT % 16 == 0 && BT >= 16 && BT <= 128, "token tile");
+};
+
+__device__ __forceinline__ void tc_ld_32x32b_x16(uint32_t taddr, uint32_t v[16]) {
+    asm volatile(
+        "tcgen05.ld.sync.aligned.32x32b.x16.b32 "
+        "{%0, %1, %2, %3, %4, %5, %6, %7, %8, %9, %10, %11, %12, %13, %14, %15}, [%16];"
+        : "=r"(v[0]), "=r"(v[1]), "=r"(v[2]), "=r"(v[3]), "=r"(v[4]), "=r"(v[5]), "=r"(v[6]), "=r"(v[7]), "=r"(v[8]),
+          "=r"(v[9]), "=r"(v[10]), "=r"(v[11]), "=r"(v[12]), "=r"(v[13]), "=r"(v[14]), "=r"(v[15])
+        : "r"(taddr)
+        : "memory");
+}
+__device__ __forceinline__ void st_cluster_f32(uint32_t cluster_addr, float v) {
+    asm volatile("st.shared::cluster.f32 [%0], %1;" ::"r"(cluster_addr), "f"(v) : "memory");
+}
+
+struct SkinnyParams {
+    const uint8_t* sfx;   // token scales (group 0 of the tiled layout)
+    const uint8_t* sfw;   // weight scales
+    const float* alpha;
+    __nv_bfloat16* out;   // [M, N]
+    int M, N, K;
+    int64_t sf_group_stride;
+    int k_tiles_per_rank;
+    int stages;
+};
+
+template <int BT>
+__global__ void __launch_bounds__(kThreads)
+skinny_kernel(const __grid_constant__ CUtensorMap tmap_w, const __grid_constant__ CUtensorMap tmap_x, const SkinnyParams p) {
+    using C = SkinnyCfg<BT>;
+    extern __shared__ uint8_t smem_raw[];
+    const uint32_t raw_addr = smem_u32(smem_raw);
+    const uint32_t base = (raw_addr + 1023u) & ~1023u;
+    uint8_t* aligned = smem_raw + (base - raw_addr);
+    const int nstages = p.stages;
+    uint64_t* bars = reinterpret_cast<uint64_t*>(aligned + nstages * C::kStageBytes);
+    const uint32_t bar_base = smem_u32(bars);
+    auto full_bar = [&](int s) { return bar_base + 8u * s; };
+    auto empty_bar = [&](int s) { return bar_base + 8u * (kMaxStages + s); };
+    const uint32_t tfull_bar = bar_base + 8u * (2 * kMaxStages);
+    volatile uint32_t* tmem_slot = reinterpret_cast<volatile uint32_t*>(bars + 2 * kMaxStages + 1);
+    volatile uint32_t* abort_flag = tmem_slot + 1;
+
+    const int warp = __shfl_sync(0xffffffffu, threadIdx.x >> 5, 0);
+    const int lane = threadIdx.x & 31;
+    const uint32_t rank = cluster_ctarank();
+    uint32_t ranks;
+    asm volatile("mov.u32 %0, %%cluster_nctarank;" : "=r"(ranks));
+    const int nt = blockIdx.x / ranks;                  // 128-row weight tile (clusters run along x)
+
+    if (threadIdx.x == 0) {
+        for (int s = 0; s < nstages; ++s) {
+            mbar_init(full_bar(s), 1);
+            mbar_init(empty_bar(s), 1);
+        }
+        mbar_init(tfull_bar, 1);
+        *abort_flag = 0;
+        asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+        asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
+    }
+    if (warp == 1) {
+        asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(
+                         smem_u32(const_cast<uint32_t*>(tmem_slot))),
+                     "r"(C::kTmemCols)
+                     : "memory");
+        asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;" ::: "memory");
+    }
+    tc_fence_before();
+    __syncthreads();
+    tc_fence_after();
+    const uint32_t tmem_base = *tmem_slot;
+
+    const int k_tiles = (p.K + kBK - 1) / kBK;
+    const int kt_begin = static_cast<int>(rank) * p.k_tiles_per_rank;
+    const int kcount = max(0, min(k_tiles, kt_begin + p.k_tiles_per_rank) - kt_begin);   // host: never 0
+
+    if (warp == 0) {
+        // ------------------------------------------------------------------ producer
+        const bool issuer = elect_one();
+        if (issuer) {
+            asm volatile("prefetch.tensormap [%0];" ::"l"(&tmap_w) : "memory");
+            asm volatile("prefetch.tensormap [%0];" ::"l"(&tmap_x) : "memory");
+        }
+        int stage = 0;
+        uint32_t phase = 0;
+        for (int i = 0; i < kcount; ++i) {
+            const int kt = kt_begin + i;
+            if (!mbar_wait_warp(empty_bar(stage), phase ^ 1u, abort_flag, (7u << 24) | kt)) break;
+            const int kb_count = min(4, (p.K - kt * kBK + 63) / 64);
+            const uint32_t sf_bytes = 512u * kb_count;
+            const uint32_t sbase = base + stage * C::kStageBytes;
+            if (issuer) {
+                mbar_expect_tx(full_bar(stage), C::kWBytes + C::kXBytes + 2 * sf_bytes);
+                tma_load_2d(sbase, &tmap_w, kt * kBKBytes, nt * 128, full_bar(stage));
+                tma_load_2d(sbase + C::kWBytes, &tmap_x, kt * kBKBytes, 0, full_bar(stage));
+                bulk_load_1d(sbase + C::kWBytes + C::kXBytes,
+                             p.sfw + static_cast<int64_t>(nt) * p.sf_group_stride + static_cast<int64_t>(kt) * 2048, sf_bytes,
+                             full_bar(stage));
+                bulk_load_1d(sbase + C::kWBytes + C::kXBytes + C::kSfBytes, p.sfx + static_cast<int64_t>(kt) * 2048, sf_bytes,
+                             full_bar(stage));
+            }
+            __syncwarp();
+            if (++stage == nstages) {
+                stage = 0;
+                phase ^= 1u;
+            }
+        }
+    } else if (warp == 1) {
+        // ------------------------------------------------------------------ MMA issuer
+        const bool issuer = elect_one();
+        constexpr uint32_t idesc = instr_desc<BT>();
+        int stage = 0;
+        uint32_t phase = 0;
+        bool ok = true;
+        for (int i = 0; i < kcount; ++i) {
+            if (!(ok = mbar_wait_warp(full_bar(stage), phase, abort_flag, (8u << 24) | i))) break;
+            tc_fence_after();
+            const int kb_count = min(4, (p.K - (kt_begin + i) * kBK + 63) / 64);
+            const uint32_t sbase = base + stage * C::kStageBytes;
+            const uint32_t w_lo = ((sbase & 0x3ffffu) >> 4) | (1u << 16);
+            const uint32_t x_lo = w_lo + (C::kWBytes >> 4);
+            const uint32_t sfw_lo = ((sbase + C::kWBytes + C::kXBytes) & 0x3ffffu) >> 4;
+            const uint32_t sfx_lo = sfw_lo + (C::kSfBytes >> 4);
+            const uint32_t sfw_t = tmem_base + C::kSfCol + (i & 1) * 32;
+            const uint32_t sfx_t = sfw_t + 16;
+            if (issuer) {
+                for (int kb = 0; kb < kb_count; ++kb) {
+                    tc_cp_lohi(sfw_t + 4 * kb, sfw_lo + 32 * kb);
+                    tc_cp_lohi(sfx_t + 4 * kb, sfx_lo + 32 * kb);
+                }
+                for (int kb = 0; kb < kb_count; ++kb)
+                    tc_mma_lohi(tmem_base, w_lo + 2 * kb, x_lo + 2 * kb, idesc, sfw_t + 4 * kb, sfx_t + 4 * kb,
+                                (i > 0 || kb > 0) ? 1u : 0u);
+                tc_commit(empty_bar(stage));
+            }
+            __syncwarp();
+            if (++stage == nstages) {
+                stage = 0;
+                phase ^= 1u;
+            }
+        }
+        if (ok && issuer) tc_commit(tfull_bar);
+        __syncwarp();
+    }
+
+    // ---------------------------------------------------------------------- epilogue
+    // Thread (sub-partition sp, lane) of warps 2..5 owns weight row nt*128 + 32*sp + lane; TMEM column m of its
+    // lane is the partial sum for token m.  Columns are handled 16 at a time to keep the register count low.
+    const int sp = warp & 3;
+    const int n_local = sp * 32 + lane;
+    bool have = false;
+    if (warp >= 2) {
+        bool ok = mbar_wait(tfull_bar, 0, abort_flag, (9u << 24) | nt);
+        have = __shfl_sync(0xffffffffu, ok ? 1 : 0, 0) != 0;
+        if (have) tc_fence_after();
+    }
+    const uint32_t t_lane = tmem_base + (static_cast<uint32_t>(sp * 32) << 16);
+    if (ranks > 1) {
+        // rank 0's ring is idle once its accumulator is complete (all its copies landed and were consumed);
+        // the first cluster barrier tells the other ranks so, the second that their partials have arrived.
+        cluster_sync_all();
+        if (warp >= 2 && rank > 0 && have) {
+            const uint32_t dst0 = map_to_cta(base, 0) + ((rank - 1) * BT * 128 + n_local) * 4;
+#pragma unroll 1
+            for (int c = 0; c < BT / 16 && c * 16 < p.M; ++c) {
+                uint32_t v[16];
+                tc_ld_32x32b_x16(t_lane + c * 16, v);
+                tc_ld_wait();
+#pragma unroll
+                for (int e = 0; e < 16; ++e)
+                    if (c * 16 + e < p.M) st_cluster_f32(dst0 + (c * 16 + e) * 512, __uint_as_float(v[e]));
+            }
+        }
+        cluster_sync_all();
+    }
+    if (warp >= 2 && rank == 0 && have) {
+        const float alpha = __ldg(p.alpha);
+        const float* staged = reinterpret_cast<const float*>(aligned);
+        const int n = nt * 128 + n_local;
+#pragma unroll 1
+        for (int c = 0; c < BT / 16 && c * 16 < p.M; ++c) {
+            uint32_t v[16];
+            tc_ld_32x32b_x16(t_lane + c * 16, v);
+            tc_ld_wait();
+            float acc[16];
+#pragma unroll
+            for (int e = 0; e < 16; ++e) acc[e] = __uint_as_float(v[e]);
+            for (uint32_t r = 1; r < ranks; ++r)
+#pragma unroll
+                for (int e = 0; e < 16; ++e)
+                    if (c * 16 + e < p.M) acc[e] = __fadd_rn(acc[e], staged[((r - 1) * BT + c * 16 + e) * 128 + n_local]);
+            if (n < p.N) {
+#pragma unroll
+                for (int e = 0; e < 16; ++e)
+                    if (c * 16 + e < p.M)
+                        p.out[static_cast<int64_t>(c * 16 + e) * p.N + n] = __float2bfloat16_rn(__fmul_rn(acc[e], alpha));
+            }
+        }
+    }
+
+    // ---------------------------------------------------------------------- teardown
+    if (*abort_flag) {
+        const uint64_t t0 = global_timer_ns();
+        while (global_timer_ns() - t0 < 200000ull) __nanosleep(1000);
+    }
+    tc_fence_before();
+    __syncthreads();
+    if (warp == 1) {
+        tc_fence_after();
+        asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(tmem_base), "r"(C::kTmemCols) : "memory");
+    }
+}
+
+// K ranges per weight tile: the largest power of two that keeps every CTA of the grid resident at once (one per
+// SM), with at least two K stages each, at most 8 (the portable cluster size) and at most 64 / token tile.  Cluster sizes that are not a
+// power of two measured slower on B200 (6144 x 4096: 3 ranges 11.9 us, 2 ranges 8.0 us).
+static int choose_ranks(int n_tiles, int k_tiles, int sms, int forced, int bt) {
+    int r = 1;
+    if (forced > 0) {
+        r = forced;
+    } else {
+        // the reduction in rank 0 costs ranks x tokens; beyond 64 of those it ate the gain of the extra SMs
+        const int cap = bt >= 64 ? 1 : 64 / bt;
+        while (r < 8 && 2 * r <= cap && n_tiles * (2 * r) <= sms) r *= 2;
+    }
+    if (r > 8) r = 8;
+    while (r > 1 && r > k_tiles / 2) --r;
+    return r;
+}
+
+template <int BT>
+static int launch_skinny(const uint8_t* x, const uint8_t* w, const GemmParams& g, int forced_ranks, cudaStream_t stream) {
+    using C = SkinnyCfg<BT>;
+    CUtensorMap mw, mx;
+    int st = make_operand_map(&mw, w, g.N, g.K / 2, 128);
+    if (st == NVFP4_OK) st = make_operand_map(&mx, x, g.M, g.K / 2, BT);
+    if (st != NVFP4_OK) return st;
+    int dev = 0, sms = 148;
+    cudaGetDevice(&dev);
+    cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev);
+    const int n_tiles = (g.N + 127) / 128;
+    const int k_tiles = (g.K + kBK - 1) / kBK;
+    int ranks = choose_ranks(n_tiles, k_tiles, sms, forced_ranks, BT);
+    while (ranks > 1 && (ranks - 1) * BT * 512 > C::kMaxStages * C::kStageBytes) --ranks;   // partials must fit in rank 0's ring
+    SkinnyParams p;
+    p.sfx = g.sfa;
+    p.sfw = g.sfb;
+    p.alpha = g.alpha;
+    p.out = g.out;
+    p.M = g.M;
+    p.N = g.N;
+    p.K = g.K;
+    p.sf_group_stride = g.sf_group_stride;
+    p.k_tiles_per_rank = (k_tiles + ranks - 1) / ranks;
+    ranks = (k_tiles + p.k_tiles_per_rank - 1) / p.k_tiles_per_rank;   // no empty range
+    // one CTA per SM with a deep ring when the whole grid is resident at once, else two CTAs per SM
+    p.stages = (n_tiles * ranks <= sms) ? C::kMaxStages : 4;
+    if (p.stages > p.k_tiles_per_rank) p.stages = p.k_tiles_per_rank < 2 ? 2 : p.k_tiles_per_rank;
+    while ((ranks - 1) * BT * 512 > p.stages * C::kStageBytes) ++p.stages;   // room for the partials
+    if (p.stages > C::kMaxStages) return NVFP4_ERR_UNSUPPORTED;
+    const int smem = p.stages * C::kStageBytes + 1024 + 256;
+    cudaError_t e = cudaFuncSetAttribute(skinny_kernel<BT>, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                                         C::kMaxStages * C::kStageBytes + 1024 + 256);
+    if (e != cudaSuccess) return static_cast<int>(e);
+    cudaLaunchConfig_t cfg = {};
+    cfg.gridDim = dim3(n_tiles * ranks, 1, 1);
+    cfg.blockDim = dim3(kThreads, 1, 1);
+    cfg.dynamicSmemBytes = smem;
+    cfg.stream = stream;
+    cudaLaunchAttribute attr[1];
+    attr[0].id = cudaLaunchAttributeClusterDimension;
+    attr[0].val.clusterDim.x = ranks;
+    attr[0].val.clusterDim.y = 1;
+    attr[0].val.clusterDim.z = 1;
+    cfg.attrs = attr;
+    cfg.numAttrs = 1;
+    e = cudaLaunchKernelEx(&cfg, skinny_kernel<BT>, mw, mx, p);
+    return static_cast<int>(e);
+}
+
+}  // namespace skinny
+
 }  // namespace gemm
 }  // namespace nvfp4
 
 static int g_gemm_force_path = 0;
+constexpr int64_t kSkinnyMaxM = 128;   // what the skinny kernel accepts
+constexpr int64_t kSkinnyAutoM = 32;   // what it is chosen for by default
 static int g_gemm_force_splits = 0;    // 0 = by shape
 static int g_gemm_force_rotate = -1;   // -1 = by shape
 static int g_gemm_raster_group = 0;    // 0 = default
@@ -910,9 +1226,10 @@ extern "C" int nvfp4_gemm_tune(int k_splits, int k_rotate) {
 }
 
 // Testing hook: 0 = choose the kernel by shape, 1 = 128x128 tiles, 2 = 128x256 tiles, 3 = CTA-pair 256x256 tiles,
-// 4 = CTA-pair 256x192 tiles with two accumulators.
+// 4 = CTA-pair 256x192 tiles with two accumulators, 5 = skinny kernel (M <= 64; nvfp4_gemm_tune's k_splits then sets its K ranges per weight tile; larger M falls
+// back to the choice by shape).
 extern "C" int nvfp4_gemm_force_path(int path) {
-    if (path < 0 || path > 4) return NVFP4_ERR_BAD_ENUM;
+    if (path < 0 || path > 5) return NVFP4_ERR_BAD_ENUM;
     g_gemm_force_path = path;
     return NVFP4_OK;
 }
@@ -949,16 +1266,26 @@ extern "C" int nvfp4_gemm_launch(const uint8_t* a, const uint8_t* b, const uint8
     p.partial = static_cast<float*>(workspace);
     // default: one band over all m-tiles (band sizes 1..16 measured within noise of it on B200)
     p.raster_group = g_gemm_raster_group > 0 ? g_gemm_raster_group : (1 << 20);
+    cudaStream_t s = static_cast<cudaStream_t>(stream);
+    // Decode-sized batches: weight rows on the MMA's 128 rows, tokens on its N dimension, K ranges across a cluster.
+    // Measured on B200 against the other kernels with the weights streaming from HBM: faster up to 32 tokens.
+    if ((g_gemm_force_path == 5 && M <= kSkinnyMaxM) ||
+        (g_gemm_force_path == 0 && g_gemm_force_splits == 0 && M <= kSkinnyAutoM)) {
+        const int forced = g_gemm_force_path == 5 ? g_gemm_force_splits : 0;
+        if (M <= 16) return gemm::skinny::launch_skinny<16>(a, b, p, forced, s);
+        if (M <= 32) return gemm::skinny::launch_skinny<32>(a, b, p, forced, s);
+        if (M <= 64) return gemm::skinny::launch_skinny<64>(a, b, p, forced, s);
+        return gemm::skinny::launch_skinny<128>(a, b, p, forced, s);
+    }
     if (p.k_splits > 1) {
         const size_t need = static_cast<size_t>(p.k_splits) * static_cast<size_t>(M) * static_cast<size_t>(N) * sizeof(float);
         if (!workspace || workspace_bytes < need) return NVFP4_ERR_WORKSPACE;
         if (reinterpret_cast<uintptr_t>(workspace) & 15) return NVFP4_ERR_MISALIGNED;
     }
-    cudaStream_t s = static_cast<cudaStream_t>(stream);
     // Kernel choice by a small cost model fitted to measurements on B200: time ~ waves x cost of one tile, where a
     // wave is 148 single-CTA tiles or 74 CTA-pair tiles.  Relative tile costs: 128x128 -> 0.7, 128x256 -> 1.0,
     // pair 256x192 -> 0.68 (0.75 of the MMA work per SM, and its epilogue overlaps the next tile).
-    int path = g_gemm_force_path;   // 0 = choose by shape
+    int path = g_gemm_force_path >= 5 ? 0 : g_gemm_force_path;   // 0 = choose by shape
     if (path == 0) {
         const int64_t mt = (M + 127) / 128;
         const double c1 = static_cast<double>((mt * ((N + 127) / 128) + 147) / 148) * 0.7;

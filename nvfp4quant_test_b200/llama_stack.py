@@ -67,9 +67,22 @@ def quantize_layer(weights: dict[str, torch.Tensor], importance: dict[int, torch
     return {name: quantize_weight(w, importance[w.shape[1]]) for name, w in weights.items()}
 
 
-def layer_gemms(qlayer: dict, acts: dict[int, torch.Tensor], act_importance: dict[str, torch.Tensor]):
+def stack_weight_scales(qlayer: dict) -> dict[int, tuple[torch.Tensor, dict[str, int]]]:
+    """{K: (fp32 vector of the global scales of the layer's matrices with K input features, {name: slot})}.
+    Built once per layer so that a forward pass needs one multiplication per input width for all its alphas."""
+    by_k: dict[int, list[str]] = {}
+    for name, (codes, _, _) in qlayer.items():
+        by_k.setdefault(codes.shape[1] * 2, []).append(name)
+    return {k: (torch.stack([qlayer[n][2].reshape(()).float() for n in names]), {n: i for i, n in enumerate(names)})
+            for k, names in by_k.items()}
+
+
+def layer_gemms(qlayer: dict, acts: dict[int, torch.Tensor], act_importance: dict[str, torch.Tensor],
+                weight_scales: dict | None = None):
     """y = x @ W.T for every matrix of the layer with NVFP4 operands; activations quantized with the unweighted sweep
     unless an importance vector for them is given.  Returns {name: bf16 [tokens, N]}."""
+    if weight_scales is None:
+        weight_scales = stack_weight_scales(qlayer)
     out = {}
     qact: dict[int, tuple] = {}
     for name, (codes, scales, gs_w) in qlayer.items():
@@ -82,10 +95,10 @@ def layer_gemms(qlayer: dict, acts: dict[int, torch.Tensor], act_importance: dic
                 qa, sa = K.scalesweep_mse_nvfp4_quant_impl(x, gs_x_inv)
             else:
                 qa, sa = K.scalesweep_weighted_mse_nvfp4_quant_impl(x, imp, gs_x_inv)
-            qact[k] = (qa, sa, gs_x)
-        qa, sa, gs_x = qact[k]
-        alpha = (gs_x * gs_w).reshape(1).float()
-        out[name] = K.nvfp4_scaled_mm(qa, codes, sa, scales, alpha, torch.bfloat16)
+            qact[k] = (qa, sa, gs_x.float() * weight_scales[k][0])      # alphas of every matrix fed by this input
+        qa, sa, alphas = qact[k]
+        slot = weight_scales[k][1][name]
+        out[name] = K.nvfp4_scaled_mm(qa, codes, sa, scales, alphas[slot:slot + 1], torch.bfloat16)
     return out
 
 
@@ -127,6 +140,7 @@ def run(n_layers: int, token_batches: list[int], seed: int = 0, use_graph: bool 
     qlayers = [quantize_layer(w, importance) for w in layers]
     e1.record()
     sync()
+    wscales = [stack_weight_scales(q) for q in qlayers]
     quant_ms = max_ms(e0.elapsed_time(e1))
     n_weights = n_layers * weights_per_layer()
     result = {
@@ -139,8 +153,8 @@ def run(n_layers: int, token_batches: list[int], seed: int = 0, use_graph: bool 
         gen.manual_seed(seed + 1000 + tokens)
         acts = {k: torch.normal(0.0, 1.0, size=(tokens, k), generator=gen, device=dev, dtype=torch.bfloat16)
                 for k in calib}
-        for q in qlayers[:1]:
-            layer_gemms(q, acts, {})
+        for q, ws in zip(qlayers[:1], wscales):
+            layer_gemms(q, acts, {}, ws)
         sync()
         graph = None
         if use_graph and qlayers:
@@ -148,16 +162,16 @@ def run(n_layers: int, token_batches: list[int], seed: int = 0, use_graph: bool 
             # records into one CUDA graph; replaying it removes the per-launch host cost that dominates small batches
             graph = torch.cuda.CUDAGraph()
             with torch.cuda.graph(graph):
-                for q in qlayers:
-                    layer_gemms(q, acts, {})
+                for q, ws in zip(qlayers, wscales):
+                    layer_gemms(q, acts, {}, ws)
             graph.replay()
             sync()
         e0.record()
         if graph is not None:
             graph.replay()
         else:
-            for q in qlayers:
-                layer_gemms(q, acts, {})
+            for q, ws in zip(qlayers, wscales):
+                layer_gemms(q, acts, {}, ws)
         e1.record()
         sync()
         ms = max_ms(e0.elapsed_time(e1))

@@ -57,7 +57,7 @@ def test_gemm_matches_fp64_oracle(cuda_lib, oracle, M, N, K_):
 @pytest.mark.parametrize("M,N,K_", [(128, 256, 256), (300, 520, 320), (1, 512, 1024), (512, 768, 1024), (257, 1000, 192),
                                     (1024, 2048, 4096)])
 def test_gemm_kernel_paths_agree(cuda_lib, oracle, M, N, K_):
-    """128x128, 128x256 and CTA-pair 256x256 kernels must give the same bf16 bits (fp32 accumulation in
+    """128x128, 128x256 and CTA-pair kernels must give the same bf16 bits (fp32 accumulation in
     the same K order) and each must satisfy the oracle tolerance."""
     import nvfp4quant_test_b200.kernels as K
     from nvfp4quant_test_b200.kernels.kernel_gemm import gemm_last_status
@@ -251,3 +251,55 @@ def test_config4_gemm_shapes(cuda_lib, N):
         tol = np.maximum(np.abs(ref) * 2.0 ** -7, np.abs(ref).max() * 2.0 ** -16)
         assert (np.abs(got - ref) <= tol).all(), (M, N, float(np.abs(got - ref).max()))
         del out
+
+
+@pytest.mark.parametrize("M,N,K_,ranks", [(1, 512, 1024, 0), (1, 512, 1024, 2), (2, 130, 64, 0), (5, 1000, 2304, 3),
+                                          (16, 8192, 8192, 0), (16, 8192, 8192, 8), (17, 264, 320, 2), (32, 4096, 4096, 0),
+                                          (33, 520, 1280, 4), (64, 1024, 8192, 4), (4, 96, 24576, 8), (65, 264, 2304, 2),
+                                          (128, 1000, 4096, 3)])
+def test_gemm_skinny_kernel(cuda_lib, oracle, M, N, K_, ranks):
+    """The decode-sized kernel (weight rows on the MMA's 128 rows, token tile 16..128, K ranges spread over a
+    thread-block cluster and reduced in rank 0's shared memory), with the number of ranges chosen by shape
+    (0) or forced.  Oracle tolerance; with one range the bits must equal the 128x128 kernel's."""
+    import nvfp4quant_test_b200.kernels as K
+    from nvfp4quant_test_b200.kernels.kernel_gemm import gemm_last_status
+
+    a, b = C.gemm_operands(M, N, K_, 40 + M)
+    qa, sa, gsa = _quantize(a.cuda())
+    qb, sb, gsb = _quantize(b.cuda())
+    alpha = (gsa * gsb).reshape(1).float()
+    outs = {}
+    try:
+        for path, r in ((1, 0), (5, ranks), (5, 1)):
+            assert cuda_lib.nvfp4_gemm_force_path(path) == 0
+            assert cuda_lib.nvfp4_gemm_tune(r, -1) == 0
+            out = torch.full((M, N), float("nan"), dtype=torch.bfloat16, device="cuda")
+            K.nvfp4_scaled_mm(qa, qb, sa, sb, alpha, torch.bfloat16, out=out)
+            assert gemm_last_status() == 0, f"path {path} ranks {r}"
+            outs[(path, r)] = out
+    finally:
+        cuda_lib.nvfp4_gemm_force_path(0)
+        cuda_lib.nvfp4_gemm_tune(0, -1)
+    ref = oracle.gemm(qa.cpu().numpy(), qb.cpu().numpy(), sa.view(torch.uint8).cpu().numpy().reshape(-1),
+                      sb.view(torch.uint8).cpu().numpy().reshape(-1), float(alpha))
+    for out in outs.values():
+        _check(out, ref)
+    assert torch.equal(outs[(1, 0)], outs[(5, 1)])
+
+
+def test_gemm_skinny_is_default_for_decode_batches(cuda_lib):
+    """Shapes with M <= 32 take the skinny kernel when nothing is forced: same bits as forcing it."""
+    import nvfp4quant_test_b200.kernels as K
+
+    M, N, K_ = 8, 768, 2048
+    a, b = C.gemm_operands(M, N, K_, 77)
+    qa, sa, gsa = _quantize(a.cuda())
+    qb, sb, gsb = _quantize(b.cuda())
+    alpha = (gsa * gsb).reshape(1).float()
+    auto = K.nvfp4_scaled_mm(qa, qb, sa, sb, alpha, torch.bfloat16)
+    try:
+        assert cuda_lib.nvfp4_gemm_force_path(5) == 0
+        forced = K.nvfp4_scaled_mm(qa, qb, sa, sb, alpha, torch.bfloat16)
+    finally:
+        cuda_lib.nvfp4_gemm_force_path(0)
+    assert torch.equal(auto, forced)
