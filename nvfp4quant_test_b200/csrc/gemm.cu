@@ -33,8 +33,8 @@ __device__ uint32_t g_gemm_status;  // 0 = ok; else (role << 24) | detail of the
 
 template <int BN>
 struct Cfg {
-    static constexpr int kNG = BN / 128;                    // 128-row scale groups per B tile
-    static constexpr int kAcc = (BN == 128) ? 2 : 1;        // accumulator buffers in TMEM
+    static constexpr int kNG = (BN + 127) / 128;            // 128-row scale groups a B tile touches (a 64-row tile: half of one)
+    static constexpr int kAcc = (BN <= 128) ? 2 : 1;        // accumulator buffers in TMEM
     static constexpr int kABytes = kBM * kBKBytes;          // 16 KiB
     static constexpr int kBBytes = BN * kBKBytes;
     static constexpr int kSfaBytes = 2048;                  // 128 rows x 16 blocks
@@ -42,7 +42,7 @@ struct Cfg {
     static constexpr int kStageBytes = kABytes + kBBytes + kSfaBytes + kSfbBytes;
     // ring depth: as many stages as fit in shared memory (the bytes in flight per SM are what keeps HBM busy when
     // few CTAs stream a long K)
-    static constexpr int kStages = (BN == 128) ? 6 : 4;
+    static constexpr int kStages = (BN == 64) ? 8 : (BN == 128) ? 6 : 4;
     static constexpr int kSmemBytes = kStages * kStageBytes + 1024 /*align*/ + 256 /*barriers*/;
     // scale factors sit behind the accumulators, in two sets used by alternate K tiles so that the
     // copies for the next K tile do not have to wait for the MMAs still reading the current set
@@ -270,7 +270,8 @@ gemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant__ 
                     const int kb_count = min(4, (p.K - kt * kBK + 63) / 64);  // 64-element K blocks in this stage
                     const uint32_t sf_bytes = 512u * kb_count;
                     int sfb_present = 0;
-                    for (int g = 0; g < C::kNG; ++g) sfb_present += (nt * C::kNG + g < p.sfb_groups) ? 1 : 0;
+                    const int grp0 = BN == 64 ? (nt >> 1) : nt * C::kNG;   // first 128-row scale group of this B tile
+                    for (int g = 0; g < C::kNG; ++g) sfb_present += (grp0 + g < p.sfb_groups) ? 1 : 0;
                     const uint32_t tx = C::kABytes + C::kBBytes + sf_bytes * (1 + sfb_present);
                     const uint32_t sbase = base + stage * C::kStageBytes;
                     if (issuer) {
@@ -281,7 +282,7 @@ gemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant__ 
                                  p.sfa + static_cast<int64_t>(mt) * p.sf_group_stride + static_cast<int64_t>(kt) * 2048,
                                  sf_bytes, full_bar(stage));
                     for (int g = 0; g < C::kNG; ++g) {
-                        const int grp = nt * C::kNG + g;
+                        const int grp = grp0 + g;
                         if (grp < p.sfb_groups)
                             bulk_load_1d(sbase + C::kABytes + C::kBBytes + C::kSfaBytes + g * 2048,
                                          p.sfb + static_cast<int64_t>(grp) * p.sf_group_stride +
@@ -312,6 +313,13 @@ gemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant__ 
                 tc_fence_after();
                 const uint32_t d_tmem = tmem_base + acc * BN;
                 const int ks = tile / mn_tiles, t2 = tile - ks * mn_tiles;
+                // a 64-row B tile is one half of a 128-row scale group: rows 64..127 sit two TMEM columns further on
+                uint32_t sfb_half = 0;
+                if (BN == 64) {
+                    int mt, nt;
+                    tile_to_mn(t2, m_tiles, n_tiles, p.raster_group, mt, nt);
+                    sfb_half = 2u * (nt & 1);
+                }
                 const int kt_begin = ks * p.k_tiles_per_split;
                 const int kcount = min(k_tiles, kt_begin + p.k_tiles_per_split) - kt_begin;
                 const int rot = p.k_rotate ? (t2 * 5) % kcount : 0;
@@ -328,6 +336,7 @@ gemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant__ 
                     const uint32_t set = (i & 1) * C::kSfSetCols;
                     const uint32_t sfa_t = tmem_base + C::kSfaCol + set;
                     const uint32_t sfb_t = tmem_base + C::kSfbCol + set;
+                    const uint32_t sfb_use = sfb_t + sfb_half;
                     const uint32_t first = i > 0 ? 1u : 0u;
                     if (!issuer) {
                         // nothing to issue on this lane
@@ -341,7 +350,7 @@ gemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant__ 
                         }
 #pragma unroll
                         for (int kb = 0; kb < 4; ++kb)   // 32 bytes of K per instruction: start address + 2 (x16 B)
-                            tc_mma_lohi(d_tmem, a_lo + 2 * kb, b_lo + 2 * kb, idesc, sfa_t + 4 * kb, sfb_t + 4 * C::kNG * kb,
+                            tc_mma_lohi(d_tmem, a_lo + 2 * kb, b_lo + 2 * kb, idesc, sfa_t + 4 * kb, sfb_use + 4 * C::kNG * kb,
                                         kb == 0 ? first : 1u);
                     } else {
                         for (int kb = 0; kb < kb_count; ++kb) {
@@ -350,7 +359,7 @@ gemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant__ 
                                 tc_cp_lohi(sfb_t + 4 * C::kNG * kb + 4 * g, sfb_lo + 128 * g + 32 * kb);
                         }
                         for (int kb = 0; kb < kb_count; ++kb)
-                            tc_mma_lohi(d_tmem, a_lo + 2 * kb, b_lo + 2 * kb, idesc, sfa_t + 4 * kb, sfb_t + 4 * C::kNG * kb,
+                            tc_mma_lohi(d_tmem, a_lo + 2 * kb, b_lo + 2 * kb, idesc, sfa_t + 4 * kb, sfb_use + 4 * C::kNG * kb,
                                         kb == 0 ? first : 1u);
                     }
                     if (issuer) tc_commit(empty_bar(stage));  // slot reusable once these MMAs have read it
@@ -874,14 +883,17 @@ static int launch_pair(const uint8_t* a, const uint8_t* b, const GemmParams& p, 
 }  // namespace pair
 
 // =============================================================================================
-// Skinny variant for decode-sized batches (M <= 64).  The roles of the operands are swapped: the 128 rows of
-// the MMA are WEIGHT rows and its N dimension is the (padded) token count BT = 16 / 32 / 64, so the tensor
+// Skinny variant for decode-sized batches (M <= 128).  The roles of the operands are swapped: the 128 rows of
+// the MMA are WEIGHT rows and its N dimension is the (padded) token count BT = 16 / 32 / 64 / 128, so the tensor
 // cores spend BT/128 of the time a 128-row token tile of mostly padding would take and the kernel is a
 // stream of the weights.  One CTA owns 128 weight rows and one K range; the K ranges of a tile are the CTAs
 // of one thread-block cluster (1..8), which lets a shape with few weight tiles still pull from every SM.
-// The partial accumulators of ranks 1.. are written into rank 0's shared memory (st.shared::cluster) and
-// rank 0 adds them in ascending rank order, applies alpha and stores bf16: one kernel, no workspace, and
-// the result does not depend on timing.  Every TMA copy has one destination CTA (no multicast).
+// The partial accumulators are combined by a reduce-scatter through distributed shared memory: the token
+// columns are dealt out to the ranks, every rank writes its partial tile to its own shared memory and sends
+// each other rank the columns that rank owns with one bulk copy (cp.async.bulk shared::cta -> shared::cluster,
+// completion counted on the receiver's mbarrier); the owner adds the partials in ascending rank order, applies
+// alpha and stores bf16.  One kernel, no workspace, and the result does not depend on timing.  Every copy has
+// one destination CTA (no multicast).
 // =============================================================================================
 namespace skinny {
 
@@ -914,8 +926,11 @@ __device__ __forceinline__ void tc_ld_32x32b_x16(uint32_t taddr, uint32_t v[16])
         : "r"(taddr)
         : "memory");
 }
-__device__ __forceinline__ void st_cluster_f32(uint32_t cluster_addr, float v) {
-    asm volatile("st.shared::cluster.f32 [%0], %1;" ::"r"(cluster_addr), "f"(v) : "memory");
+// shared memory of this CTA -> shared memory of a CTA of the cluster; the bytes are counted on the receiver's barrier
+__device__ __forceinline__ void bulk_copy_to_cta(uint32_t dst_cluster, uint32_t src_cta, uint32_t bytes, uint32_t bar_cluster) {
+    asm volatile("cp.async.bulk.shared::cluster.shared::cta.mbarrier::complete_tx::bytes [%0], [%1], %2, [%3];" ::"r"(dst_cluster),
+                 "r"(src_cta), "r"(bytes), "r"(bar_cluster)
+                 : "memory");
 }
 
 struct SkinnyParams {
@@ -943,7 +958,8 @@ skinny_kernel(const __grid_constant__ CUtensorMap tmap_w, const __grid_constant_
     auto full_bar = [&](int s) { return bar_base + 8u * s; };
     auto empty_bar = [&](int s) { return bar_base + 8u * (kMaxStages + s); };
     const uint32_t tfull_bar = bar_base + 8u * (2 * kMaxStages);
-    volatile uint32_t* tmem_slot = reinterpret_cast<volatile uint32_t*>(bars + 2 * kMaxStages + 1);
+    const uint32_t recv_bar = bar_base + 8u * (2 * kMaxStages + 1);   // partials from the other ranks have landed
+    volatile uint32_t* tmem_slot = reinterpret_cast<volatile uint32_t*>(bars + 2 * kMaxStages + 2);
     volatile uint32_t* abort_flag = tmem_slot + 1;
 
     const int warp = __shfl_sync(0xffffffffu, threadIdx.x >> 5, 0);
@@ -952,6 +968,11 @@ skinny_kernel(const __grid_constant__ CUtensorMap tmap_w, const __grid_constant_
     uint32_t ranks;
     asm volatile("mov.u32 %0, %%cluster_nctarank;" : "=r"(ranks));
     const int nt = blockIdx.x / ranks;                  // 128-row weight tile (clusters run along x)
+    // reduce-scatter: token column c belongs to rank c / cols_per_rank
+    const uint32_t m_cols = static_cast<uint32_t>(min(p.M, BT));
+    const uint32_t cols_per_rank = (m_cols + ranks - 1) / ranks;
+    const uint32_t my_first = rank * cols_per_rank;
+    const uint32_t my_cols = my_first < m_cols ? min(cols_per_rank, m_cols - my_first) : 0u;
 
     if (threadIdx.x == 0) {
         for (int s = 0; s < nstages; ++s) {
@@ -959,9 +980,13 @@ skinny_kernel(const __grid_constant__ CUtensorMap tmap_w, const __grid_constant_
             mbar_init(empty_bar(s), 1);
         }
         mbar_init(tfull_bar, 1);
+        mbar_init(recv_bar, 1);
         *abort_flag = 0;
         asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
         asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
+        // (ranks - 1) senders x my columns x 128 rows x 4 bytes; armed before any rank can send (they send after
+        // the cluster barrier below the main loop)
+        if (ranks > 1 && my_cols > 0) mbar_expect_tx(recv_bar, (ranks - 1) * my_cols * 512u);
     }
     if (warp == 1) {
         asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(
@@ -1053,6 +1078,7 @@ skinny_kernel(const __grid_constant__ CUtensorMap tmap_w, const __grid_constant_
     // lane is the partial sum for token m.  Columns are handled 16 at a time to keep the register count low.
     const int sp = warp & 3;
     const int n_local = sp * 32 + lane;
+    const int n = nt * 128 + n_local;
     bool have = false;
     if (warp >= 2) {
         bool ok = mbar_wait(tfull_bar, 0, abort_flag, (9u << 24) | nt);
@@ -1060,12 +1086,29 @@ skinny_kernel(const __grid_constant__ CUtensorMap tmap_w, const __grid_constant_
         if (have) tc_fence_after();
     }
     const uint32_t t_lane = tmem_base + (static_cast<uint32_t>(sp * 32) << 16);
-    if (ranks > 1) {
-        // rank 0's ring is idle once its accumulator is complete (all its copies landed and were consumed);
-        // the first cluster barrier tells the other ranks so, the second that their partials have arrived.
-        cluster_sync_all();
-        if (warp >= 2 && rank > 0 && have) {
-            const uint32_t dst0 = map_to_cta(base, 0) + ((rank - 1) * BT * 128 + n_local) * 4;
+    if (ranks == 1) {
+        if (warp >= 2 && have) {
+            const float alpha = __ldg(p.alpha);
+#pragma unroll 1
+            for (int c = 0; c < BT / 16 && c * 16 < p.M; ++c) {
+                uint32_t v[16];
+                tc_ld_32x32b_x16(t_lane + c * 16, v);
+                tc_ld_wait();
+                if (n < p.N) {
+#pragma unroll
+                    for (int e = 0; e < 16; ++e)
+                        if (c * 16 + e < p.M)
+                            p.out[static_cast<int64_t>(c * 16 + e) * p.N + n] =
+                                __float2bfloat16_rn(__fmul_rn(__uint_as_float(v[e]), alpha));
+                }
+            }
+        }
+    } else {
+        // The ring is idle once the accumulator is complete (all copies landed and were consumed), so it is reused:
+        // `part` [token column][128 rows] fp32 = this rank's partial tile, `recv` [sending rank][owned column][128 rows].
+        float* part = reinterpret_cast<float*>(aligned);
+        float* recv = part + BT * 128;
+        if (warp >= 2 && have) {
 #pragma unroll 1
             for (int c = 0; c < BT / 16 && c * 16 < p.M; ++c) {
                 uint32_t v[16];
@@ -1073,34 +1116,51 @@ skinny_kernel(const __grid_constant__ CUtensorMap tmap_w, const __grid_constant_
                 tc_ld_wait();
 #pragma unroll
                 for (int e = 0; e < 16; ++e)
-                    if (c * 16 + e < p.M) st_cluster_f32(dst0 + (c * 16 + e) * 512, __uint_as_float(v[e]));
+                    if (c * 16 + e < p.M) part[(c * 16 + e) * 128 + n_local] = __uint_as_float(v[e]);
             }
+            asm volatile("fence.proxy.async.shared::cta;" ::: "memory");   // the bulk copies below read `part`
         }
+        // every rank has left its main loop: the `recv` areas may be written
         cluster_sync_all();
-    }
-    if (warp >= 2 && rank == 0 && have) {
-        const float alpha = __ldg(p.alpha);
-        const float* staged = reinterpret_cast<const float*>(aligned);
-        const int n = nt * 128 + n_local;
-#pragma unroll 1
-        for (int c = 0; c < BT / 16 && c * 16 < p.M; ++c) {
-            uint32_t v[16];
-            tc_ld_32x32b_x16(t_lane + c * 16, v);
-            tc_ld_wait();
-            float acc[16];
-#pragma unroll
-            for (int e = 0; e < 16; ++e) acc[e] = __uint_as_float(v[e]);
-            for (uint32_t r = 1; r < ranks; ++r)
-#pragma unroll
-                for (int e = 0; e < 16; ++e)
-                    if (c * 16 + e < p.M) acc[e] = __fadd_rn(acc[e], staged[((r - 1) * BT + c * 16 + e) * 128 + n_local]);
-            if (n < p.N) {
-#pragma unroll
-                for (int e = 0; e < 16; ++e)
-                    if (c * 16 + e < p.M)
-                        p.out[static_cast<int64_t>(c * 16 + e) * p.N + n] = __float2bfloat16_rn(__fmul_rn(acc[e], alpha));
+        if (warp == 2 && have && elect_one()) {
+            for (uint32_t o = 0; o < ranks; ++o) {
+                const uint32_t first = o * cols_per_rank;
+                if (o == rank || first >= m_cols) continue;
+                const uint32_t cols = min(cols_per_rank, m_cols - first);
+                bulk_copy_to_cta(map_to_cta(smem_u32(recv + (rank * cols_per_rank) * 128), o), smem_u32(part + first * 128),
+                                 cols * 512u, map_to_cta(recv_bar, o));
             }
         }
+        if (warp >= 2 && have && my_cols > 0) {
+            bool ok = mbar_wait(recv_bar, 0, abort_flag, (10u << 24) | nt);
+            ok = __shfl_sync(0xffffffffu, ok ? 1 : 0, 0) != 0;
+            if (ok && n < p.N) {
+                const float alpha = __ldg(p.alpha);
+                // this rank's own partial sits in `recv` terms at part[my_first ..]; eight columns at a time so that
+                // the shared-memory loads of one rank's partials are in flight together
+                const float* own = part + my_first * 128 + n_local;
+                __nv_bfloat16* dst = p.out + static_cast<int64_t>(my_first) * p.N + n;
+                for (uint32_t c0 = 0; c0 < my_cols; c0 += 8) {
+                    float acc[8];
+#pragma unroll
+                    for (int j = 0; j < 8; ++j) acc[j] = 0.0f;
+                    for (uint32_t r = 0; r < ranks; ++r) {
+                        const float* src = (r == rank) ? own : recv + (r * cols_per_rank) * 128 + n_local;
+                        float v[8];
+#pragma unroll
+                        for (int j = 0; j < 8; ++j) v[j] = (c0 + j < my_cols) ? src[(c0 + j) * 128] : 0.0f;
+#pragma unroll
+                        for (int j = 0; j < 8; ++j) acc[j] = r == 0 ? v[j] : __fadd_rn(acc[j], v[j]);
+                    }
+#pragma unroll
+                    for (int j = 0; j < 8; ++j)
+                        if (c0 + j < my_cols)
+                            dst[static_cast<int64_t>(c0 + j) * p.N] = __float2bfloat16_rn(__fmul_rn(acc[j], alpha));
+                }
+            }
+        }
+        // no rank may leave while another still copies out of its `part`
+        cluster_sync_all();
     }
 
     // ---------------------------------------------------------------------- teardown
@@ -1117,16 +1177,18 @@ skinny_kernel(const __grid_constant__ CUtensorMap tmap_w, const __grid_constant_
 }
 
 // K ranges per weight tile: the largest power of two that keeps every CTA of the grid resident at once (one per
-// SM), with at least two K stages each, at most 8 (the portable cluster size) and at most 64 / token tile.  Cluster sizes that are not a
-// power of two measured slower on B200 (6144 x 4096: 3 ranges 11.9 us, 2 ranges 8.0 us).
+// SM), with at least two K stages each and at most 8 (the portable cluster size).  With small token tiles two
+// CTAs fit on an SM, and where the K range is already cut, cutting it once more measured faster (16 x 8192 x 8192:
+// 12.2 -> 11.4 us); going from one range to two when the tiles already cover most SMs did not (16 x 14336 x 4096:
+// 10.5 -> 11.1 us).  Cluster sizes that are not a power of two measured slower (6144 x 4096: 3 ranges 11.9 us,
+// 2 ranges 8.0 us).
 static int choose_ranks(int n_tiles, int k_tiles, int sms, int forced, int bt) {
     int r = 1;
     if (forced > 0) {
         r = forced;
     } else {
-        // the reduction in rank 0 costs ranks x tokens; beyond 64 of those it ate the gain of the extra SMs
-        const int cap = bt >= 64 ? 1 : 64 / bt;
-        while (r < 8 && 2 * r <= cap && n_tiles * (2 * r) <= sms) r *= 2;
+        while (r < 8 && n_tiles * (2 * r) <= sms) r *= 2;
+        if (bt <= 32 && r >= 2 && r < 8 && n_tiles * (2 * r) <= 2 * sms - 40 && k_tiles / (2 * r) >= 4) r *= 2;
     }
     if (r > 8) r = 8;
     while (r > 1 && r > k_tiles / 2) --r;
@@ -1146,7 +1208,6 @@ static int launch_skinny(const uint8_t* x, const uint8_t* w, const GemmParams& g
     const int n_tiles = (g.N + 127) / 128;
     const int k_tiles = (g.K + kBK - 1) / kBK;
     int ranks = choose_ranks(n_tiles, k_tiles, sms, forced_ranks, BT);
-    while (ranks > 1 && (ranks - 1) * BT * 512 > C::kMaxStages * C::kStageBytes) --ranks;   // partials must fit in rank 0's ring
     SkinnyParams p;
     p.sfx = g.sfa;
     p.sfw = g.sfb;
@@ -1161,7 +1222,8 @@ static int launch_skinny(const uint8_t* x, const uint8_t* w, const GemmParams& g
     // one CTA per SM with a deep ring when the whole grid is resident at once, else two CTAs per SM
     p.stages = (n_tiles * ranks <= sms) ? C::kMaxStages : 4;
     if (p.stages > p.k_tiles_per_rank) p.stages = p.k_tiles_per_rank < 2 ? 2 : p.k_tiles_per_rank;
-    while ((ranks - 1) * BT * 512 > p.stages * C::kStageBytes) ++p.stages;   // room for the partials
+    // the ring doubles as the reduce-scatter buffers: the partial tile plus one slot per rank of the owned columns
+    while (ranks > 1 && (2 * BT + 8) * 512 > p.stages * C::kStageBytes) ++p.stages;
     if (p.stages > C::kMaxStages) return NVFP4_ERR_UNSUPPORTED;
     const int smem = p.stages * C::kStageBytes + 1024 + 256;
     cudaError_t e = cudaFuncSetAttribute(skinny_kernel<BT>, cudaFuncAttributeMaxDynamicSharedMemorySize,
@@ -1226,10 +1288,10 @@ extern "C" int nvfp4_gemm_tune(int k_splits, int k_rotate) {
 }
 
 // Testing hook: 0 = choose the kernel by shape, 1 = 128x128 tiles, 2 = 128x256 tiles, 3 = CTA-pair 256x256 tiles,
-// 4 = CTA-pair 256x192 tiles with two accumulators, 5 = skinny kernel (M <= 64; nvfp4_gemm_tune's k_splits then sets its K ranges per weight tile; larger M falls
-// back to the choice by shape).
+// 4 = CTA-pair 256x192 tiles with two accumulators, 5 = skinny kernel (M <= 128; nvfp4_gemm_tune's k_splits then
+// sets its K ranges per weight tile; larger M falls back to the choice by shape), 6 = 128x64 tiles.
 extern "C" int nvfp4_gemm_force_path(int path) {
-    if (path < 0 || path > 5) return NVFP4_ERR_BAD_ENUM;
+    if (path < 0 || path > 6) return NVFP4_ERR_BAD_ENUM;
     g_gemm_force_path = path;
     return NVFP4_OK;
 }
@@ -1268,9 +1330,20 @@ extern "C" int nvfp4_gemm_launch(const uint8_t* a, const uint8_t* b, const uint8
     p.raster_group = g_gemm_raster_group > 0 ? g_gemm_raster_group : (1 << 20);
     cudaStream_t s = static_cast<cudaStream_t>(stream);
     // Decode-sized batches: weight rows on the MMA's 128 rows, tokens on its N dimension, K ranges across a cluster.
-    // Measured on B200 against the other kernels with the weights streaming from HBM: faster up to 32 tokens.
-    if ((g_gemm_force_path == 5 && M <= kSkinnyMaxM) ||
-        (g_gemm_force_path == 0 && g_gemm_force_splits == 0 && M <= kSkinnyAutoM)) {
+    // Measured on B200 with the weights streaming from HBM: faster than every other kernel up to 32 tokens; from 33
+    // to 128 tokens only where few weight tiles meet a long K (at least 4 K ranges of at least 12 stages each, e.g.
+    // 64 x 4096 x 14336: 13.2 us against 19.4 us), because its epilogue grows with the token tile.
+    bool skinny = false;
+    if (g_gemm_force_path == 5) {
+        skinny = M <= kSkinnyMaxM;
+    } else if (g_gemm_force_path == 0 && g_gemm_force_splits == 0 && M <= kSkinnyMaxM) {
+        int dev = 0, sms = 148;
+        cudaGetDevice(&dev);
+        cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev);
+        const int ranks = gemm::skinny::choose_ranks(static_cast<int>((N + 127) / 128), k_tiles_total, sms, 0, M <= 64 ? 64 : 128);
+        skinny = M <= kSkinnyAutoM || (ranks >= 4 && k_tiles_total / ranks >= 12);
+    }
+    if (skinny) {
         const int forced = g_gemm_force_path == 5 ? g_gemm_force_splits : 0;
         if (M <= 16) return gemm::skinny::launch_skinny<16>(a, b, p, forced, s);
         if (M <= 32) return gemm::skinny::launch_skinny<32>(a, b, p, forced, s);
@@ -1283,22 +1356,29 @@ extern "C" int nvfp4_gemm_launch(const uint8_t* a, const uint8_t* b, const uint8
         if (reinterpret_cast<uintptr_t>(workspace) & 15) return NVFP4_ERR_MISALIGNED;
     }
     // Kernel choice by a small cost model fitted to measurements on B200: time ~ waves x cost of one tile, where a
-    // wave is 148 single-CTA tiles or 74 CTA-pair tiles.  Relative tile costs: 128x128 -> 0.7, 128x256 -> 1.0,
+    // wave is 148 single-CTA tiles or 74 CTA-pair tiles.  Relative tile costs: 128x64 -> 0.45, 128x128 -> 0.7, 128x256 -> 1.0,
     // pair 256x192 -> 0.68 (0.75 of the MMA work per SM, and its epilogue overlaps the next tile).
-    int path = g_gemm_force_path >= 5 ? 0 : g_gemm_force_path;   // 0 = choose by shape
+    int path = g_gemm_force_path == 5 ? 0 : g_gemm_force_path;   // 0 = choose by shape
     if (path == 0) {
         const int64_t mt = (M + 127) / 128;
         const double c1 = static_cast<double>((mt * ((N + 127) / 128) + 147) / 148) * 0.7;
         const double c2 = static_cast<double>((mt * ((N + 255) / 256) + 147) / 148) * 1.0;
         const double c4 = static_cast<double>((((M + 255) / 256) * ((N + 191) / 192) + 73) / 74) * 0.68;
         path = (c1 <= c2) ? 1 : 2;
-        const double best = c1 <= c2 ? c1 : c2;
-        if (M > 128 && N > 128 && p.k_splits == 1 && c4 <= best) path = 4;
+        double best = c1 <= c2 ? c1 : c2;
+        if (M > 128 && N > 128 && p.k_splits == 1 && c4 <= best) {
+            path = 4;
+            best = c4;
+        }
+        // few, long tiles (one or two token tiles): 64 weight rows per CTA put twice as many SMs on the weight stream
+        const double c6 = static_cast<double>((mt * ((N + 63) / 64) + 147) / 148) * 0.45;
+        if (mt <= 2 && c6 < best) path = 6;
     }
-    if (p.k_splits > 1 && path != 1 && path != 2) path = 1;
+    if (p.k_splits > 1 && path != 1 && path != 2 && path != 6) path = 1;
     if (path == 3) return gemm::pair::launch_pair<256>(a, b, p, s);
     if (path == 4) return gemm::pair::launch_pair<192>(a, b, p, s);
     if (path == 2) return gemm::launch<256>(a, b, p, s);
+    if (path == 6) return gemm::launch<64>(a, b, p, s);
     return gemm::launch<128>(a, b, p, s);
 }
 

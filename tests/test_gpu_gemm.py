@@ -57,7 +57,7 @@ def test_gemm_matches_fp64_oracle(cuda_lib, oracle, M, N, K_):
 @pytest.mark.parametrize("M,N,K_", [(128, 256, 256), (300, 520, 320), (1, 512, 1024), (512, 768, 1024), (257, 1000, 192),
                                     (1024, 2048, 4096)])
 def test_gemm_kernel_paths_agree(cuda_lib, oracle, M, N, K_):
-    """128x128, 128x256 and CTA-pair kernels must give the same bf16 bits (fp32 accumulation in
+    """128x64, 128x128, 128x256 and CTA-pair kernels must give the same bf16 bits (fp32 accumulation in
     the same K order) and each must satisfy the oracle tolerance."""
     import nvfp4quant_test_b200.kernels as K
     from nvfp4quant_test_b200.kernels.kernel_gemm import gemm_last_status
@@ -68,7 +68,7 @@ def test_gemm_kernel_paths_agree(cuda_lib, oracle, M, N, K_):
     alpha = (gsa * gsb).reshape(1).float()
     outs = []
     try:
-        for path in (1, 2, 3, 4):
+        for path in (1, 2, 3, 4, 6):
             assert cuda_lib.nvfp4_gemm_force_path(path) == 0
             out = torch.full((M, N), float("nan"), dtype=torch.bfloat16, device="cuda")
             K.nvfp4_scaled_mm(qa, qb, sa, sb, alpha, torch.bfloat16, out=out)
@@ -78,7 +78,7 @@ def test_gemm_kernel_paths_agree(cuda_lib, oracle, M, N, K_):
         cuda_lib.nvfp4_gemm_force_path(0)
     ref = oracle.gemm(qa.cpu().numpy(), qb.cpu().numpy(), sa.view(torch.uint8).cpu().numpy().reshape(-1),
                       sb.view(torch.uint8).cpu().numpy().reshape(-1), float(alpha))
-    for path, out in zip((1, 2, 3, 4), outs):
+    for path, out in zip((1, 2, 3, 4, 6), outs):
         _check(out, ref)
     assert all(torch.equal(outs[0], o) for o in outs[1:])
 
