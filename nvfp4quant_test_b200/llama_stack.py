@@ -78,14 +78,20 @@ def stack_weight_scales(qlayer: dict) -> dict[int, tuple[torch.Tensor, dict[str,
 
 
 def layer_gemms(qlayer: dict, acts: dict[int, torch.Tensor], act_importance: dict[str, torch.Tensor],
-                weight_scales: dict | None = None):
+                weight_scales: dict | None = None, side_streams: list | None = None):
     """y = x @ W.T for every matrix of the layer with NVFP4 operands; activations quantized with the unweighted sweep
-    unless an importance vector for them is given.  Returns {name: bf16 [tokens, N]}."""
+    unless an importance vector for them is given.  Returns {name: bf16 [tokens, N]}.
+
+    The GEMMs of a layer are independent of one another.  With `side_streams` they are dealt out over those streams
+    (forked from and joined back into the current stream, which also works under CUDA-graph capture), so that at
+    small token counts, where one GEMM does not fill the GPU, several run at the same time."""
     if weight_scales is None:
         weight_scales = stack_weight_scales(qlayer)
+    main = torch.cuda.current_stream()
     out = {}
     qact: dict[int, tuple] = {}
-    for name, (codes, scales, gs_w) in qlayer.items():
+    used = []
+    for i, (name, (codes, scales, gs_w)) in enumerate(qlayer.items()):
         k = codes.shape[1] * 2
         if k not in qact:
             x = acts[k]
@@ -95,14 +101,33 @@ def layer_gemms(qlayer: dict, acts: dict[int, torch.Tensor], act_importance: dic
                 qa, sa = K.scalesweep_mse_nvfp4_quant_impl(x, gs_x_inv)
             else:
                 qa, sa = K.scalesweep_weighted_mse_nvfp4_quant_impl(x, imp, gs_x_inv)
-            qact[k] = (qa, sa, gs_x.float() * weight_scales[k][0])      # alphas of every matrix fed by this input
-        qa, sa, alphas = qact[k]
+            ready = None
+            if side_streams:
+                ready = torch.cuda.Event()
+                alphas = gs_x.float() * weight_scales[k][0]
+                ready.record(main)
+            else:
+                alphas = gs_x.float() * weight_scales[k][0]      # alphas of every matrix fed by this input
+            qact[k] = (qa, sa, alphas, ready)
+        qa, sa, alphas, ready = qact[k]
         slot = weight_scales[k][1][name]
-        out[name] = K.nvfp4_scaled_mm(qa, codes, sa, scales, alphas[slot:slot + 1], torch.bfloat16)
+        if side_streams:
+            st = side_streams[i % len(side_streams)]
+            st.wait_event(ready)
+            with torch.cuda.stream(st):
+                out[name] = K.nvfp4_scaled_mm(qa, codes, sa, scales, alphas[slot:slot + 1], torch.bfloat16)
+            if st not in used:
+                used.append(st)
+        else:
+            out[name] = K.nvfp4_scaled_mm(qa, codes, sa, scales, alphas[slot:slot + 1], torch.bfloat16)
+    for st in used:
+        done = torch.cuda.Event()
+        done.record(st)
+        main.wait_event(done)
     return out
 
 
-def run(n_layers: int, token_batches: list[int], seed: int = 0, use_graph: bool = True) -> dict:
+def run(n_layers: int, token_batches: list[int], seed: int = 0, use_graph: bool = True, n_streams: int = 4) -> dict:
     import torch.distributed as dist
 
     rank = int(os.environ.get("RANK", "0"))
@@ -141,6 +166,7 @@ def run(n_layers: int, token_batches: list[int], seed: int = 0, use_graph: bool 
     e1.record()
     sync()
     wscales = [stack_weight_scales(q) for q in qlayers]
+    side = [torch.cuda.Stream(device=dev) for _ in range(n_streams)] if n_streams > 1 else None
     quant_ms = max_ms(e0.elapsed_time(e1))
     n_weights = n_layers * weights_per_layer()
     result = {
@@ -154,7 +180,7 @@ def run(n_layers: int, token_batches: list[int], seed: int = 0, use_graph: bool 
         acts = {k: torch.normal(0.0, 1.0, size=(tokens, k), generator=gen, device=dev, dtype=torch.bfloat16)
                 for k in calib}
         for q, ws in zip(qlayers[:1], wscales):
-            layer_gemms(q, acts, {}, ws)
+            layer_gemms(q, acts, {}, ws, side)
         sync()
         graph = None
         if use_graph and qlayers:
@@ -163,7 +189,7 @@ def run(n_layers: int, token_batches: list[int], seed: int = 0, use_graph: bool 
             graph = torch.cuda.CUDAGraph()
             with torch.cuda.graph(graph):
                 for q, ws in zip(qlayers, wscales):
-                    layer_gemms(q, acts, {}, ws)
+                    layer_gemms(q, acts, {}, ws, side)
             graph.replay()
             sync()
         e0.record()
@@ -171,13 +197,13 @@ def run(n_layers: int, token_batches: list[int], seed: int = 0, use_graph: bool 
             graph.replay()
         else:
             for q, ws in zip(qlayers, wscales):
-                layer_gemms(q, acts, {}, ws)
+                layer_gemms(q, acts, {}, ws, side)
         e1.record()
         sync()
         ms = max_ms(e0.elapsed_time(e1))
         flops = 2.0 * tokens * weights_per_layer() * n_layers
         result["gemm"].append({"tokens": tokens, "ms_all_layers": ms, "tflops": flops / (ms * 1e-3) / 1e12,
-                               "cuda_graph": graph is not None,
+                               "cuda_graph": graph is not None, "streams": n_streams,
                                "includes": "activation global scale + quantization + 7 GEMMs per layer"})
     if world > 1:
         dist.destroy_process_group()
@@ -189,9 +215,11 @@ def main() -> None:
     ap.add_argument("--layers", type=int, default=32)
     ap.add_argument("--batches", type=int, nargs="*", default=[1, 32, 256, 4096])
     ap.add_argument("--seed", type=int, default=0)
+    ap.add_argument("--streams", type=int, default=4,
+                    help="streams the GEMMs of a layer are dealt out over (1 = all on the current stream)")
     ap.add_argument("--no-graph", action="store_true", help="launch the GEMM phase eagerly instead of replaying a CUDA graph")
     args = ap.parse_args()
-    res = run(args.layers, args.batches, args.seed, use_graph=not args.no_graph)
+    res = run(args.layers, args.batches, args.seed, use_graph=not args.no_graph, n_streams=args.streams)
     if res:
         print(json.dumps(res))
 

@@ -204,6 +204,11 @@ def test_llama_stack_layer_shapes(cuda_lib, oracle):
     gen.manual_seed(5)
     acts = {kk: torch.normal(0.0, 1.0, size=(32, kk), generator=gen, device=dev, dtype=torch.bfloat16) for kk in calib}
     outs = LS.layer_gemms(q, acts, {})
+    # the same GEMMs dealt out over side streams (forked from / joined into the current stream): same bits
+    side = [torch.cuda.Stream() for _ in range(3)]
+    outs_side = LS.layer_gemms(q, acts, {}, None, side)
+    torch.cuda.synchronize()
+    assert all(torch.equal(outs[name], outs_side[name]) for name in outs)
     for name in ("k", "down", "gate"):
         n, k = LS.LAYER_SHAPES[name]
         codes, scales, gs_w = q[name]
