@@ -70,10 +70,11 @@ int nvfp4_quant_launch(int variant, const void* x, int x_dtype, const float* imp
                        const float* gs_inv, uint8_t* codes, uint8_t* scales, int64_t m, int64_t n,
                        int64_t padded_n, int lower, int upper, int swizzled, void* stream);
 
-/* Same, choosing the kernel body: 0 = default (= 3), 1 = scalar (one candidate at a time, the plainest
- * transcription), 2 = one candidate per trip with packed multiplies and the mixed-precision subtract,
- * 3 = two candidates per trip sharing one f32x2 FMA chain.  All give identical bytes; exposed for testing
- * and timing. */
+/* Same, choosing the kernel body: 0 = default (3, or 5 when a quarter or more of the scale layout's rows are
+ * padding), 1 = scalar (one candidate at a time, the plainest transcription), 2 = one candidate per trip with
+ * packed multiplies and the mixed-precision subtract, 3 = two candidates per trip sharing one f32x2 FMA chain,
+ * 5 = 3 with warps that hold only padding rows skipping the sweep (4 is the fused form, which has its own entry
+ * point below).  All give identical bytes; exposed for testing and timing. */
 int nvfp4_quant_launch_impl(int impl, int variant, const void* x, int x_dtype, const float* importance,
                             const float* gs_inv, uint8_t* codes, uint8_t* scales, int64_t m, int64_t n,
                             int64_t padded_n, int lower, int upper, int swizzled, void* stream);
@@ -87,6 +88,25 @@ int nvfp4_quant_launch_impl(int impl, int variant, const void* x, int x_dtype, c
  */
 int nvfp4_global_scale_launch(const void* x, int x_dtype, int64_t numel, float fp8_max, float* out,
                               uint32_t* scratch, void* stream);
+
+/*
+ * Global scale and ScaleSweep quantization in one launch: what get_nvfp4_global_scale (helper.py:96-100)
+ * followed by scalesweep_*_quant_out (kernels/kernel_ScaleSweep_MSE.py:380-413, kernels/kernel_ScaleSweep.py:436-489)
+ * compute, as the reference's bench chains them (bench.py:57-67), with identical bytes.  variant is
+ * NVFP4_VARIANT_MSE or NVFP4_VARIANT_WEIGHTED; gs_out[0] = amax(|x|) / (6 * fp8_max), gs_out[1] = 1 / gs_out[0].
+ * Every 16-element block stays in its thread's registers while the CTAs combine their maxima through
+ * `scratch` and wait for one another (cooperative launch; the wait is bounded, see nvfp4_quant_fused_last_status),
+ * so x crosses HBM once.  The tensor must fit the resident grid of the device (about 3 M elements on a B200):
+ * otherwise NVFP4_ERR_TOO_LARGE is returned, nothing is launched, and the caller issues the two launches.
+ * `scratch` = 4 uint32, zero before the first call; the kernel leaves them zero.  Calls that share a scratch
+ * must be ordered on one stream.
+ */
+int nvfp4_quant_fused_launch(int variant, const void* x, int x_dtype, const float* importance, float fp8_max,
+                             float* gs_out, uint32_t* scratch, uint8_t* codes, uint8_t* scales, int64_t m, int64_t n,
+                             int64_t padded_n, int lower, int upper, int swizzled, void* stream);
+/* Synchronises `stream`; *status = 0, or 1 if a fused launch on this device gave up its grid-wide wait (its
+ * outputs are then invalid and its scratch must be zeroed again).  Reading a non-zero status clears it. */
+int nvfp4_quant_fused_last_status(void* stream, uint32_t* status);
 
 /*
  * out[j] = sum_i x[i, j]^2 in fp32 for x[m, n] (n % 4 == 0, x 16-byte aligned): the per-input-channel squared

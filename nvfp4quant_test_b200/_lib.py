@@ -13,9 +13,11 @@ LIB_PATH = _PKG / "libnvfp4_b200.so"
 
 VARIANT_MSE, VARIANT_WEIGHTED, VARIANT_AMAX = 0, 1, 2
 DT_BF16, DT_F16, DT_F32 = 0, 1, 2
+ERR_TOO_LARGE = -8
 
 EXPORTS = (
-    "nvfp4_quant_launch", "nvfp4_quant_launch_impl", "nvfp4_global_scale_launch", "nvfp4_channel_sqnorm_launch",
+    "nvfp4_quant_launch", "nvfp4_quant_launch_impl", "nvfp4_quant_fused_launch", "nvfp4_quant_fused_last_status",
+    "nvfp4_global_scale_launch", "nvfp4_channel_sqnorm_launch",
     "nvfp4_gemm_launch", "nvfp4_gemm_workspace_bytes", "nvfp4_gemm_last_status", "nvfp4_gemm_force_path", "nvfp4_gemm_tune", "nvfp4_gemm_tune_raster",
     "nvfp4_probe_div_full_table", "nvfp4_probe_amax_out_scale_table",
     "nvfp4_status_string", "nvfp4_abi_version",
@@ -45,6 +47,10 @@ def lib() -> ctypes.CDLL:
         L.nvfp4_quant_launch.argtypes = [ci, vp, ci, vp, vp, vp, vp, i64, i64, i64, ci, ci, ci, vp]
         L.nvfp4_quant_launch_impl.restype = ci
         L.nvfp4_quant_launch_impl.argtypes = [ci, ci, vp, ci, vp, vp, vp, vp, i64, i64, i64, ci, ci, ci, vp]
+        L.nvfp4_quant_fused_launch.restype = ci
+        L.nvfp4_quant_fused_launch.argtypes = [ci, vp, ci, vp, f32, vp, vp, vp, vp, i64, i64, i64, ci, ci, ci, vp]
+        L.nvfp4_quant_fused_last_status.restype = ci
+        L.nvfp4_quant_fused_last_status.argtypes = [vp, vp]
         L.nvfp4_global_scale_launch.restype = ci
         L.nvfp4_global_scale_launch.argtypes = [vp, ci, i64, f32, vp, vp, vp]
         L.nvfp4_channel_sqnorm_launch.restype = ci

@@ -18,6 +18,12 @@
 // multiplies and the mixed-precision subtract (2), and the default (3): two
 // candidates per trip whose FMA chains share one f32x2 instruction (each lane of
 // a packed instruction is an independent IEEE operation).
+//
+// Body 4 is body 3 with the tensor-wide global scale (helper.py:96-100: amax / (6 * fp8_max) and its reciprocal)
+// computed inside the same launch: every thread keeps its block in registers, the CTAs combine their maxima
+// through a scratch word and wait for one another (cooperative launch: all CTAs are resident; the wait is bounded
+// by the global timer), then the sweep runs as usual.  x is read from HBM once and one launch replaces two; the
+// tensor must fit the resident grid (about 3 M elements on a B200).
 #include <cuda_bf16.h>
 #include <cuda_fp16.h>
 
@@ -46,7 +52,14 @@ struct QuantParams {
     int64_t total;          // rows * width
     int lower, ncand;
     int swizzled;
+    // fused global-scale variant only
+    float fp8_max;
+    float* gs_out;          // [2]: global scale, its reciprocal
+    uint32_t* fused_scratch;  // [4]: running maximum, arrivals, readers, unused; zero between calls
 };
+
+__device__ uint32_t g_quant_status;   // 0 = ok; 1 = the grid-wide wait of the fused kernel gave up
+constexpr uint64_t kFusedWaitLimitNs = 2000000000ull;
 
 template <int DT>
 __device__ __forceinline__ void load16(const void* base, int64_t elem, float v[16]);
@@ -303,7 +316,9 @@ __global__ void __launch_bounds__(kThreads, VARIANT == NVFP4_VARIANT_WEIGHTED ? 
 quant_kernel(const QuantParams p) {
     static_assert(kThreads == kTabSize, "one table entry per thread");
     __shared__ float4 tab[kTabSize];
-    const float gs_inv = __ldg(p.gs_inv);
+    constexpr bool FUSED = IMPL == 4;
+    static_assert(!FUSED || VARIANT != NVFP4_VARIANT_AMAX, "the fused variant covers the two sweeps");
+    float gs_inv = FUSED ? 0.0f : __ldg(p.gs_inv);
     {
         float4 e;
         if (VARIANT == NVFP4_VARIANT_AMAX) {   // tab[raw].x = multiplier for scale byte raw (entries 0..127 used)
@@ -349,9 +364,65 @@ quant_kernel(const QuantParams p) {
         if (VARIANT == NVFP4_VARIANT_WEIGHTED) load16<NVFP4_DT_F32>(p.importance, col * kBlock, w);
     }
 
+    if (FUSED) {
+        // tensor-wide maximum on fp32 magnitude bit patterns (a NaN pattern is larger than +inf, as torch's max wants)
+        __shared__ uint32_t warp_max[kThreads / 32];
+        __shared__ float gs_inv_shared;
+        uint32_t bits = 0;
+#pragma unroll
+        for (int j = 0; j < 16; ++j) bits = max(bits, __float_as_uint(v[j]) & 0x7fffffffu);
+#pragma unroll
+        for (int o = 16; o > 0; o >>= 1) bits = max(bits, __shfl_xor_sync(0xffffffffu, bits, o));
+        if ((threadIdx.x & 31) == 0) warp_max[threadIdx.x >> 5] = bits;
+        __syncthreads();
+        if (threadIdx.x == 0) {
+            uint32_t b = 0;
+            for (int i = 0; i < kThreads / 32; ++i) b = max(b, warp_max[i]);
+            volatile uint32_t* sc = p.fused_scratch;
+            atomicMax(p.fused_scratch, b);
+            __threadfence();
+            atomicAdd(p.fused_scratch + 1, 1u);
+            // every CTA of a cooperative launch is resident, so the others will arrive; bounded all the same
+            uint64_t t0 = 0;
+            asm volatile("mov.u64 %0, %globaltimer;" : "=l"(t0));
+            while (sc[1] < gridDim.x) {
+                uint64_t t1;
+                asm volatile("mov.u64 %0, %globaltimer;" : "=l"(t1));
+                if (t1 - t0 > kFusedWaitLimitNs) {
+                    atomicExch(&g_quant_status, 1u);
+                    break;
+                }
+                __nanosleep(64);
+            }
+            __threadfence();
+            const float amax = __uint_as_float(sc[0]);
+            const float inv_den = __fdiv_rn(1.0f, __fmul_rn(6.0f, p.fp8_max));
+            const float gs = __fmul_rn(amax, inv_den);
+            const float gsi = __fdiv_rn(1.0f, gs);
+            gs_inv_shared = gsi;
+            __threadfence();
+            // the last CTA to have read the maximum publishes the result and leaves the scratch zeroed
+            if (atomicAdd(p.fused_scratch + 2, 1u) == gridDim.x - 1) {
+                p.gs_out[0] = gs;
+                p.gs_out[1] = gsi;
+                sc[0] = 0u;
+                sc[1] = 0u;
+                sc[2] = 0u;
+            }
+        }
+        __syncthreads();
+        gs_inv = gs_inv_shared;
+    }
+
     uint32_t sbyte = 0;
     float inv = 0.0f;
-    if (VARIANT == NVFP4_VARIANT_AMAX) {
+    // Body 5 = body 3 plus: a warp whose 32 slots are all padding (rows beyond m in the tiled scale layout: 127 of
+    // 128 rows for a single token) has nothing to sweep and only writes its zero scale bytes below.  A separate
+    // instantiation because the vote and branch cost the full-size kernel 6 % (8192 x 8192: 123.7 -> 131.8 us);
+    // the launcher picks it when at least a quarter of the slot grid is padding rows.
+    if (IMPL == 5 && !__any_sync(0xffffffffu, valid)) {
+        // nothing
+    } else if (VARIANT == NVFP4_VARIANT_AMAX) {
         const float amax = max_abs16(v);
         const float sf = __fmul_rn(gs_inv, __fmul_rn(amax, rcp_approx_ftz(6.0f)));
         sbyte = f32_to_e4m3(sf);
@@ -412,6 +483,8 @@ cudaError_t launch_impl(int impl, const QuantParams& p, cudaStream_t stream) {
         quant_kernel<DT, VARIANT, 1><<<static_cast<unsigned>(grid), kThreads, 0, stream>>>(p);
     else if (impl == 2)
         quant_kernel<DT, VARIANT, 2><<<static_cast<unsigned>(grid), kThreads, 0, stream>>>(p);
+    else if (impl == 5 || (impl == 0 && (p.rows - p.m) * 4 >= p.rows))
+        quant_kernel<DT, VARIANT, 5><<<static_cast<unsigned>(grid), kThreads, 0, stream>>>(p);
     else
         quant_kernel<DT, VARIANT, 3><<<static_cast<unsigned>(grid), kThreads, 0, stream>>>(p);
     return cudaGetLastError();
@@ -435,7 +508,7 @@ extern "C" int nvfp4_quant_launch_impl(int impl, int variant, const void* x, int
     using namespace nvfp4;
     if (variant < NVFP4_VARIANT_MSE || variant > NVFP4_VARIANT_AMAX) return NVFP4_ERR_BAD_ENUM;
     if (x_dtype < NVFP4_DT_BF16 || x_dtype > NVFP4_DT_F32) return NVFP4_ERR_BAD_ENUM;
-    if (impl < 0 || impl > 3) return NVFP4_ERR_BAD_ENUM;
+    if (impl < 0 || impl > 5 || impl == 4) return NVFP4_ERR_BAD_ENUM;
     if (m < 0 || n < 0 || (n % kBlock) != 0 || (padded_n % kBlock) != 0 || padded_n < n) return NVFP4_ERR_BAD_SHAPE;
     if (variant != NVFP4_VARIANT_AMAX && (upper < lower || upper - lower + 1 > 64)) return NVFP4_ERR_BAD_RANGE;
     QuantParams p;
@@ -473,6 +546,99 @@ extern "C" int nvfp4_quant_launch_impl(int impl, int variant, const void* x, int
         default: err = launch_variant<NVFP4_DT_F32>(variant, impl, p, s); break;
     }
     return static_cast<int>(err);
+}
+
+namespace nvfp4 {
+namespace {
+template <int DT, int VARIANT>
+cudaError_t launch_fused(const QuantParams& p, int sms, cudaStream_t stream, bool* too_large) {
+    const int64_t grid = (p.total + kThreads - 1) / kThreads;
+    int per_sm = 0;
+    cudaError_t e = cudaOccupancyMaxActiveBlocksPerMultiprocessor(&per_sm, quant_kernel<DT, VARIANT, 4>, kThreads, 0);
+    if (e != cudaSuccess) return e;
+    if (grid > static_cast<int64_t>(per_sm) * sms) {
+        *too_large = true;
+        return cudaSuccess;
+    }
+    QuantParams q = p;
+    void* args[] = {&q};
+    return cudaLaunchCooperativeKernel(reinterpret_cast<const void*>(quant_kernel<DT, VARIANT, 4>),
+                                       dim3(static_cast<unsigned>(grid)), dim3(kThreads), args, 0, stream);
+}
+template <int DT>
+cudaError_t launch_fused_variant(int variant, const QuantParams& p, int sms, cudaStream_t stream, bool* too_large) {
+    if (variant == NVFP4_VARIANT_MSE) return launch_fused<DT, NVFP4_VARIANT_MSE>(p, sms, stream, too_large);
+    return launch_fused<DT, NVFP4_VARIANT_WEIGHTED>(p, sms, stream, too_large);
+}
+}  // namespace
+}  // namespace nvfp4
+
+extern "C" int nvfp4_quant_fused_launch(int variant, const void* x, int x_dtype, const float* importance, float fp8_max,
+                                        float* gs_out, uint32_t* scratch, uint8_t* codes, uint8_t* scales, int64_t m,
+                                        int64_t n, int64_t padded_n, int lower, int upper, int swizzled, void* stream) {
+    using namespace nvfp4;
+    if (variant != NVFP4_VARIANT_MSE && variant != NVFP4_VARIANT_WEIGHTED) return NVFP4_ERR_BAD_ENUM;
+    if (x_dtype < NVFP4_DT_BF16 || x_dtype > NVFP4_DT_F32) return NVFP4_ERR_BAD_ENUM;
+    if (m < 0 || n < 0 || (n % kBlock) != 0 || (padded_n % kBlock) != 0 || padded_n < n) return NVFP4_ERR_BAD_SHAPE;
+    if (upper < lower || upper - lower + 1 > 64) return NVFP4_ERR_BAD_RANGE;
+    if (!(fp8_max > 0.0f)) return NVFP4_ERR_BAD_RANGE;
+    QuantParams p;
+    p.m = m;
+    p.n = n;
+    p.bin = n / kBlock;
+    p.bout = padded_n / kBlock;
+    p.k_pad = round_up_i64(p.bout, 4);
+    p.swizzled = swizzled ? 1 : 0;
+    p.width = swizzled ? p.k_pad : p.bout;
+    p.rows = swizzled ? round_up_i64(m, 128) : m;
+    p.total = p.rows * p.width;
+    if (p.total == 0 || m * n == 0) return NVFP4_ERR_BAD_SHAPE;   // an empty tensor has no maximum
+    if (!gs_out || !scratch || !codes || !scales || !x) return NVFP4_ERR_NULL_POINTER;
+    if (variant == NVFP4_VARIANT_WEIGHTED && !importance) return NVFP4_ERR_NULL_POINTER;
+    if ((reinterpret_cast<uintptr_t>(x) & 15) || (reinterpret_cast<uintptr_t>(codes) & 7) ||
+        (reinterpret_cast<uintptr_t>(gs_out) & 3) || (reinterpret_cast<uintptr_t>(scratch) & 3))
+        return NVFP4_ERR_MISALIGNED;
+    if (swizzled && (reinterpret_cast<uintptr_t>(scales) & 3)) return NVFP4_ERR_MISALIGNED;
+    if (!swizzled && (p.width & 3) == 0 && (reinterpret_cast<uintptr_t>(scales) & 3)) return NVFP4_ERR_MISALIGNED;
+    if (variant == NVFP4_VARIANT_WEIGHTED && (reinterpret_cast<uintptr_t>(importance) & 15)) return NVFP4_ERR_MISALIGNED;
+    p.x = x;
+    p.importance = importance;
+    p.gs_inv = nullptr;
+    p.codes = codes;
+    p.scales = scales;
+    p.lower = lower;
+    p.ncand = upper - lower + 1;
+    p.fp8_max = fp8_max;
+    p.gs_out = gs_out;
+    p.fused_scratch = scratch;
+    int dev = 0, sms = 0, coop = 0;
+    cudaGetDevice(&dev);
+    cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev);
+    cudaDeviceGetAttribute(&coop, cudaDevAttrCooperativeLaunch, dev);
+    if (!coop) return NVFP4_ERR_UNSUPPORTED;
+    cudaStream_t s = static_cast<cudaStream_t>(stream);
+    bool too_large = false;
+    cudaError_t err;
+    switch (x_dtype) {
+        case NVFP4_DT_BF16: err = launch_fused_variant<NVFP4_DT_BF16>(variant, p, sms, s, &too_large); break;
+        case NVFP4_DT_F16: err = launch_fused_variant<NVFP4_DT_F16>(variant, p, sms, s, &too_large); break;
+        default: err = launch_fused_variant<NVFP4_DT_F32>(variant, p, sms, s, &too_large); break;
+    }
+    if (too_large) return NVFP4_ERR_TOO_LARGE;
+    return static_cast<int>(err);
+}
+
+extern "C" int nvfp4_quant_fused_last_status(void* stream, uint32_t* status_host) {
+    if (!status_host) return NVFP4_ERR_NULL_POINTER;
+    cudaError_t e = cudaStreamSynchronize(static_cast<cudaStream_t>(stream));
+    if (e != cudaSuccess) return static_cast<int>(e);
+    e = cudaMemcpyFromSymbol(status_host, nvfp4::g_quant_status, sizeof(uint32_t));
+    if (e != cudaSuccess) return static_cast<int>(e);
+    if (*status_host != 0) {
+        const uint32_t zero = 0;
+        e = cudaMemcpyToSymbol(nvfp4::g_quant_status, &zero, sizeof(uint32_t));
+    }
+    return static_cast<int>(e);
 }
 
 extern "C" int nvfp4_quant_launch(int variant, const void* x, int x_dtype, const float* importance,

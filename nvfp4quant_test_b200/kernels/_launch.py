@@ -36,13 +36,8 @@ def check_importance(input: torch.Tensor, importance: torch.Tensor) -> None:
             f"input and importance must be on the same device: {input.device} vs {importance.device}")
 
 
-def quant_out(variant: int, input: torch.Tensor, importance: torch.Tensor | None, input_scale: torch.Tensor,
-              is_sf_swizzled_layout: bool, output: torch.Tensor, output_scale: torch.Tensor,
-              lower: int, upper: int, impl: int = 0) -> None:
-    """Validate, then launch on the current stream of input.device.  Writes output / output_scale in place."""
-    _check_common(input, input_scale)
-    if not input.is_contiguous():
-        input = input.contiguous()
+def _check_outputs(input: torch.Tensor, is_sf_swizzled_layout: bool, output: torch.Tensor,
+                   output_scale: torch.Tensor) -> tuple[int, int, int]:
     m, n = input.shape
     if output.dtype != torch.uint8 or output.ndim != 2 or output.shape[0] != m or not output.is_contiguous():
         raise ValueError(f"output must be a contiguous uint8 tensor [num_row, padded_n/2], got {tuple(output.shape)} {output.dtype}")
@@ -61,13 +56,35 @@ def quant_out(variant: int, input: torch.Tensor, importance: torch.Tensor | None
     have = output_scale.numel() * output_scale.element_size()
     if have < need:
         raise ValueError(f"output_scale holds {have} bytes, the scale layout needs {need}")
-    imp_ptr = None
-    if variant == _lib.VARIANT_WEIGHTED:
-        if importance.dtype != torch.float32:
-            importance = importance.float()
-        if not importance.is_contiguous():
-            importance = importance.contiguous()
-        imp_ptr = importance.data_ptr()
+    return m, n, physical_n
+
+
+def _importance_ptr(variant: int, importance: torch.Tensor | None):
+    """(pointer or None, tensor kept alive until the launch is enqueued)."""
+    if variant != _lib.VARIANT_WEIGHTED:
+        return None, None
+    if importance.dtype != torch.float32:
+        importance = importance.float()
+    if not importance.is_contiguous():
+        importance = importance.contiguous()
+    return importance.data_ptr(), importance
+
+
+def _raise(st: int, what: str) -> None:
+    if st < 0 and st in (-2, -5):
+        raise ValueError(_lib.status_string(st))
+    _lib.check(st, what)
+
+
+def quant_out(variant: int, input: torch.Tensor, importance: torch.Tensor | None, input_scale: torch.Tensor,
+              is_sf_swizzled_layout: bool, output: torch.Tensor, output_scale: torch.Tensor,
+              lower: int, upper: int, impl: int = 0) -> None:
+    """Validate, then launch on the current stream of input.device.  Writes output / output_scale in place."""
+    _check_common(input, input_scale)
+    if not input.is_contiguous():
+        input = input.contiguous()
+    m, n, physical_n = _check_outputs(input, is_sf_swizzled_layout, output, output_scale)
+    imp_ptr, _keep = _importance_ptr(variant, importance)
     if m == 0 or physical_n == 0:
         return
     args = (impl, variant, input.data_ptr(), _lib.dtype_code(input.dtype), imp_ptr, input_scale.data_ptr(),
@@ -78,6 +95,40 @@ def quant_out(variant: int, input: torch.Tensor, importance: torch.Tensor | None
     else:  # launch with the tensor's device current
         with torch.cuda.device(input.device):
             st = _lib.lib().nvfp4_quant_launch_impl(*args)
-    if st < 0 and st in (-2, -5):
-        raise ValueError(_lib.status_string(st))
-    _lib.check(st, "nvfp4_quant_launch")
+    _raise(st, "nvfp4_quant_launch")
+
+
+_fused_scratch: dict = {}
+
+
+def quant_fused_out(variant: int, input: torch.Tensor, importance: torch.Tensor | None, fp8_max: float,
+                    is_sf_swizzled_layout: bool, output: torch.Tensor, output_scale: torch.Tensor,
+                    lower: int, upper: int) -> torch.Tensor | None:
+    """Global scale and sweep in ONE launch (the tensor's blocks stay in registers across a grid-wide wait).
+    Returns a float32 [2] CUDA tensor (global_scale, 1 / global_scale), or None when the tensor does not fit the
+    resident grid of the device, in which case nothing was launched and the caller uses the two-launch path."""
+    if not isinstance(input, torch.Tensor) or input.ndim != 2:
+        raise ValueError(f"input must be 2D [num_row, dim], got {tuple(getattr(input, 'shape', ()))}")
+    if input.shape[-1] % BLOCK_SIZE != 0:
+        raise ValueError(f"input.shape[-1] must be divisible by {BLOCK_SIZE}")
+    if not input.is_cuda:
+        raise ValueError("input must be a CUDA tensor: these kernels have no CPU path")
+    if not input.is_contiguous():
+        input = input.contiguous()
+    m, n, physical_n = _check_outputs(input, is_sf_swizzled_layout, output, output_scale)
+    if m == 0 or n == 0:
+        raise ValueError("the global scale of an empty tensor is undefined")
+    imp_ptr, _keep = _importance_ptr(variant, importance)
+    key = (input.device, torch.cuda.current_stream(input.device).cuda_stream)
+    if key not in _fused_scratch:
+        _fused_scratch[key] = torch.zeros(4, dtype=torch.int32, device=input.device)
+    gs = torch.empty(2, dtype=torch.float32, device=input.device)
+    with torch.cuda.device(input.device):
+        st = _lib.lib().nvfp4_quant_fused_launch(
+            variant, input.data_ptr(), _lib.dtype_code(input.dtype), imp_ptr, float(fp8_max), gs.data_ptr(),
+            _fused_scratch[key].data_ptr(), output.data_ptr(), output_scale.data_ptr(), m, n, physical_n,
+            lower, upper, 1 if is_sf_swizzled_layout else 0, _lib.current_stream_ptr(input.device))
+    if st == _lib.ERR_TOO_LARGE:
+        return None
+    _raise(st, "nvfp4_quant_fused_launch")
+    return gs

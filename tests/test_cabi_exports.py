@@ -91,3 +91,26 @@ def test_global_scale_rejects_bad_arguments(L):
     assert f(P, 0, -1, 448.0, P, P, None) == -2
     assert f(P, 0, 16, 448.0, None, P, None) == -1
     assert f(P + 2, 0, 16, 448.0, P, P, None) == -4
+
+
+def test_fused_launch_rejects_bad_arguments_before_launching(L):
+    f = L.nvfp4_quant_fused_launch
+    P = 0x1000  # fake, aligned, never dereferenced: validation fails first
+    ok = [0, P, 0, None, 256.0, P, P, P, P, 4, 64, 64, -3, 7, 1, None]
+
+    def call(**kw):
+        a = list(ok)
+        for i, v in kw.items():
+            a[int(i[1:])] = v
+        return f(*a)
+
+    assert call(a0=2) == -3            # the amax variant has no fused form
+    assert call(a2=5) == -3            # dtype
+    assert call(a10=60) == -2          # n not a multiple of 16
+    assert call(a11=48) == -2          # padded_n < n
+    assert call(a12=7, a13=-3) == -5   # empty window
+    assert call(a4=0.0) == -5          # fp8_max must be positive
+    assert call(a9=0) == -2            # an empty tensor has no maximum
+    assert call(a5=None) == -1         # null outputs
+    assert call(a0=1) == -1            # weighted without importance
+    assert call(a1=P + 2) == -4        # misaligned input

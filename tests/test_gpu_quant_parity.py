@@ -59,7 +59,7 @@ def test_cuda_matches_oracle_bit_for_bit(cuda_lib, oracle, name):
     idx = util.logical_scale_index(m, blocks, c["swizzled"])
     pad = np.ones(want_scales.size, dtype=bool)
     pad[idx] = False
-    for impl in (0, 1, 2, 3):
+    for impl in (0, 1, 2, 3, 5):
         codes, scales, intact = _run_cuda(c, gs_inv, impl)
         assert intact, f"impl {impl} wrote outside its buffers"
         assert np.array_equal(codes, want_codes), f"impl {impl}: {(codes != want_codes).sum()} code bytes differ"
@@ -361,3 +361,103 @@ def test_randomized_differential_against_oracle(cuda_lib, oracle):
         assert intact, tag
         assert np.array_equal(codes, want_codes), tag
         assert np.array_equal(scales[idx], want_scales[idx]), tag
+
+
+def _two_launch(x, fp8_max, importance, swizzled, padded_n, lower=None, upper=None):
+    import nvfp4quant_test_b200.kernels as K
+    from nvfp4quant_test_b200 import helper as H
+
+    gs, gs_inv = H.get_nvfp4_global_scale(x, fp8_max)
+    if importance is None:
+        q, s = K.scalesweep_mse_nvfp4_quant_impl(x, gs_inv, swizzled, padded_n)
+    else:
+        kw = {} if lower is None else {"lower_bound": lower, "upper_bound": upper}
+        q, s = K.scalesweep_weighted_mse_nvfp4_quant_impl(x, importance, gs_inv, swizzled, padded_n, **kw)
+    return q, s, gs, gs_inv
+
+
+@pytest.mark.parametrize("shape,dtype,weighted,swizzled,padded_n", [
+    ((1, 4096), torch.bfloat16, False, True, None),
+    ((1, 14336), torch.bfloat16, False, True, None),
+    ((16, 8192), torch.bfloat16, False, True, None),
+    ((130, 208), torch.bfloat16, False, True, 256),
+    ((33, 64), torch.float16, False, False, None),
+    ((16, 128), torch.float32, False, True, None),
+    ((257, 1024), torch.bfloat16, True, False, None),
+    ((128, 8192), torch.bfloat16, True, True, None),
+    ((300, 8192), torch.bfloat16, False, True, None),     # close to the largest tensor one launch takes
+    ((1024, 8192), torch.bfloat16, False, True, None),    # too large for one launch: the wrapper issues two
+])
+def test_fused_global_scale_and_sweep_equals_two_launches(cuda_lib, shape, dtype, weighted, swizzled, padded_n):
+    """One cooperative launch computing the tensor-wide scale and the sweep must give the bytes, the scale bytes
+    and the two fp32 scale values of get_nvfp4_global_scale followed by the quantizer."""
+    import nvfp4quant_test_b200.kernels as K
+
+    x = C._laplace(shape, 60 + shape[0], dtype).cuda()
+    imp = C._importance("random", shape[1]).cuda() if weighted else None
+    want = _two_launch(x, 256.0, imp, swizzled, padded_n)
+    for _ in range(2):      # twice in a row: the scratch must come back zeroed
+        got = K.scalesweep_nvfp4_quant_with_global_scale(x, 256.0, imp, swizzled, padded_n)
+        torch.cuda.synchronize()
+        status = torch.zeros(1, dtype=torch.int32).numpy()
+        assert cuda_lib.nvfp4_quant_fused_last_status(None, status.ctypes.data) == 0 and status[0] == 0
+        assert torch.equal(got[0], want[0])
+        assert torch.equal(got[1].view(torch.uint8), want[1].view(torch.uint8))
+        assert got[2].item() == want[2].item() and got[3].item() == want[3].item()
+
+
+def test_fused_edge_values_and_window(cuda_lib):
+    """NaN / inf / all-zero tensors and a custom weighted window through the fused launch."""
+    import nvfp4quant_test_b200.kernels as K
+
+    for x in (C._edge_rows(torch.bfloat16).cuda(), torch.zeros((4, 64), dtype=torch.bfloat16, device="cuda"),
+              C._gauss((8, 256), 3).cuda()):
+        for imp, lo, up in ((None, None, None), (C._importance("ramp", x.shape[1]).cuda(), -2, 3)):
+            want = _two_launch(x, 448.0, imp, True, None, lo, up)
+            kw = {} if lo is None else {"lower_bound": lo, "upper_bound": up}
+            got = K.scalesweep_nvfp4_quant_with_global_scale(x, 448.0, imp, True, None, **kw)
+            assert torch.equal(got[0], want[0])
+            assert torch.equal(got[1].view(torch.uint8), want[1].view(torch.uint8))
+            for g, w in ((got[2], want[2]), (got[3], want[3])):
+                assert torch.equal(g.view(torch.int32), w.view(torch.int32))      # NaN-safe bit comparison
+
+
+def test_fused_launch_rejects_and_reports(cuda_lib):
+    from nvfp4quant_test_b200 import _lib
+
+    x = C._gauss((2048, 8192), 5).cuda()
+    codes = torch.empty((2048, 4096), dtype=torch.uint8, device="cuda")
+    scales = torch.empty((2048, 512), dtype=torch.uint8, device="cuda")
+    gs = torch.empty(2, dtype=torch.float32, device="cuda")
+    scratch = torch.zeros(4, dtype=torch.int32, device="cuda")
+    args = [0, x.data_ptr(), 0, None, 256.0, gs.data_ptr(), scratch.data_ptr(), codes.data_ptr(), scales.data_ptr(),
+            2048, 8192, 8192, -3, 7, 1, None]
+    assert cuda_lib.nvfp4_quant_fused_launch(*args) == _lib.ERR_TOO_LARGE          # nothing launched
+    args[0] = 2                                                                     # amax variant: not covered
+    assert cuda_lib.nvfp4_quant_fused_launch(*args) < 0
+    args[0], args[9] = 0, 16
+    args[5] = None
+    assert cuda_lib.nvfp4_quant_fused_launch(*args) < 0                             # null output
+    torch.cuda.synchronize()
+    assert int(scratch.abs().sum()) == 0
+
+
+def test_fused_launch_records_into_a_cuda_graph(cuda_lib):
+    import nvfp4quant_test_b200.kernels as K
+
+    x = C._gauss((16, 4096), 77).cuda()
+    want = _two_launch(x, 256.0, None, True, None)
+    side = torch.cuda.Stream()
+    side.wait_stream(torch.cuda.current_stream())
+    with torch.cuda.stream(side):
+        K.scalesweep_nvfp4_quant_with_global_scale(x, 256.0)
+    torch.cuda.current_stream().wait_stream(side)
+    graph = torch.cuda.CUDAGraph()
+    with torch.cuda.graph(graph):
+        got = K.scalesweep_nvfp4_quant_with_global_scale(x, 256.0)
+    for _ in range(3):
+        got[0].zero_()
+        graph.replay()
+        torch.cuda.synchronize()
+        assert torch.equal(got[0], want[0]) and torch.equal(got[1].view(torch.uint8), want[1].view(torch.uint8))
+        assert got[3].item() == want[3].item()
