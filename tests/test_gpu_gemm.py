@@ -308,3 +308,50 @@ def test_gemm_skinny_is_default_for_decode_batches(cuda_lib):
     finally:
         cuda_lib.nvfp4_gemm_force_path(0)
     assert torch.equal(auto, forced)
+
+
+def test_gemm_randomized_shapes_all_kernels(cuda_lib):
+    """Seeded random shapes with random codes and scale bytes: the tile and pair kernels (paths 1, 2, 3, 4, 6) must
+    agree bit for bit, the skinny kernel with one K range too; with a random number of K ranges it must stay
+    within one bf16 ulp of them (floor: 2^-16 of the largest output, for sums that cancel)."""
+    import random
+
+    import nvfp4quant_test_b200.kernels as K
+    from nvfp4quant_test_b200.kernels.kernel_gemm import gemm_last_status
+
+    rng = random.Random(20240607)
+    gen = torch.Generator(device="cuda")
+    gen.manual_seed(7)
+    try:
+        for _ in range(40):
+            M = rng.choice([1, 3, 16, 17, 32, 33, 64, 100, 128, 129, 256, 300])
+            N = rng.choice([8, 64, 136, 200, 256, 520, 1024, 4096])
+            K_ = 64 * rng.choice([1, 2, 3, 5, 8, 16, 33, 64])
+            qa = torch.randint(0, 256, (M, K_ // 2), dtype=torch.uint8, device="cuda", generator=gen)
+            qb = torch.randint(0, 256, (N, K_ // 2), dtype=torch.uint8, device="cuda", generator=gen)
+            kp = (K_ // 16 + 3) // 4 * 4
+            sa = torch.randint(0x28, 0x48, ((M + 127) // 128 * 128, kp), dtype=torch.uint8, device="cuda", generator=gen)
+            sb = torch.randint(0x28, 0x48, ((N + 127) // 128 * 128, kp), dtype=torch.uint8, device="cuda", generator=gen)
+            alpha = torch.rand(1, device="cuda", generator=gen) + 0.5
+            runs = [(1, 0), (2, 0), (3, 0), (4, 0), (6, 0), (0, 0)]
+            if M <= 128:
+                runs += [(5, 1), (5, rng.choice([2, 3, 4, 8]))]
+            outs = {}
+            for path, ranks in runs:
+                assert cuda_lib.nvfp4_gemm_force_path(path) == 0 and cuda_lib.nvfp4_gemm_tune(ranks, -1) == 0
+                out = torch.full((M, N), float("nan"), dtype=torch.bfloat16, device="cuda")
+                K.nvfp4_scaled_mm(qa, qb, sa.view(torch.float8_e4m3fn), sb.view(torch.float8_e4m3fn), alpha,
+                                  torch.bfloat16, out=out)
+                outs[(path, ranks)] = out
+            assert gemm_last_status() == 0
+            ref = outs[(1, 0)]
+            assert not torch.isnan(ref).any()
+            for key in ((2, 0), (3, 0), (4, 0), (6, 0), (5, 1)):
+                if key in outs:
+                    assert torch.equal(outs[key], ref), (M, N, K_, key)
+            tol = torch.maximum(ref.float().abs() * 2.0 ** -7, ref.float().abs().max() * 2.0 ** -16)
+            for key, out in outs.items():
+                assert bool(((out.float() - ref.float()).abs() <= tol).all()), (M, N, K_, key)
+    finally:
+        cuda_lib.nvfp4_gemm_force_path(0)
+        cuda_lib.nvfp4_gemm_tune(0, -1)
