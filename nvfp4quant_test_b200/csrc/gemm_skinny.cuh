@@ -1,0 +1,375 @@
+// Decode-sized kernel of the NVFP4 GEMM: weights on the MMA rows, K ranges across a thread-block cluster.
+#pragma once
+
+#include "gemm_pair.cuh"
+
+namespace nvfp4 {
+namespace gemm {
+
+// =============================================================================================
+// Skinny variant for decode-sized batches (M <= 128).  The roles of the operands are swapped: the 128 rows of
+// the MMA are WEIGHT rows and its N dimension is the (padded) token count BT = 16 / 32 / 64 / 128, so the tensor
+// cores spend BT/128 of the time a 128-row token tile of mostly padding would take and the kernel is a
+// stream of the weights.  One CTA owns 128 weight rows and one K range; the K ranges of a tile are the CTAs
+// of one thread-block cluster (1..8), which lets a shape with few weight tiles still pull from every SM.
+// The partial accumulators are combined by a reduce-scatter through distributed shared memory: the token
+// columns are dealt out to the ranks, every rank writes its partial tile to its own shared memory and sends
+// each other rank the columns that rank owns with one bulk copy (cp.async.bulk shared::cta -> shared::cluster,
+// completion counted on the receiver's mbarrier); the owner adds the partials in ascending rank order, applies
+// alpha and stores bf16.  One kernel, no workspace, and the result does not depend on timing.  Every copy has
+// one destination CTA (no multicast).
+// =============================================================================================
+namespace skinny {
+
+using pair::cluster_ctarank;
+using pair::cluster_sync_all;
+using pair::map_to_cta;
+
+constexpr int kMaxStages = 8;
+// TMEM: accumulator in columns 0..BT-1, then two scale sets of 32 columns
+
+template <int BT>
+struct SkinnyCfg {
+    static constexpr int kWBytes = 128 * kBKBytes;     // 128 weight rows x 256 codes
+    static constexpr int kXBytes = BT * kBKBytes;      // BT token rows x 256 codes
+    static constexpr int kSfBytes = 2048;              // one 128-row scale group x 16 blocks, for each operand
+    static constexpr int kStageBytes = kWBytes + kXBytes + 2 * kSfBytes;
+    static constexpr int kSfCol = BT <= 64 ? 64 : 128; // scale set 0: weights +0..15, tokens +16..31; set 1: +32
+    static constexpr int kTmemCols = BT <= 64 ? 128 : 256;
+    static constexpr int kMaxStages = (BT <= 64) ? 8 : 6;
+    static_assert(kStageBytes % 1024 == 0, "stage alignment for the 128-byte swizzle");
+    static_assert(BT % 16 == 0 && BT >= 16 && BT <= 128, "token tile");
+};
+
+__device__ __forceinline__ void tc_ld_32x32b_x16(uint32_t taddr, uint32_t v[16]) {
+    asm volatile(
+        "tcgen05.ld.sync.aligned.32x32b.x16.b32 "
+        "{%0, %1, %2, %3, %4, %5, %6, %7, %8, %9, %10, %11, %12, %13, %14, %15}, [%16];"
+        : "=r"(v[0]), "=r"(v[1]), "=r"(v[2]), "=r"(v[3]), "=r"(v[4]), "=r"(v[5]), "=r"(v[6]), "=r"(v[7]), "=r"(v[8]),
+          "=r"(v[9]), "=r"(v[10]), "=r"(v[11]), "=r"(v[12]), "=r"(v[13]), "=r"(v[14]), "=r"(v[15])
+        : "r"(taddr)
+        : "memory");
+}
+// shared memory of this CTA -> shared memory of a CTA of the cluster; the bytes are counted on the receiver's barrier
+__device__ __forceinline__ void bulk_copy_to_cta(uint32_t dst_cluster, uint32_t src_cta, uint32_t bytes, uint32_t bar_cluster) {
+    asm volatile("cp.async.bulk.shared::cluster.shared::cta.mbarrier::complete_tx::bytes [%0], [%1], %2, [%3];" ::"r"(dst_cluster),
+                 "r"(src_cta), "r"(bytes), "r"(bar_cluster)
+                 : "memory");
+}
+
+struct SkinnyParams {
+    const uint8_t* sfx;   // token scales (group 0 of the tiled layout)
+    const uint8_t* sfw;   // weight scales
+    const float* alpha;
+    __nv_bfloat16* out;   // [M, N]
+    int M, N, K;
+    int64_t sf_group_stride;
+    int k_tiles_per_rank;
+    int stages;
+};
+
+template <int BT>
+__global__ void __launch_bounds__(kThreads)
+skinny_kernel(const __grid_constant__ CUtensorMap tmap_w, const __grid_constant__ CUtensorMap tmap_x, const SkinnyParams p) {
+    using C = SkinnyCfg<BT>;
+    extern __shared__ uint8_t smem_raw[];
+    const uint32_t raw_addr = smem_u32(smem_raw);
+    const uint32_t base = (raw_addr + 1023u) & ~1023u;
+    uint8_t* aligned = smem_raw + (base - raw_addr);
+    const int nstages = p.stages;
+    uint64_t* bars = reinterpret_cast<uint64_t*>(aligned + nstages * C::kStageBytes);
+    const uint32_t bar_base = smem_u32(bars);
+    auto full_bar = [&](int s) { return bar_base + 8u * s; };
+    auto empty_bar = [&](int s) { return bar_base + 8u * (kMaxStages + s); };
+    const uint32_t tfull_bar = bar_base + 8u * (2 * kMaxStages);
+    const uint32_t recv_bar = bar_base + 8u * (2 * kMaxStages + 1);   // partials from the other ranks have landed
+    volatile uint32_t* tmem_slot = reinterpret_cast<volatile uint32_t*>(bars + 2 * kMaxStages + 2);
+    volatile uint32_t* abort_flag = tmem_slot + 1;
+
+    const int warp = __shfl_sync(0xffffffffu, threadIdx.x >> 5, 0);
+    const int lane = threadIdx.x & 31;
+    const uint32_t rank = cluster_ctarank();
+    uint32_t ranks;
+    asm volatile("mov.u32 %0, %%cluster_nctarank;" : "=r"(ranks));
+    const int nt = blockIdx.x / ranks;                  // 128-row weight tile (clusters run along x)
+    // reduce-scatter: token column c belongs to rank c / cols_per_rank
+    const uint32_t m_cols = static_cast<uint32_t>(min(p.M, BT));
+    const uint32_t cols_per_rank = (m_cols + ranks - 1) / ranks;
+    const uint32_t my_first = rank * cols_per_rank;
+    const uint32_t my_cols = my_first < m_cols ? min(cols_per_rank, m_cols - my_first) : 0u;
+
+    if (threadIdx.x == 0) {
+        for (int s = 0; s < nstages; ++s) {
+            mbar_init(full_bar(s), 1);
+            mbar_init(empty_bar(s), 1);
+        }
+        mbar_init(tfull_bar, 1);
+        mbar_init(recv_bar, 1);
+        *abort_flag = 0;
+        asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+        asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
+        // (ranks - 1) senders x my columns x 128 rows x 4 bytes; armed before any rank can send (they send after
+        // the cluster barrier below the main loop)
+        if (ranks > 1 && my_cols > 0) mbar_expect_tx(recv_bar, (ranks - 1) * my_cols * 512u);
+    }
+    if (warp == 1) {
+        asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(
+                         smem_u32(const_cast<uint32_t*>(tmem_slot))),
+                     "r"(C::kTmemCols)
+                     : "memory");
+        asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;" ::: "memory");
+    }
+    tc_fence_before();
+    __syncthreads();
+    tc_fence_after();
+    const uint32_t tmem_base = *tmem_slot;
+
+    const int k_tiles = (p.K + kBK - 1) / kBK;
+    const int kt_begin = static_cast<int>(rank) * p.k_tiles_per_rank;
+    const int kcount = max(0, min(k_tiles, kt_begin + p.k_tiles_per_rank) - kt_begin);   // host: never 0
+
+    if (warp == 0) {
+        // ------------------------------------------------------------------ producer
+        const bool issuer = elect_one();
+        if (issuer) {
+            asm volatile("prefetch.tensormap [%0];" ::"l"(&tmap_w) : "memory");
+            asm volatile("prefetch.tensormap [%0];" ::"l"(&tmap_x) : "memory");
+        }
+        int stage = 0;
+        uint32_t phase = 0;
+        for (int i = 0; i < kcount; ++i) {
+            const int kt = kt_begin + i;
+            if (!mbar_wait_warp(empty_bar(stage), phase ^ 1u, abort_flag, (7u << 24) | kt)) break;
+            const int kb_count = min(4, (p.K - kt * kBK + 63) / 64);
+            const uint32_t sf_bytes = 512u * kb_count;
+            const uint32_t sbase = base + stage * C::kStageBytes;
+            if (issuer) {
+                mbar_expect_tx(full_bar(stage), C::kWBytes + C::kXBytes + 2 * sf_bytes);
+                tma_load_2d(sbase, &tmap_w, kt * kBKBytes, nt * 128, full_bar(stage));
+                tma_load_2d(sbase + C::kWBytes, &tmap_x, kt * kBKBytes, 0, full_bar(stage));
+                bulk_load_1d(sbase + C::kWBytes + C::kXBytes,
+                             p.sfw + static_cast<int64_t>(nt) * p.sf_group_stride + static_cast<int64_t>(kt) * 2048, sf_bytes,
+                             full_bar(stage));
+                bulk_load_1d(sbase + C::kWBytes + C::kXBytes + C::kSfBytes, p.sfx + static_cast<int64_t>(kt) * 2048, sf_bytes,
+                             full_bar(stage));
+            }
+            __syncwarp();
+            if (++stage == nstages) {
+                stage = 0;
+                phase ^= 1u;
+            }
+        }
+    } else if (warp == 1) {
+        // ------------------------------------------------------------------ MMA issuer
+        const bool issuer = elect_one();
+        constexpr uint32_t idesc = instr_desc<BT>();
+        int stage = 0;
+        uint32_t phase = 0;
+        bool ok = true;
+        for (int i = 0; i < kcount; ++i) {
+            if (!(ok = mbar_wait_warp(full_bar(stage), phase, abort_flag, (8u << 24) | i))) break;
+            tc_fence_after();
+            const int kb_count = min(4, (p.K - (kt_begin + i) * kBK + 63) / 64);
+            const uint32_t sbase = base + stage * C::kStageBytes;
+            const uint32_t w_lo = ((sbase & 0x3ffffu) >> 4) | (1u << 16);
+            const uint32_t x_lo = w_lo + (C::kWBytes >> 4);
+            const uint32_t sfw_lo = ((sbase + C::kWBytes + C::kXBytes) & 0x3ffffu) >> 4;
+            const uint32_t sfx_lo = sfw_lo + (C::kSfBytes >> 4);
+            const uint32_t sfw_t = tmem_base + C::kSfCol + (i & 1) * 32;
+            const uint32_t sfx_t = sfw_t + 16;
+            if (issuer) {
+                for (int kb = 0; kb < kb_count; ++kb) {
+                    tc_cp_lohi(sfw_t + 4 * kb, sfw_lo + 32 * kb);
+                    tc_cp_lohi(sfx_t + 4 * kb, sfx_lo + 32 * kb);
+                }
+                for (int kb = 0; kb < kb_count; ++kb)
+                    tc_mma_lohi(tmem_base, w_lo + 2 * kb, x_lo + 2 * kb, idesc, sfw_t + 4 * kb, sfx_t + 4 * kb,
+                                (i > 0 || kb > 0) ? 1u : 0u);
+                tc_commit(empty_bar(stage));
+            }
+            __syncwarp();
+            if (++stage == nstages) {
+                stage = 0;
+                phase ^= 1u;
+            }
+        }
+        if (ok && issuer) tc_commit(tfull_bar);
+        __syncwarp();
+    }
+
+    // ---------------------------------------------------------------------- epilogue
+    // Thread (sub-partition sp, lane) of warps 2..5 owns weight row nt*128 + 32*sp + lane; TMEM column m of its
+    // lane is the partial sum for token m.  Columns are handled 16 at a time to keep the register count low.
+    const int sp = warp & 3;
+    const int n_local = sp * 32 + lane;
+    const int n = nt * 128 + n_local;
+    bool have = false;
+    if (warp >= 2) {
+        bool ok = mbar_wait(tfull_bar, 0, abort_flag, (9u << 24) | nt);
+        have = __shfl_sync(0xffffffffu, ok ? 1 : 0, 0) != 0;
+        if (have) tc_fence_after();
+    }
+    const uint32_t t_lane = tmem_base + (static_cast<uint32_t>(sp * 32) << 16);
+    if (ranks == 1) {
+        if (warp >= 2 && have) {
+            const float alpha = __ldg(p.alpha);
+#pragma unroll 1
+            for (int c = 0; c < BT / 16 && c * 16 < p.M; ++c) {
+                uint32_t v[16];
+                tc_ld_32x32b_x16(t_lane + c * 16, v);
+                tc_ld_wait();
+                if (n < p.N) {
+#pragma unroll
+                    for (int e = 0; e < 16; ++e)
+                        if (c * 16 + e < p.M)
+                            p.out[static_cast<int64_t>(c * 16 + e) * p.N + n] =
+                                __float2bfloat16_rn(__fmul_rn(__uint_as_float(v[e]), alpha));
+                }
+            }
+        }
+    } else {
+        // The ring is idle once the accumulator is complete (all copies landed and were consumed), so it is reused:
+        // `part` [token column][128 rows] fp32 = this rank's partial tile, `recv` [sending rank][owned column][128 rows].
+        float* part = reinterpret_cast<float*>(aligned);
+        float* recv = part + BT * 128;
+        if (warp >= 2 && have) {
+#pragma unroll 1
+            for (int c = 0; c < BT / 16 && c * 16 < p.M; ++c) {
+                uint32_t v[16];
+                tc_ld_32x32b_x16(t_lane + c * 16, v);
+                tc_ld_wait();
+#pragma unroll
+                for (int e = 0; e < 16; ++e)
+                    if (c * 16 + e < p.M) part[(c * 16 + e) * 128 + n_local] = __uint_as_float(v[e]);
+            }
+            asm volatile("fence.proxy.async.shared::cta;" ::: "memory");   // the bulk copies below read `part`
+        }
+        // every rank has left its main loop: the `recv` areas may be written
+        cluster_sync_all();
+        if (warp == 2 && have && elect_one()) {
+            for (uint32_t o = 0; o < ranks; ++o) {
+                const uint32_t first = o * cols_per_rank;
+                if (o == rank || first >= m_cols) continue;
+                const uint32_t cols = min(cols_per_rank, m_cols - first);
+                bulk_copy_to_cta(map_to_cta(smem_u32(recv + (rank * cols_per_rank) * 128), o), smem_u32(part + first * 128),
+                                 cols * 512u, map_to_cta(recv_bar, o));
+            }
+        }
+        if (warp >= 2 && have && my_cols > 0) {
+            bool ok = mbar_wait(recv_bar, 0, abort_flag, (10u << 24) | nt);
+            ok = __shfl_sync(0xffffffffu, ok ? 1 : 0, 0) != 0;
+            if (ok && n < p.N) {
+                const float alpha = __ldg(p.alpha);
+                // this rank's own partial sits in `recv` terms at part[my_first ..]; eight columns at a time so that
+                // the shared-memory loads of one rank's partials are in flight together
+                const float* own = part + my_first * 128 + n_local;
+                __nv_bfloat16* dst = p.out + static_cast<int64_t>(my_first) * p.N + n;
+                for (uint32_t c0 = 0; c0 < my_cols; c0 += 8) {
+                    float acc[8];
+#pragma unroll
+                    for (int j = 0; j < 8; ++j) acc[j] = 0.0f;
+                    for (uint32_t r = 0; r < ranks; ++r) {
+                        const float* src = (r == rank) ? own : recv + (r * cols_per_rank) * 128 + n_local;
+                        float v[8];
+#pragma unroll
+                        for (int j = 0; j < 8; ++j) v[j] = (c0 + j < my_cols) ? src[(c0 + j) * 128] : 0.0f;
+#pragma unroll
+                        for (int j = 0; j < 8; ++j) acc[j] = r == 0 ? v[j] : __fadd_rn(acc[j], v[j]);
+                    }
+#pragma unroll
+                    for (int j = 0; j < 8; ++j)
+                        if (c0 + j < my_cols)
+                            dst[static_cast<int64_t>(c0 + j) * p.N] = __float2bfloat16_rn(__fmul_rn(acc[j], alpha));
+                }
+            }
+        }
+        // no rank may leave while another still copies out of its `part`
+        cluster_sync_all();
+    }
+
+    // ---------------------------------------------------------------------- teardown
+    if (*abort_flag) {
+        const uint64_t t0 = global_timer_ns();
+        while (global_timer_ns() - t0 < 200000ull) __nanosleep(1000);
+    }
+    tc_fence_before();
+    __syncthreads();
+    if (warp == 1) {
+        tc_fence_after();
+        asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(tmem_base), "r"(C::kTmemCols) : "memory");
+    }
+}
+
+// K ranges per weight tile: the largest power of two that keeps every CTA of the grid resident at once (one per
+// SM), with at least two K stages each and at most 8 (the portable cluster size).  With small token tiles two
+// CTAs fit on an SM, and where the K range is already cut, cutting it once more measured faster (16 x 8192 x 8192:
+// 12.2 -> 11.4 us); going from one range to two when the tiles already cover most SMs did not (16 x 14336 x 4096:
+// 10.5 -> 11.1 us).  Cluster sizes that are not a power of two measured slower (6144 x 4096: 3 ranges 11.9 us,
+// 2 ranges 8.0 us).
+static int choose_ranks(int n_tiles, int k_tiles, int sms, int forced, int bt) {
+    int r = 1;
+    if (forced > 0) {
+        r = forced;
+    } else {
+        while (r < 8 && n_tiles * (2 * r) <= sms) r *= 2;
+        if (bt <= 32 && r >= 2 && r < 8 && n_tiles * (2 * r) <= 2 * sms - 40 && k_tiles / (2 * r) >= 4) r *= 2;
+    }
+    if (r > 8) r = 8;
+    while (r > 1 && r > k_tiles / 2) --r;
+    return r;
+}
+
+template <int BT>
+static int launch_skinny(const uint8_t* x, const uint8_t* w, const GemmParams& g, int forced_ranks, cudaStream_t stream) {
+    using C = SkinnyCfg<BT>;
+    CUtensorMap mw, mx;
+    int st = make_operand_map(&mw, w, g.N, g.K / 2, 128);
+    if (st == NVFP4_OK) st = make_operand_map(&mx, x, g.M, g.K / 2, BT);
+    if (st != NVFP4_OK) return st;
+    int dev = 0, sms = 148;
+    cudaGetDevice(&dev);
+    cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev);
+    const int n_tiles = (g.N + 127) / 128;
+    const int k_tiles = (g.K + kBK - 1) / kBK;
+    int ranks = choose_ranks(n_tiles, k_tiles, sms, forced_ranks, BT);
+    SkinnyParams p;
+    p.sfx = g.sfa;
+    p.sfw = g.sfb;
+    p.alpha = g.alpha;
+    p.out = g.out;
+    p.M = g.M;
+    p.N = g.N;
+    p.K = g.K;
+    p.sf_group_stride = g.sf_group_stride;
+    p.k_tiles_per_rank = (k_tiles + ranks - 1) / ranks;
+    ranks = (k_tiles + p.k_tiles_per_rank - 1) / p.k_tiles_per_rank;   // no empty range
+    // one CTA per SM with a deep ring when the whole grid is resident at once, else two CTAs per SM
+    p.stages = (n_tiles * ranks <= sms) ? C::kMaxStages : 4;
+    if (p.stages > p.k_tiles_per_rank) p.stages = p.k_tiles_per_rank < 2 ? 2 : p.k_tiles_per_rank;
+    // the ring doubles as the reduce-scatter buffers: the partial tile plus one slot per rank of the owned columns
+    while (ranks > 1 && (2 * BT + 8) * 512 > p.stages * C::kStageBytes) ++p.stages;
+    if (p.stages > C::kMaxStages) return NVFP4_ERR_UNSUPPORTED;
+    const int smem = p.stages * C::kStageBytes + 1024 + 256;
+    cudaError_t e = cudaFuncSetAttribute(skinny_kernel<BT>, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                                         C::kMaxStages * C::kStageBytes + 1024 + 256);
+    if (e != cudaSuccess) return static_cast<int>(e);
+    cudaLaunchConfig_t cfg = {};
+    cfg.gridDim = dim3(n_tiles * ranks, 1, 1);
+    cfg.blockDim = dim3(kThreads, 1, 1);
+    cfg.dynamicSmemBytes = smem;
+    cfg.stream = stream;
+    cudaLaunchAttribute attr[1];
+    attr[0].id = cudaLaunchAttributeClusterDimension;
+    attr[0].val.clusterDim.x = ranks;
+    attr[0].val.clusterDim.y = 1;
+    attr[0].val.clusterDim.z = 1;
+    cfg.attrs = attr;
+    cfg.numAttrs = 1;
+    e = cudaLaunchKernelEx(&cfg, skinny_kernel<BT>, mw, mx, p);
+    return static_cast<int>(e);
+}
+
+}  // namespace skinny
+
+}  // namespace gemm
+}  // namespace nvfp4
