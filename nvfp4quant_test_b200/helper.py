@@ -21,15 +21,17 @@ def get_nvfp4_global_scale(x: torch.Tensor, FP8_MAX: float = FP8_E4M3_MAX_NVFP4)
     """(global_scale, global_scale_inv) as 0-dim float32 CUDA tensors; amax(|x|)/(6*FP8_MAX) and its reciprocal."""
     if not x.is_cuda:
         raise ValueError("x must be a CUDA tensor")
-    x = x.contiguous()
-    key = (x.device, torch.cuda.current_stream(x.device).cuda_stream)
-    if key not in _scratch:
-        _scratch[key] = torch.zeros(2, dtype=torch.int32, device=x.device)
+    if not x.is_contiguous():
+        x = x.contiguous()
+    stream = _lib.current_stream_ptr(x.device)
+    key = (x.device, stream)
+    scratch = _scratch.get(key)
+    if scratch is None:
+        scratch = _scratch[key] = torch.zeros(2, dtype=torch.int32, device=x.device)
     out = torch.empty(2, dtype=torch.float32, device=x.device)
-    with torch.cuda.device(x.device):
+    with _lib.device_guard(x.device):
         st = _lib.lib().nvfp4_global_scale_launch(x.data_ptr(), _lib.dtype_code(x.dtype), x.numel(), float(FP8_MAX),
-                                                  out.data_ptr(), _scratch[key].data_ptr(),
-                                                  _lib.current_stream_ptr(x.device))
+                                                  out.data_ptr(), scratch.data_ptr(), stream)
     _lib.check(st, "nvfp4_global_scale_launch")
     return out[0], out[1]
 
@@ -41,9 +43,10 @@ def channel_square_norm(x: torch.Tensor) -> torch.Tensor:
         raise ValueError("x must be a 2D CUDA tensor")
     if x.shape[1] % 4:
         raise ValueError("x.shape[1] must be divisible by 4")
-    x = x.contiguous()
+    if not x.is_contiguous():
+        x = x.contiguous()
     out = torch.empty((1, x.shape[1]), dtype=torch.float32, device=x.device)
-    with torch.cuda.device(x.device):
+    with _lib.device_guard(x.device):
         st = _lib.lib().nvfp4_channel_sqnorm_launch(x.data_ptr(), _lib.dtype_code(x.dtype), x.shape[0], x.shape[1],
                                                     out.data_ptr(), _lib.current_stream_ptr(x.device))
     _lib.check(st, "nvfp4_channel_sqnorm_launch")

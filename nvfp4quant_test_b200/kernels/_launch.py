@@ -90,11 +90,8 @@ def quant_out(variant: int, input: torch.Tensor, importance: torch.Tensor | None
     args = (impl, variant, input.data_ptr(), _lib.dtype_code(input.dtype), imp_ptr, input_scale.data_ptr(),
             output.data_ptr(), output_scale.data_ptr(), m, n, physical_n, lower, upper,
             1 if is_sf_swizzled_layout else 0, _lib.current_stream_ptr(input.device))
-    if input.device.index == torch.cuda.current_device():
+    with _lib.device_guard(input.device):   # launch with the tensor's device current
         st = _lib.lib().nvfp4_quant_launch_impl(*args)
-    else:  # launch with the tensor's device current
-        with torch.cuda.device(input.device):
-            st = _lib.lib().nvfp4_quant_launch_impl(*args)
     _raise(st, "nvfp4_quant_launch")
 
 
@@ -119,15 +116,16 @@ def quant_fused_out(variant: int, input: torch.Tensor, importance: torch.Tensor 
     if m == 0 or n == 0:
         raise ValueError("the global scale of an empty tensor is undefined")
     imp_ptr, _keep = _importance_ptr(variant, importance)
-    key = (input.device, torch.cuda.current_stream(input.device).cuda_stream)
+    stream = _lib.current_stream_ptr(input.device)
+    key = (input.device, stream)
     if key not in _fused_scratch:
         _fused_scratch[key] = torch.zeros(4, dtype=torch.int32, device=input.device)
     gs = torch.empty(2, dtype=torch.float32, device=input.device)
-    with torch.cuda.device(input.device):
+    with _lib.device_guard(input.device):
         st = _lib.lib().nvfp4_quant_fused_launch(
             variant, input.data_ptr(), _lib.dtype_code(input.dtype), imp_ptr, float(fp8_max), gs.data_ptr(),
             _fused_scratch[key].data_ptr(), output.data_ptr(), output_scale.data_ptr(), m, n, physical_n,
-            lower, upper, 1 if is_sf_swizzled_layout else 0, _lib.current_stream_ptr(input.device))
+            lower, upper, 1 if is_sf_swizzled_layout else 0, stream)
     if st == _lib.ERR_TOO_LARGE:
         return None
     _raise(st, "nvfp4_quant_fused_launch")

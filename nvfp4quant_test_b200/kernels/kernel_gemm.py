@@ -36,8 +36,12 @@ def nvfp4_scaled_mm(a: torch.Tensor, b: torch.Tensor, block_scale_a: torch.Tenso
         raise ValueError(f"K must be a multiple of 64 (quantize with padded_n to pad it), got {k}")
     if alpha.dtype != torch.float32 or alpha.numel() < 1:
         raise ValueError("alpha must be a float32 tensor with one element")
-    a, b = a.contiguous(), b.contiguous()
-    sfa, sfb = block_scale_a.contiguous(), block_scale_b.contiguous()
+    if not a.is_contiguous():
+        a = a.contiguous()
+    if not b.is_contiguous():
+        b = b.contiguous()
+    sfa = block_scale_a if block_scale_a.is_contiguous() else block_scale_a.contiguous()
+    sfb = block_scale_b if block_scale_b.is_contiguous() else block_scale_b.contiguous()
     for name, sf, rows in (("block_scale_a", sfa, m), ("block_scale_b", sfb, n)):
         have = sf.numel() * sf.element_size()
         if have < _scale_bytes(rows, k):
@@ -51,7 +55,7 @@ def nvfp4_scaled_mm(a: torch.Tensor, b: torch.Tensor, block_scale_a: torch.Tenso
     L = _lib.lib()
     ws_bytes = L.nvfp4_gemm_workspace_bytes(m, n, k)
     ws = torch.empty(ws_bytes, dtype=torch.uint8, device=a.device) if ws_bytes else None   # caching allocator
-    with torch.cuda.device(a.device):
+    with _lib.device_guard(a.device):
         st = L.nvfp4_gemm_launch(a.data_ptr(), b.data_ptr(), sfa.data_ptr(), sfb.data_ptr(),
                                  alpha.data_ptr(), out.data_ptr(), m, n, k,
                                  ws.data_ptr() if ws is not None else None, ws_bytes,
