@@ -117,6 +117,21 @@ def test_llama_stack_layer_partition():
     assert list(layers_for_rank(32, 5, 8)) == [20, 21, 22, 23]
 
 
+def test_llama_stack_weight_scale_slots():
+    """The alphas of a layer come from one multiplication per input width: the global scales of the matrices that
+    share an input are stacked in dict order and every matrix knows its slot."""
+    from nvfp4quant_test_b200.llama_stack import LAYER_SHAPES, stack_weight_scales
+
+    qlayer = {name: (torch.empty((n, k // 2), dtype=torch.uint8), None, torch.tensor(float(i + 1)))
+              for i, (name, (n, k)) in enumerate(LAYER_SHAPES.items())}
+    ws = stack_weight_scales(qlayer)
+    assert sorted(ws) == [4096, 14336]
+    vec, slots = ws[4096]
+    assert list(slots) == ["q", "k", "v", "o", "gate", "up"] and vec.tolist() == [1.0, 2.0, 3.0, 4.0, 5.0, 6.0]
+    vec, slots = ws[14336]
+    assert slots == {"down": 0} and vec.tolist() == [7.0] and vec.dtype == torch.float32
+
+
 def test_storage_round_trip(tmp_path):
     """codes + tiled scales + global scale survive save/load bit for bit; linear <-> tiled converters invert."""
     from nvfp4quant_test_b200 import storage
