@@ -28,15 +28,26 @@ __global__ void __launch_bounds__(kGsThreads) global_scale_kernel(const void* x,
     const uint4* xv = static_cast<const uint4*>(x);
     const int64_t stride = static_cast<int64_t>(gridDim.x) * kGsThreads;
     uint32_t acc = 0;
-    for (int64_t i = static_cast<int64_t>(blockIdx.x) * kGsThreads + threadIdx.x; i < nvec; i += stride) {
-        const uint4 q = __ldg(xv + i);
+    auto fold = [&](const uint4& q) {
         if (DT == NVFP4_DT_F32) {
             acc = max(acc, max(max(q.x & 0x7fffffffu, q.y & 0x7fffffffu), max(q.z & 0x7fffffffu, q.w & 0x7fffffffu)));
         } else {
             acc = umax2x16(acc, umax2x16(umax2x16(q.x & 0x7fff7fffu, q.y & 0x7fff7fffu),
                                          umax2x16(q.z & 0x7fff7fffu, q.w & 0x7fff7fffu)));
         }
+    };
+    int64_t i = static_cast<int64_t>(blockIdx.x) * kGsThreads + threadIdx.x;
+    // four independent 16-byte loads in flight per thread: with one, a resident grid holds too few bytes in
+    // flight to cover the HBM latency
+    for (; i + 3 * stride < nvec; i += 4 * stride) {
+        const uint4 q0 = __ldg(xv + i), q1 = __ldg(xv + i + stride), q2 = __ldg(xv + i + 2 * stride),
+                    q3 = __ldg(xv + i + 3 * stride);
+        fold(q0);
+        fold(q1);
+        fold(q2);
+        fold(q3);
     }
+    for (; i < nvec; i += stride) fold(__ldg(xv + i));
     // ragged tail (numel not a multiple of the vector width): first threads of block 0
     if (blockIdx.x == 0) {
         const int64_t t = nvec * kPerVec + threadIdx.x;

@@ -3,8 +3,9 @@
 // This is the importance vector the reference feeds to the weighted quantizer ("the importance scores for
 // weight tensors are based on the activation input-channel square norm, and vice versa", README.md:11 of
 // efsotr/nvfp4quant_test; its driver script is not published, torch's `(x.float() ** 2).sum(0)` is the
-// obvious spelling).  One pass over x; the summation order is fixed (rows strided by 8 per thread, then a
-// fixed tree over the 8 row groups), so the result is reproducible run to run.
+// obvious spelling).  One pass over x; the summation order is fixed (rows strided by 64 per thread in ascending
+// order, then a fixed binary tree over the 64 row groups), so the result is reproducible run to run.  A CTA owns
+// 16 columns, so an 8192-column batch runs on 512 CTAs with eight loads in flight per thread.
 #include <cuda_bf16.h>
 #include <cuda_fp16.h>
 
@@ -13,8 +14,11 @@
 namespace nvfp4 {
 namespace {
 
-constexpr int kSqThreads = 256;   // 8 row groups x 32 lanes
-constexpr int kSqCols = 128;      // columns per CTA: 4 per lane
+constexpr int kSqThreads = 256;   // 64 row groups x 4 lanes
+constexpr int kSqLanes = 4;       // lanes side by side on one row segment
+constexpr int kSqGroups = kSqThreads / kSqLanes;
+constexpr int kSqCols = 4 * kSqLanes;   // columns per CTA: 4 per lane (32 bytes of bf16 per row: one DRAM sector)
+constexpr int kSqUnroll = 8;      // independent loads in flight per thread
 
 template <int DT>
 __device__ __forceinline__ void load4(const void* x, int64_t elem, float v[4]) {
@@ -36,27 +40,43 @@ __device__ __forceinline__ void load4(const void* x, int64_t elem, float v[4]) {
 
 template <int DT>
 __global__ void __launch_bounds__(kSqThreads) channel_sqnorm_kernel(const void* x, int64_t m, int64_t n, float* out) {
-    const int lane = threadIdx.x & 31, rg = threadIdx.x >> 5;
+    const int lane = threadIdx.x % kSqLanes, rg = threadIdx.x / kSqLanes;
     const int64_t col = static_cast<int64_t>(blockIdx.x) * kSqCols + lane * 4;
     float acc[4] = {0.0f, 0.0f, 0.0f, 0.0f};
     if (col < n) {   // n % 4 == 0 is required, so a lane's 4 columns are all inside or all outside
-        for (int64_t r = rg; r < m; r += 8) {
+        int64_t r = rg;
+        // rows rg, rg + 64, ... in ascending order; kSqUnroll loads are issued before the first is consumed
+        for (; r + (kSqUnroll - 1) * kSqGroups < m; r += kSqUnroll * kSqGroups) {
+            float v[kSqUnroll][4];
+#pragma unroll
+            for (int u = 0; u < kSqUnroll; ++u) load4<DT>(x, (r + u * kSqGroups) * n + col, v[u]);
+#pragma unroll
+            for (int u = 0; u < kSqUnroll; ++u)
+#pragma unroll
+                for (int k = 0; k < 4; ++k) acc[k] = __fmaf_rn(v[u][k], v[u][k], acc[k]);
+        }
+        for (; r < m; r += kSqGroups) {
             float v[4];
             load4<DT>(x, r * n + col, v);
 #pragma unroll
             for (int k = 0; k < 4; ++k) acc[k] = __fmaf_rn(v[k], v[k], acc[k]);
         }
     }
-    __shared__ float part[8][kSqCols];
+    // fixed binary tree over the 64 row groups
+    __shared__ float part[kSqGroups][kSqCols];
 #pragma unroll
     for (int k = 0; k < 4; ++k) part[rg][lane * 4 + k] = acc[k];
     __syncthreads();
+    for (int half = kSqGroups / 2; half >= 1; half >>= 1) {
+        for (int idx = threadIdx.x; idx < half * kSqCols; idx += kSqThreads) {
+            const int g = idx / kSqCols, c = idx - g * kSqCols;
+            part[g][c] = __fadd_rn(part[g][c], part[g + half][c]);
+        }
+        __syncthreads();
+    }
     if (threadIdx.x < kSqCols) {
-        const int c = threadIdx.x;
-        const float s = __fadd_rn(__fadd_rn(__fadd_rn(part[0][c], part[1][c]), __fadd_rn(part[2][c], part[3][c])),
-                                  __fadd_rn(__fadd_rn(part[4][c], part[5][c]), __fadd_rn(part[6][c], part[7][c])));
-        const int64_t oc = static_cast<int64_t>(blockIdx.x) * kSqCols + c;
-        if (oc < n) out[oc] = s;
+        const int64_t oc = static_cast<int64_t>(blockIdx.x) * kSqCols + threadIdx.x;
+        if (oc < n) out[oc] = part[0][threadIdx.x];
     }
 }
 
