@@ -70,11 +70,13 @@ int nvfp4_quant_launch(int variant, const void* x, int x_dtype, const float* imp
                        const float* gs_inv, uint8_t* codes, uint8_t* scales, int64_t m, int64_t n,
                        int64_t padded_n, int lower, int upper, int swizzled, void* stream);
 
-/* Same, choosing the kernel body: 0 = default (3, or 5 when a quarter or more of the scale layout's rows are
- * padding), 1 = scalar (one candidate at a time, the plainest transcription), 2 = one candidate per trip with
+/* Same, choosing the kernel body: 0 = default (5 when a quarter or more of the scale layout's rows are
+ * padding, else 6 where it applies, else 3), 1 = scalar (one candidate at a time, the plainest transcription), 2 = one candidate per trip with
  * packed multiplies and the mixed-precision subtract, 3 = two candidates per trip sharing one f32x2 FMA chain,
- * 5 = 3 with warps that hold only padding rows skipping the sweep (4 is the fused form, which has its own entry
- * point below).  All give identical bytes; exposed for testing and timing. */
+ * 5 = 3 with warps that hold only padding rows skipping the sweep, 6 = 3 on a two-dimensional grid (row =
+ * blockIdx.x, uniform over the CTA; taken by default when the row is a whole number of 256-block chunks wide,
+ * otherwise 6 means 3).  4 is the fused form, which has its own entry point below.  All give identical bytes;
+ * exposed for testing and timing. */
 int nvfp4_quant_launch_impl(int impl, int variant, const void* x, int x_dtype, const float* importance,
                             const float* gs_inv, uint8_t* codes, uint8_t* scales, int64_t m, int64_t n,
                             int64_t padded_n, int lower, int upper, int swizzled, void* stream);

@@ -338,10 +338,18 @@ quant_kernel(const QuantParams p) {
     }
     __syncthreads();
 
-    const int64_t id = static_cast<int64_t>(blockIdx.x) * kThreads + threadIdx.x;
-    const bool in_range = id < p.total;
+    // Body 6 = body 3 with a two-dimensional grid: blockIdx.x is the row, blockIdx.y the 256-block column chunk.
+    // The row is then uniform over the CTA, so the division below, the row part of the addresses and most of the
+    // tiled scale offset leave the per-thread instruction stream.  Used when the slot grid is a whole number of
+    // chunks wide (e.g. 512 blocks per row at 8192 columns); narrow or ragged widths keep the flat numbering.
+    constexpr bool GRID2D = IMPL == 6;
+    const int64_t id = GRID2D ? 0 : static_cast<int64_t>(blockIdx.x) * kThreads + threadIdx.x;
+    const bool in_range = GRID2D ? true : id < p.total;
     int64_t row = 0, col = 0;
-    if (in_range) {
+    if (GRID2D) {
+        row = blockIdx.x;
+        col = static_cast<int64_t>(blockIdx.y) * kThreads + threadIdx.x;
+    } else if (in_range) {
         if (p.total <= 0x7fffffffLL) {  // 32-bit division is several times cheaper than the 64-bit one
             const uint32_t r32 = static_cast<uint32_t>(id) / static_cast<uint32_t>(p.width);
             row = r32;
@@ -485,6 +493,9 @@ cudaError_t launch_impl(int impl, const QuantParams& p, cudaStream_t stream) {
         quant_kernel<DT, VARIANT, 2><<<static_cast<unsigned>(grid), kThreads, 0, stream>>>(p);
     else if (impl == 5 || (impl == 0 && (p.rows - p.m) * 4 >= p.rows))
         quant_kernel<DT, VARIANT, 5><<<static_cast<unsigned>(grid), kThreads, 0, stream>>>(p);
+    else if ((impl == 6 || impl == 0) && (p.width % kThreads) == 0 && p.width / kThreads <= 65535 && p.rows <= 0x7fffffffLL)
+        quant_kernel<DT, VARIANT, 6><<<dim3(static_cast<unsigned>(p.rows), static_cast<unsigned>(p.width / kThreads)), kThreads, 0,
+                                       stream>>>(p);
     else
         quant_kernel<DT, VARIANT, 3><<<static_cast<unsigned>(grid), kThreads, 0, stream>>>(p);
     return cudaGetLastError();
@@ -508,7 +519,7 @@ extern "C" int nvfp4_quant_launch_impl(int impl, int variant, const void* x, int
     using namespace nvfp4;
     if (variant < NVFP4_VARIANT_MSE || variant > NVFP4_VARIANT_AMAX) return NVFP4_ERR_BAD_ENUM;
     if (x_dtype < NVFP4_DT_BF16 || x_dtype > NVFP4_DT_F32) return NVFP4_ERR_BAD_ENUM;
-    if (impl < 0 || impl > 5 || impl == 4) return NVFP4_ERR_BAD_ENUM;
+    if (impl < 0 || impl > 6 || impl == 4) return NVFP4_ERR_BAD_ENUM;
     if (m < 0 || n < 0 || (n % kBlock) != 0 || (padded_n % kBlock) != 0 || padded_n < n) return NVFP4_ERR_BAD_SHAPE;
     if (variant != NVFP4_VARIANT_AMAX && (upper < lower || upper - lower + 1 > 64)) return NVFP4_ERR_BAD_RANGE;
     QuantParams p;
