@@ -37,7 +37,7 @@ NOMINAL_FP4_TFLOPS = 9000.0
 # dram__bytes_read.sum + dram__bytes_write.sum of one quant_kernel launch on this workload (ncu capture,
 # summarised under profiles/): 134.23 MB read + 21.57 MB written (the rest of the 37.7 MB of
 # outputs is still in L2 when the kernel ends).
-NCU_TRAFFIC_BYTES_PER_LAUNCH = 155_797_248
+NCU_TRAFFIC_BYTES_PER_LAUNCH = 156_999_168
 
 
 def measured_peaks():
