@@ -75,8 +75,10 @@ int nvfp4_quant_launch(int variant, const void* x, int x_dtype, const float* imp
  * packed multiplies and the mixed-precision subtract, 3 = two candidates per trip sharing one f32x2 FMA chain,
  * 5 = 3 with warps that hold only padding rows skipping the sweep, 6 = 3 on a two-dimensional grid (row =
  * blockIdx.x, uniform over the CTA; taken by default when the row is a whole number of 256-block chunks wide,
- * otherwise 6 means 3).  4 is the fused form, which has its own entry point below.  All give identical bytes;
- * exposed for testing and timing. */
+ * otherwise 6 means 3), 7 = 6 with the reference's candidate count (11 unweighted, 16 weighted) compiled in and
+ * the sweep unrolled (default for the unweighted sweep with the reference's window; other windows make it 6).
+ * 4 is the fused form, which has its own entry point below.  All give identical bytes; exposed for testing and
+ * timing. */
 int nvfp4_quant_launch_impl(int impl, int variant, const void* x, int x_dtype, const float* importance,
                             const float* gs_inv, uint8_t* codes, uint8_t* scales, int64_t m, int64_t n,
                             int64_t padded_n, int lower, int upper, int swizzled, void* stream);

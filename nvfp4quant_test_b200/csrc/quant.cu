@@ -47,8 +47,8 @@ constexpr int kThreads = 256;
 #define NVFP4_QUANT_MIN_BLOCKS_W2D 4
 #endif
 constexpr int min_blocks(int variant, int impl) {
-    return variant == NVFP4_VARIANT_WEIGHTED ? (impl == 6 ? NVFP4_QUANT_MIN_BLOCKS_W2D : 4)
-           : (impl == 6 && variant == NVFP4_VARIANT_MSE) ? NVFP4_QUANT_MIN_BLOCKS_2D
+    return variant == NVFP4_VARIANT_WEIGHTED ? (impl >= 6 ? NVFP4_QUANT_MIN_BLOCKS_W2D : 4)
+           : (impl >= 6 && variant == NVFP4_VARIANT_MSE) ? NVFP4_QUANT_MIN_BLOCKS_2D
                                                          : NVFP4_QUANT_MIN_BLOCKS;
 }
 
@@ -189,16 +189,18 @@ __device__ __forceinline__ void e2m1_diff_pair(uint64_t x2, float& d0, float& d1
         : "l"(x2));
 }
 
-template <bool WEIGHTED>
-__device__ __forceinline__ uint32_t sweep_paired(const float v[16], const float w[16], int first_idx, int ncand,
+// NC > 0: the candidate count is the compile-time constant NC and the trips are unrolled (the table index and the
+// loop control leave the instruction stream); NC = 0: `ncand` at run time, one rolled loop.
+template <bool WEIGHTED, int NC = 0>
+__device__ __forceinline__ uint32_t sweep_paired(const float v[16], const float w[16], int first_idx, int ncand_rt,
                                                  const float4* tab) {
+    const int ncand = NC > 0 ? NC : ncand_rt;
     uint64_t vp[8];  // (v[2p], v[2p+1])
 #pragma unroll
     for (int p = 0; p < 8; ++p) vp[p] = pack_f32x2(v[2 * p], v[2 * p + 1]);
     float best = __int_as_float(0x7f800000);
     uint32_t best_raw = 0;
-#pragma unroll 1
-    for (int i = 0; i + 1 < ncand; i += 2) {
+    auto trip = [&](int i) {
         const float4 ea = tab[first_idx + i], eb = tab[first_idx + i + 1];
         const uint32_t raw_a = __float_as_uint(ea.w), raw_b = __float_as_uint(eb.w);
         const uint64_t inv_a = pack_f32x2(ea.x, ea.y), inv_b = pack_f32x2(eb.x, eb.y);
@@ -239,6 +241,13 @@ __device__ __forceinline__ uint32_t sweep_paired(const float v[16], const float 
             best = err_b;
             best_raw = raw_b;
         }
+    };
+    if (NC > 0) {
+#pragma unroll
+        for (int i = 0; i + 1 < NC; i += 2) trip(i);
+    } else {
+#pragma unroll 1
+        for (int i = 0; i + 1 < ncand; i += 2) trip(i);
     }
     if (ncand & 1) {  // odd count: the last candidate alone, scalar chain
         const float4 e4 = tab[first_idx + ncand - 1];
@@ -355,7 +364,7 @@ quant_kernel(const QuantParams p) {
     // The row is then uniform over the CTA, so the division below, the row part of the addresses and most of the
     // tiled scale offset leave the per-thread instruction stream.  Used when the slot grid is a whole number of
     // chunks wide (e.g. 512 blocks per row at 8192 columns); narrow or ragged widths keep the flat numbering.
-    constexpr bool GRID2D = IMPL == 6;
+    constexpr bool GRID2D = IMPL == 6 || IMPL == 7;   // 7 = 6 with the reference's candidate count compiled in
     const int64_t id = GRID2D ? 0 : static_cast<int64_t>(blockIdx.x) * kThreads + threadIdx.x;
     const bool in_range = GRID2D ? true : id < p.total;
     int64_t row = 0, col = 0;
@@ -463,6 +472,7 @@ quant_kernel(const QuantParams p) {
         const int first_idx = min(max(base_raw + p.lower, -kTabPad), 127) + kTabPad;
         sbyte = (IMPL == 1)   ? sweep_scalar<W>(v, w, first_idx, p.ncand, tab)
                 : (IMPL == 2) ? sweep_single<W>(v, w, first_idx, p.ncand, tab)
+                : (IMPL == 7) ? sweep_paired<W, W ? 16 : 11>(v, w, first_idx, p.ncand, tab)
                               : sweep_paired<W>(v, w, first_idx, p.ncand, tab);
         // sbyte is 0 only when no candidate had a comparable (non-NaN, < inf) error: 1/0 as the reference computes it
         inv = (sbyte == 0) ? div_full(1.0f, 0.0f) : tab[sbyte + kTabPad].x;
@@ -506,9 +516,16 @@ cudaError_t launch_impl(int impl, const QuantParams& p, cudaStream_t stream) {
         quant_kernel<DT, VARIANT, 2><<<static_cast<unsigned>(grid), kThreads, 0, stream>>>(p);
     else if (impl == 5 || (impl == 0 && (p.rows - p.m) * 4 >= p.rows))
         quant_kernel<DT, VARIANT, 5><<<static_cast<unsigned>(grid), kThreads, 0, stream>>>(p);
-    else if ((impl == 6 || impl == 0) && (p.width % kThreads) == 0 && p.width / kThreads <= 65535 && p.rows <= 0x7fffffffLL)
-        quant_kernel<DT, VARIANT, 6><<<dim3(static_cast<unsigned>(p.rows), static_cast<unsigned>(p.width / kThreads)), kThreads, 0,
-                                       stream>>>(p);
+    else if ((impl == 6 || impl == 7 || impl == 0) && (p.width % kThreads) == 0 && p.width / kThreads <= 65535 &&
+             p.rows <= 0x7fffffffLL) {
+        const dim3 grid2(static_cast<unsigned>(p.rows), static_cast<unsigned>(p.width / kThreads));
+        // the reference's own windows (11 candidates unweighted, 16 weighted) have an unrolled instantiation
+        const bool fixed = VARIANT == NVFP4_VARIANT_MSE ? p.ncand == 11 : VARIANT == NVFP4_VARIANT_WEIGHTED && p.ncand == 16;
+        if (fixed && (impl == 7 || (impl == 0 && VARIANT == NVFP4_VARIANT_MSE)))
+            quant_kernel<DT, VARIANT, 7><<<grid2, kThreads, 0, stream>>>(p);
+        else
+            quant_kernel<DT, VARIANT, 6><<<grid2, kThreads, 0, stream>>>(p);
+    }
     else
         quant_kernel<DT, VARIANT, 3><<<static_cast<unsigned>(grid), kThreads, 0, stream>>>(p);
     return cudaGetLastError();
@@ -532,7 +549,7 @@ extern "C" int nvfp4_quant_launch_impl(int impl, int variant, const void* x, int
     using namespace nvfp4;
     if (variant < NVFP4_VARIANT_MSE || variant > NVFP4_VARIANT_AMAX) return NVFP4_ERR_BAD_ENUM;
     if (x_dtype < NVFP4_DT_BF16 || x_dtype > NVFP4_DT_F32) return NVFP4_ERR_BAD_ENUM;
-    if (impl < 0 || impl > 6 || impl == 4) return NVFP4_ERR_BAD_ENUM;
+    if (impl < 0 || impl > 7 || impl == 4) return NVFP4_ERR_BAD_ENUM;
     if (m < 0 || n < 0 || (n % kBlock) != 0 || (padded_n % kBlock) != 0 || padded_n < n) return NVFP4_ERR_BAD_SHAPE;
     if (variant != NVFP4_VARIANT_AMAX && (upper < lower || upper - lower + 1 > 64)) return NVFP4_ERR_BAD_RANGE;
     QuantParams p;

@@ -59,7 +59,7 @@ def test_cuda_matches_oracle_bit_for_bit(cuda_lib, oracle, name):
     idx = util.logical_scale_index(m, blocks, c["swizzled"])
     pad = np.ones(want_scales.size, dtype=bool)
     pad[idx] = False
-    for impl in (0, 1, 2, 3, 5, 6):
+    for impl in (0, 1, 2, 3, 5, 6, 7):
         codes, scales, intact = _run_cuda(c, gs_inv, impl)
         assert intact, f"impl {impl} wrote outside its buffers"
         assert np.array_equal(codes, want_codes), f"impl {impl}: {(codes != want_codes).sum()} code bytes differ"
