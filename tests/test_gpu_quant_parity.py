@@ -461,3 +461,27 @@ def test_fused_launch_records_into_a_cuda_graph(cuda_lib):
         torch.cuda.synchronize()
         assert torch.equal(got[0], want[0]) and torch.equal(got[1].view(torch.uint8), want[1].view(torch.uint8))
         assert got[3].item() == want[3].item()
+
+
+@pytest.mark.parametrize("m,n,padded_n,swizzled", [(3, 4096, None, True), (129, 4096, None, False), (5, 4080, 4096, True),
+                                                    (2, 8192, None, False), (130, 8176, 8192, True)])
+def test_two_dimensional_grid_bodies(cuda_lib, oracle, m, n, padded_n, swizzled):
+    """Rows that are a whole number of 256-block chunks wide take the two-dimensional grid (bodies 6 and 7); cover
+    both layouts, ragged row counts, K padding and a non-default window there, against the oracle and the flat body."""
+    x = C._laplace((m, n), 3000 + m + n)
+    gs_inv = C.global_scale_cpu(x, 256.0)[1]
+    P = padded_n or n
+    for variant, imp, lo, up in (("mse", None, None, None), ("weighted", C._importance("random", n), None, None),
+                                 ("mse", None, -2, 4), ("amax", None, None, None)):
+        c = dict(x=x, variant=variant, importance=imp, swizzled=swizzled, padded_n=padded_n, lower=lo, upper=up)
+        idx = util.logical_scale_index(m, P // 16, swizzled)
+        flat_codes, flat_scales, ok = _run_cuda(c, gs_inv, 3)
+        assert ok
+        if variant != "amax":
+            want_codes, want_scales = util.oracle_quant_case(oracle, c, gs_inv)
+            assert np.array_equal(flat_codes, want_codes) and np.array_equal(flat_scales[idx], want_scales[idx])
+        for impl in (0, 6, 7):
+            codes, scales, intact = _run_cuda(c, gs_inv, impl)
+            assert intact, f"{variant} impl {impl} wrote outside its buffers"
+            assert np.array_equal(codes, flat_codes), f"{variant} impl {impl}"
+            assert np.array_equal(scales, flat_scales), f"{variant} impl {impl}"
