@@ -112,34 +112,23 @@ skinny_kernel(const __grid_constant__ CUtensorMap tmap_w, const __grid_constant_
         // the cluster barrier below the main loop)
         if (ranks > 1 && my_cols > 0) mbar_expect_tx(recv_bar, (ranks - 1) * my_cols * 512u);
     }
-    if (warp == 1) {
-        asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(
-                         smem_u32(const_cast<uint32_t*>(tmem_slot))),
-                     "r"(C::kTmemCols)
-                     : "memory");
-        asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;" ::: "memory");
-    }
-    tc_fence_before();
-    __syncthreads();
-    tc_fence_after();
-    const uint32_t tmem_base = *tmem_slot;
-
     const int k_tiles = (p.K + kBK - 1) / kBK;
     const int kt_begin = static_cast<int>(rank) * p.k_tiles_per_rank;
     const int kcount = max(0, min(k_tiles, kt_begin + p.k_tiles_per_rank) - kt_begin);   // host: never 0
 
-    if (warp == 0) {
-        // ------------------------------------------------------------------ producer
+    // Producer state (warp 0).  The first ring-full of copies is issued BEFORE the CTA-wide barrier of the prologue:
+    // the copies need the mbarriers (initialised by this warp's thread 0 just above) but neither TMEM nor the other
+    // warps, so the first HBM round trip overlaps the TMEM allocation and the barrier instead of following them.
+    int p_stage = 0, p_next = 0;
+    uint32_t p_phase = 0;
+    bool p_ok = true;
+    auto produce = [&](int end) {
         const bool issuer = elect_one();
-        if (issuer) {
-            asm volatile("prefetch.tensormap [%0];" ::"l"(&tmap_w) : "memory");
-            asm volatile("prefetch.tensormap [%0];" ::"l"(&tmap_x) : "memory");
-        }
-        int stage = 0;
-        uint32_t phase = 0;
-        for (int i = 0; i < kcount; ++i) {
-            const int kt = kt_begin + i;
-            if (!mbar_wait_warp(empty_bar(stage), phase ^ 1u, abort_flag, (7u << 24) | kt)) break;
+        for (; p_ok && p_next < end; ++p_next) {
+            const int kt = kt_begin + p_next;
+            const int stage = p_stage;
+            const uint32_t phase = p_phase;
+            if (!(p_ok = mbar_wait_warp(empty_bar(stage), phase ^ 1u, abort_flag, (7u << 24) | kt))) break;
             const int kb_count = min(4, (p.K - kt * kBK + 63) / 64);
             const uint32_t sf_bytes = 512u * kb_count;
             const uint32_t sbase = base + stage * C::kStageBytes;
@@ -154,11 +143,35 @@ skinny_kernel(const __grid_constant__ CUtensorMap tmap_w, const __grid_constant_
                              full_bar(stage));
             }
             __syncwarp();
-            if (++stage == nstages) {
-                stage = 0;
-                phase ^= 1u;
+            if (++p_stage == nstages) {
+                p_stage = 0;
+                p_phase ^= 1u;
             }
         }
+    };
+    if (warp == 0) {
+        __syncwarp();   // thread 0's barrier initialisation above, before any lane of this warp uses the barriers
+        if (elect_one()) {
+            asm volatile("prefetch.tensormap [%0];" ::"l"(&tmap_w) : "memory");
+            asm volatile("prefetch.tensormap [%0];" ::"l"(&tmap_x) : "memory");
+        }
+        produce(min(kcount, nstages));
+    }
+    if (warp == 1) {
+        asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(
+                         smem_u32(const_cast<uint32_t*>(tmem_slot))),
+                     "r"(C::kTmemCols)
+                     : "memory");
+        asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;" ::: "memory");
+    }
+    tc_fence_before();
+    __syncthreads();
+    tc_fence_after();
+    const uint32_t tmem_base = *tmem_slot;
+
+    if (warp == 0) {
+        // ------------------------------------------------------------------ producer, stages after the first ring-full
+        produce(kcount);
     } else if (warp == 1) {
         // ------------------------------------------------------------------ MMA issuer
         const bool issuer = elect_one();
