@@ -96,10 +96,18 @@ gemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant__ 
                      : "memory");
         asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;" ::: "memory");
     }
+    // The producer warp initialised the mbarriers itself (thread 0) and needs neither TMEM nor the other warps, so it
+    // only ARRIVES on the prologue barrier and starts its copies at once; the first HBM round trip then overlaps the
+    // TMEM allocation.  Warps 1..5 wait for the arrival (barrier initialisation, TMEM address).
     tc_fence_before();
-    __syncthreads();
+    if (warp == 0) {
+        __syncwarp();
+        asm volatile("bar.arrive 1, %0;" ::"n"(kThreads) : "memory");
+    } else {
+        asm volatile("bar.sync 1, %0;" ::"n"(kThreads) : "memory");
+    }
     tc_fence_after();
-    const uint32_t tmem_base = *tmem_slot;
+    const uint32_t tmem_base = *tmem_slot;   // meaningful in warps 1..5 only
 
     const int m_tiles = (p.M + kBM - 1) / kBM;
     const int n_tiles = (p.N + BN - 1) / BN;
