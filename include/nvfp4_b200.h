@@ -161,6 +161,10 @@ size_t nvfp4_gemm_workspace_bytes(int64_t M, int64_t N, int64_t K);
  * 6 = 128x64 tiles.  Paths 1-4 and 6 give identical bits; path 5 adds its K ranges in a fixed order and
  * agrees with them to fp32 rounding before the bf16 store (identical bits with one range). */
 int nvfp4_gemm_force_path(int path);
+/* Testing hook: *path = the kernel nvfp4_gemm_launch would take for this shape on a GPU with `sms` SMs under the
+ * current force / tune settings (numbering of nvfp4_gemm_force_path), *k_ranges = the skinny kernel's cluster
+ * size (1 for the other kernels).  Host arithmetic only: no GPU is touched. */
+int nvfp4_gemm_plan(int64_t M, int64_t N, int64_t K, int sms, int* path, int* k_ranges);
 /* Testing hook (process-wide): number of K ranges (0 = by shape) and K-loop rotation (-1 = by shape, 0 = off,
  * 1 = on) of the single-CTA tile kernels; while path 5 is forced, k_splits is the cluster size (K ranges per
  * weight tile, 1..8) of the skinny kernel instead.  nvfp4_gemm_workspace_bytes reflects the current setting

@@ -18,7 +18,7 @@ ERR_TOO_LARGE = -8
 EXPORTS = (
     "nvfp4_quant_launch", "nvfp4_quant_launch_impl", "nvfp4_quant_fused_launch", "nvfp4_quant_fused_last_status",
     "nvfp4_global_scale_launch", "nvfp4_channel_sqnorm_launch",
-    "nvfp4_gemm_launch", "nvfp4_gemm_workspace_bytes", "nvfp4_gemm_last_status", "nvfp4_gemm_force_path", "nvfp4_gemm_tune", "nvfp4_gemm_tune_raster",
+    "nvfp4_gemm_launch", "nvfp4_gemm_workspace_bytes", "nvfp4_gemm_last_status", "nvfp4_gemm_force_path", "nvfp4_gemm_tune", "nvfp4_gemm_tune_raster", "nvfp4_gemm_plan",
     "nvfp4_probe_div_full_table", "nvfp4_probe_amax_out_scale_table",
     "nvfp4_status_string", "nvfp4_abi_version",
 )
@@ -61,6 +61,8 @@ def lib() -> ctypes.CDLL:
         L.nvfp4_gemm_workspace_bytes.argtypes = [i64, i64, i64]
         L.nvfp4_gemm_last_status.restype = ci
         L.nvfp4_gemm_last_status.argtypes = [vp, vp]
+        L.nvfp4_gemm_plan.restype = ci
+        L.nvfp4_gemm_plan.argtypes = [i64, i64, i64, ci, vp, vp]
         L.nvfp4_gemm_tune_raster.restype = ci
         L.nvfp4_gemm_tune_raster.argtypes = [ci]
         L.nvfp4_gemm_tune.restype = ci

@@ -68,6 +68,65 @@ extern "C" int nvfp4_gemm_force_path(int path) {
     return NVFP4_OK;
 }
 
+// Kernel choice for one shape: host arithmetic only.  *path: 1 = 128x128 tiles, 2 = 128x256, 3 = pair 256x256,
+// 4 = pair 256x192, 5 = skinny, 6 = 128x64; *k_ranges: cluster size of the skinny kernel (1 for the others).
+static void plan_gemm(int64_t M, int64_t N, int64_t K, int sms, int k_splits, int* path_out, int* ranges_out) {
+    const int k_tiles_total = static_cast<int>((K + 255) / 256);
+    const int n_tiles = static_cast<int>((N + 127) / 128);
+    *ranges_out = 1;
+    // Decode-sized batches: weight rows on the MMA's 128 rows, tokens on its N dimension, K ranges across a cluster.
+    // Measured on B200 with the weights streaming from HBM: faster than every other kernel up to 32 tokens; from 33
+    // to 128 tokens only where few weight tiles meet a long K (at least 4 K ranges of at least 12 stages each, e.g.
+    // 64 x 4096 x 14336: 13.2 us against 19.4 us), because its epilogue grows with the token tile.
+    bool skinny = false;
+    if (g_gemm_force_path == 5) {
+        skinny = M <= kSkinnyMaxM;
+    } else if (g_gemm_force_path == 0 && g_gemm_force_splits == 0 && M <= kSkinnyMaxM) {
+        const int ranks = nvfp4::gemm::skinny::choose_ranks(n_tiles, k_tiles_total, sms, 0, M <= 64 ? 64 : 128);
+        skinny = M <= kSkinnyAutoM || (ranks >= 4 && k_tiles_total / ranks >= 12);
+    }
+    if (skinny) {
+        const int forced = g_gemm_force_path == 5 ? g_gemm_force_splits : 0;
+        const int bt = M <= 16 ? 16 : M <= 32 ? 32 : M <= 64 ? 64 : 128;
+        int ranks = nvfp4::gemm::skinny::choose_ranks(n_tiles, k_tiles_total, sms, forced, bt);
+        const int per = (k_tiles_total + ranks - 1) / ranks;
+        ranks = (k_tiles_total + per - 1) / per;   // no empty range
+        *path_out = 5;
+        *ranges_out = ranks;
+        return;
+    }
+    // Kernel choice by a small cost model fitted to measurements on B200: time ~ waves x cost of one tile, where a
+    // wave is 148 single-CTA tiles or 74 CTA-pair tiles.  Relative tile costs: 128x64 -> 0.45, 128x128 -> 0.7, 128x256 -> 1.0,
+    // pair 256x192 -> 0.68 (0.75 of the MMA work per SM, and its epilogue overlaps the next tile).
+    int path = g_gemm_force_path == 5 ? 0 : g_gemm_force_path;   // 0 = choose by shape
+    if (path == 0) {
+        const int64_t mt = (M + 127) / 128;
+        const double c1 = static_cast<double>((mt * ((N + 127) / 128) + 147) / 148) * 0.7;
+        const double c2 = static_cast<double>((mt * ((N + 255) / 256) + 147) / 148) * 1.0;
+        const double c4 = static_cast<double>((((M + 255) / 256) * ((N + 191) / 192) + 73) / 74) * 0.68;
+        path = (c1 <= c2) ? 1 : 2;
+        double best = c1 <= c2 ? c1 : c2;
+        if (M > 128 && N > 128 && k_splits == 1 && c4 <= best) {
+            path = 4;
+            best = c4;
+        }
+        // few, long tiles (one or two token tiles): 64 weight rows per CTA put twice as many SMs on the weight stream
+        const double c6 = static_cast<double>((mt * ((N + 63) / 64) + 147) / 148) * 0.45;
+        if (mt <= 2 && c6 < best) path = 6;
+    }
+    if (k_splits > 1 && path != 1 && path != 2 && path != 6) path = 1;
+    *path_out = path;
+}
+
+// Testing hook: the kernel nvfp4_gemm_launch would pick for this shape on a GPU with `sms` SMs (under the current
+// force / tune settings).  No GPU is touched.
+extern "C" int nvfp4_gemm_plan(int64_t M, int64_t N, int64_t K, int sms, int* path, int* k_ranges) {
+    if (!path || !k_ranges) return NVFP4_ERR_NULL_POINTER;
+    if (M <= 0 || N <= 0 || K <= 0 || (K % 64) != 0 || sms <= 0) return NVFP4_ERR_BAD_SHAPE;
+    plan_gemm(M, N, K, sms, choose_k_splits(M, N, K), path, k_ranges);
+    return NVFP4_OK;
+}
+
 extern "C" int nvfp4_gemm_launch(const uint8_t* a, const uint8_t* b, const uint8_t* sfa, const uint8_t* sfb,
                                  const float* alpha, void* out_bf16, int64_t M, int64_t N, int64_t K, void* workspace,
                                  size_t workspace_bytes, void* stream) {
@@ -101,21 +160,12 @@ extern "C" int nvfp4_gemm_launch(const uint8_t* a, const uint8_t* b, const uint8
     // default: one band over all m-tiles (band sizes 1..16 measured within noise of it on B200)
     p.raster_group = g_gemm_raster_group > 0 ? g_gemm_raster_group : (1 << 20);
     cudaStream_t s = static_cast<cudaStream_t>(stream);
-    // Decode-sized batches: weight rows on the MMA's 128 rows, tokens on its N dimension, K ranges across a cluster.
-    // Measured on B200 with the weights streaming from HBM: faster than every other kernel up to 32 tokens; from 33
-    // to 128 tokens only where few weight tiles meet a long K (at least 4 K ranges of at least 12 stages each, e.g.
-    // 64 x 4096 x 14336: 13.2 us against 19.4 us), because its epilogue grows with the token tile.
-    bool skinny = false;
-    if (g_gemm_force_path == 5) {
-        skinny = M <= kSkinnyMaxM;
-    } else if (g_gemm_force_path == 0 && g_gemm_force_splits == 0 && M <= kSkinnyMaxM) {
-        int dev = 0, sms = 148;
-        cudaGetDevice(&dev);
-        cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev);
-        const int ranks = gemm::skinny::choose_ranks(static_cast<int>((N + 127) / 128), k_tiles_total, sms, 0, M <= 64 ? 64 : 128);
-        skinny = M <= kSkinnyAutoM || (ranks >= 4 && k_tiles_total / ranks >= 12);
-    }
-    if (skinny) {
+    int dev = 0, sms = 148;
+    cudaGetDevice(&dev);
+    cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev);
+    int path = 0, ranges = 1;
+    plan_gemm(M, N, K, sms, p.k_splits, &path, &ranges);
+    if (path == 5) {
         const int forced = g_gemm_force_path == 5 ? g_gemm_force_splits : 0;
         if (M <= 16) return gemm::skinny::launch_skinny<16>(a, b, p, forced, s);
         if (M <= 32) return gemm::skinny::launch_skinny<32>(a, b, p, forced, s);
@@ -127,26 +177,6 @@ extern "C" int nvfp4_gemm_launch(const uint8_t* a, const uint8_t* b, const uint8
         if (!workspace || workspace_bytes < need) return NVFP4_ERR_WORKSPACE;
         if (reinterpret_cast<uintptr_t>(workspace) & 15) return NVFP4_ERR_MISALIGNED;
     }
-    // Kernel choice by a small cost model fitted to measurements on B200: time ~ waves x cost of one tile, where a
-    // wave is 148 single-CTA tiles or 74 CTA-pair tiles.  Relative tile costs: 128x64 -> 0.45, 128x128 -> 0.7, 128x256 -> 1.0,
-    // pair 256x192 -> 0.68 (0.75 of the MMA work per SM, and its epilogue overlaps the next tile).
-    int path = g_gemm_force_path == 5 ? 0 : g_gemm_force_path;   // 0 = choose by shape
-    if (path == 0) {
-        const int64_t mt = (M + 127) / 128;
-        const double c1 = static_cast<double>((mt * ((N + 127) / 128) + 147) / 148) * 0.7;
-        const double c2 = static_cast<double>((mt * ((N + 255) / 256) + 147) / 148) * 1.0;
-        const double c4 = static_cast<double>((((M + 255) / 256) * ((N + 191) / 192) + 73) / 74) * 0.68;
-        path = (c1 <= c2) ? 1 : 2;
-        double best = c1 <= c2 ? c1 : c2;
-        if (M > 128 && N > 128 && p.k_splits == 1 && c4 <= best) {
-            path = 4;
-            best = c4;
-        }
-        // few, long tiles (one or two token tiles): 64 weight rows per CTA put twice as many SMs on the weight stream
-        const double c6 = static_cast<double>((mt * ((N + 63) / 64) + 147) / 148) * 0.45;
-        if (mt <= 2 && c6 < best) path = 6;
-    }
-    if (p.k_splits > 1 && path != 1 && path != 2 && path != 6) path = 1;
     if (path == 3) return gemm::pair::launch_pair<256>(a, b, p, s);
     if (path == 4) return gemm::pair::launch_pair<192>(a, b, p, s);
     if (path == 2) return gemm::launch<256>(a, b, p, s);

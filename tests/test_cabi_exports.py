@@ -114,3 +114,42 @@ def test_fused_launch_rejects_bad_arguments_before_launching(L):
     assert call(a5=None) == -1         # null outputs
     assert call(a0=1) == -1            # weighted without importance
     assert call(a1=P + 2) == -4        # misaligned input
+
+
+def test_gemm_kernel_choice_by_shape(L):
+    """nvfp4_gemm_plan answers on the host which kernel a shape takes on a 148-SM GPU: the decode-sized kernel (5)
+    with its K ranges up to 32 tokens and for few-tile / long-K shapes up to 128, tile and pair kernels beyond."""
+    def plan(M, N, K, sms=148):
+        path, ranges = ctypes.c_int(-1), ctypes.c_int(-1)
+        assert L.nvfp4_gemm_plan(M, N, K, sms, ctypes.byref(path), ctypes.byref(ranges)) == 0
+        return path.value, ranges.value
+
+    assert plan(1, 4096, 4096) == (5, 4)             # 32 weight tiles x 4 ranges = 128 CTAs
+    assert plan(16, 8192, 8192) == (5, 4)            # 64 tiles: 2 ranges fill the SMs, one more cut pays (two CTAs / SM)
+    assert plan(32, 8192, 8192) == (5, 4)
+    assert plan(16, 4096, 14336) == (5, 8)
+    assert plan(16, 14336, 4096) == (5, 1)           # 112 tiles already cover most SMs
+    assert plan(16, 28672, 8192) == (5, 1)
+    assert plan(1, 512, 1024) == (5, 2)              # at least two K stages per range
+    assert plan(16, 128, 64) == (5, 1)
+    assert plan(64, 4096, 14336) == (5, 4)           # few tiles, long K: still the decode-sized kernel
+    assert plan(128, 4096, 14336) == (5, 4)
+    assert plan(64, 4096, 4096) == (6, 1)            # 128x64 tiles
+    assert plan(128, 8192, 8192) == (6, 1)
+    assert plan(128, 28672, 8192) == (2, 1)          # 128x256 tiles
+    assert plan(256, 8192, 8192)[0] in (1, 4)
+    assert plan(8192, 8192, 8192) == (4, 1)          # CTA pairs, 256x192 tiles
+    assert plan(8192, 28672, 8192) == (4, 1)
+    # forcing a kernel / K ranges is honoured, larger M than the skinny kernel takes falls back
+    try:
+        assert L.nvfp4_gemm_force_path(5) == 0 and L.nvfp4_gemm_tune(8, -1) == 0
+        assert plan(100, 1024, 8192) == (5, 8)
+        assert plan(300, 1024, 8192)[0] != 5
+        assert L.nvfp4_gemm_force_path(2) == 0 and L.nvfp4_gemm_tune(0, -1) == 0
+        assert plan(1, 4096, 4096) == (2, 1)
+    finally:
+        L.nvfp4_gemm_force_path(0)
+        L.nvfp4_gemm_tune(0, -1)
+    assert L.nvfp4_gemm_plan(1, 4096, 100, 148, None, None) < 0
+    p_, r_ = ctypes.c_int(), ctypes.c_int()
+    assert L.nvfp4_gemm_plan(1, 4096, 100, 148, ctypes.byref(p_), ctypes.byref(r_)) == -2
