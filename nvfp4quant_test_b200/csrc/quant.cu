@@ -242,8 +242,11 @@ __device__ __forceinline__ uint32_t sweep_paired(const float v[16], const float 
             best_raw = raw_b;
         }
     };
-    if (NC > 0) {
+    if (NC > 0 && !WEIGHTED) {
 #pragma unroll
+        for (int i = 0; i + 1 < NC; i += 2) trip(i);
+    } else if (NC > 0) {
+#pragma unroll 2
         for (int i = 0; i + 1 < NC; i += 2) trip(i);
     } else {
 #pragma unroll 1
