@@ -97,7 +97,7 @@ static void plan_gemm(int64_t M, int64_t N, int64_t K, int sms, int k_splits, in
     }
     // Kernel choice by a small cost model fitted to measurements on B200: time ~ waves x cost of one tile, where a
     // wave is 148 single-CTA tiles or 74 CTA-pair tiles.  Relative tile costs: 128x64 -> 0.45, 128x128 -> 0.7, 128x256 -> 1.0,
-    // pair 256x192 -> 0.68 (0.75 of the MMA work per SM, and its epilogue overlaps the next tile).
+    // pair 256x192 -> 0.68 (0.75 of the MMA work per SM, and its epilogue overlaps the next tile), pair 256x256 -> 0.96.
     int path = g_gemm_force_path == 5 ? 0 : g_gemm_force_path;   // 0 = choose by shape
     if (path == 0) {
         const int64_t mt = (M + 127) / 128;
@@ -106,9 +106,20 @@ static void plan_gemm(int64_t M, int64_t N, int64_t K, int sms, int k_splits, in
         const double c4 = static_cast<double>((((M + 255) / 256) * ((N + 191) / 192) + 73) / 74) * 0.68;
         path = (c1 <= c2) ? 1 : 2;
         double best = c1 <= c2 ? c1 : c2;
-        if (M > 128 && N > 128 && k_splits == 1 && c4 <= best) {
+        // the pair kernels need a clear margin: at equal wave counts the single-CTA kernels put more CTAs on the
+        // weight stream (512 x 4096 x 4096: 128x128 tiles 9.8 us, pair 256x192 10.5 us)
+        // ... while per K stage the pair is cheaper, so from ~26 stages on it wins again (512 x 4096 x 14336: 19.8 / 21.7 us)
+        const double margin = k_tiles_total >= 26 ? 0.0 : 0.03;
+        if (M > 128 && N > 128 && k_splits == 1 && c4 < best - margin) {
             path = 4;
             best = c4;
+        }
+        // pair 256x256: 0.96 per wave of 74 pairs; wins where it needs fewer waves than the others (1024 x 4096 x
+        // 14336: 25.4 us against 28.1 us with 128x256 tiles)
+        const double c3 = static_cast<double>((((M + 255) / 256) * ((N + 255) / 256) + 73) / 74) * 0.96;
+        if (M > 128 && N > 128 && k_splits == 1 && c3 < best) {
+            path = 3;
+            best = c3;
         }
         // few, long tiles (one or two token tiles): 64 weight rows per CTA put twice as many SMs on the weight stream
         const double c6 = static_cast<double>((mt * ((N + 63) / 64) + 147) / 148) * 0.45;
