@@ -158,7 +158,7 @@ size_t nvfp4_gemm_workspace_bytes(int64_t M, int64_t N, int64_t K);
 /* Testing hook (process-wide): 0 = pick the GEMM kernel by shape (default), 1 = 128x128 tiles,
  * 2 = 128x256 tiles, 3 = CTA-pair 256x256 tiles, 4 = CTA-pair 256x192 tiles, 5 = skinny kernel for
  * M <= 128 (weights on the MMA rows, K ranges across a thread-block cluster; the default up to 32 tokens),
- * 6 = 128x64 tiles.  Paths 1-4 and 6 give identical bits; path 5 adds its K ranges in a fixed order and
+ * 6 = 128x64 tiles, 7 = CTA-pair 256x128 tiles.  Paths 1-4, 6 and 7 give identical bits; path 5 adds its K ranges in a fixed order and
  * agrees with them to fp32 rounding before the bf16 store (identical bits with one range). */
 int nvfp4_gemm_force_path(int path);
 /* Testing hook: *path = the kernel nvfp4_gemm_launch would take for this shape on a GPU with `sms` SMs under the

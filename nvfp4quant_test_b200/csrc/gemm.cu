@@ -61,15 +61,16 @@ extern "C" int nvfp4_gemm_tune(int k_splits, int k_rotate) {
 
 // Testing hook: 0 = choose the kernel by shape, 1 = 128x128 tiles, 2 = 128x256 tiles, 3 = CTA-pair 256x256 tiles,
 // 4 = CTA-pair 256x192 tiles with two accumulators, 5 = skinny kernel (M <= 128; nvfp4_gemm_tune's k_splits then
-// sets its K ranges per weight tile; larger M falls back to the choice by shape), 6 = 128x64 tiles.
+// sets its K ranges per weight tile; larger M falls back to the choice by shape), 6 = 128x64 tiles,
+// 7 = CTA-pair 256x128 tiles.
 extern "C" int nvfp4_gemm_force_path(int path) {
-    if (path < 0 || path > 6) return NVFP4_ERR_BAD_ENUM;
+    if (path < 0 || path > 7) return NVFP4_ERR_BAD_ENUM;
     g_gemm_force_path = path;
     return NVFP4_OK;
 }
 
 // Kernel choice for one shape: host arithmetic only.  *path: 1 = 128x128 tiles, 2 = 128x256, 3 = pair 256x256,
-// 4 = pair 256x192, 5 = skinny, 6 = 128x64; *k_ranges: cluster size of the skinny kernel (1 for the others).
+// 4 = pair 256x192, 5 = skinny, 6 = 128x64, 7 = pair 256x128; *k_ranges: cluster size of the skinny kernel (1 for the others).
 static void plan_gemm(int64_t M, int64_t N, int64_t K, int sms, int k_splits, int* path_out, int* ranges_out) {
     const int k_tiles_total = static_cast<int>((K + 255) / 256);
     const int n_tiles = static_cast<int>((N + 127) / 128);
@@ -97,7 +98,8 @@ static void plan_gemm(int64_t M, int64_t N, int64_t K, int sms, int k_splits, in
     }
     // Kernel choice by a small cost model fitted to measurements on B200: time ~ waves x cost of one tile, where a
     // wave is 148 single-CTA tiles or 74 CTA-pair tiles.  Relative tile costs: 128x64 -> 0.45, 128x128 -> 0.7, 128x256 -> 1.0,
-    // pair 256x192 -> 0.68 (0.75 of the MMA work per SM, and its epilogue overlaps the next tile), pair 256x256 -> 0.96.
+    // pair 256x192 -> 0.68 (0.75 of the MMA work per SM, and its epilogue overlaps the next tile), pair 256x256 -> 0.96,
+    // pair 256x128 -> 0.6.
     int path = g_gemm_force_path == 5 ? 0 : g_gemm_force_path;   // 0 = choose by shape
     if (path == 0) {
         const int64_t mt = (M + 127) / 128;
@@ -121,8 +123,17 @@ static void plan_gemm(int64_t M, int64_t N, int64_t K, int sms, int k_splits, in
             path = 3;
             best = c3;
         }
-        // few, long tiles (one or two token tiles): 64 weight rows per CTA put twice as many SMs on the weight stream
-        const double c6 = static_cast<double>((mt * ((N + 63) / 64) + 147) / 148) * 0.45;
+        // pair 256x128: 0.6 per wave; the kernel for a few hundred tokens (256 x 8192 x 8192: 13.4 us against 14.8 us
+        // with 128x128 tiles): as many CTAs as those, each loading only half of its tile's weight rows
+        const double c7 = static_cast<double>((((M + 255) / 256) * ((N + 127) / 128) + 73) / 74) * 0.6;
+        if (M > 128 && N > 128 && k_splits == 1 && c7 < best) {
+            path = 7;
+            best = c7;
+        }
+        // few tiles (one or two token tiles): 64 weight rows per CTA put twice as many SMs on the weight stream; every
+        // CTA re-reads the token tile, which costs per K stage, so from ~20 stages on it is rated 1.4x
+        // (256 x 4096 x 14336: 20.0 us against 16.6 us with pair 256x128)
+        const double c6 = static_cast<double>((mt * ((N + 63) / 64) + 147) / 148) * 0.45 * (k_tiles_total >= 20 ? 1.4 : 1.0);
         if (mt <= 2 && c6 < best) path = 6;
     }
     if (k_splits > 1 && path != 1 && path != 2 && path != 6) path = 1;
@@ -190,6 +201,7 @@ extern "C" int nvfp4_gemm_launch(const uint8_t* a, const uint8_t* b, const uint8
     }
     if (path == 3) return gemm::pair::launch_pair<256>(a, b, p, s);
     if (path == 4) return gemm::pair::launch_pair<192>(a, b, p, s);
+    if (path == 7) return gemm::pair::launch_pair<128>(a, b, p, s);
     if (path == 2) return gemm::launch<256>(a, b, p, s);
     if (path == 6) return gemm::launch<64>(a, b, p, s);
     return gemm::launch<128>(a, b, p, s);

@@ -18,16 +18,18 @@ namespace gemm {
 namespace pair {
 
 // Tile-width dependent constants of the pair kernel.  BN = 256: one accumulator (256 columns) per CTA.
-// BN = 192: two accumulators (2 x 192 columns), so the epilogue of one tile overlaps the MMAs of the next.
+// BN = 192 / 128: two accumulators (2 x BN columns), so the epilogue of one tile overlaps the MMAs of the next.
+// BN = 128 (256 x 128 tiles) is for a few hundred tokens: twice the CTAs of the wider tiles on the weight stream,
+// and each CTA still loads only half of the tile's weight rows.
 template <int BN>
 struct PairCfg {
-    static constexpr int kAcc = (BN == 192) ? 2 : 1;
+    static constexpr int kAcc = (BN <= 192) ? 2 : 1;
     static constexpr int kABytes = 128 * kBKBytes;          // this CTA's 128 rows of A
     static constexpr int kBBytes = (BN / 2) * kBKBytes;     // this CTA's half of the B rows
     static constexpr int kSfaBytes = 2048;                  // scales of this CTA's A rows
     static constexpr int kSfbBytes = 4096;                  // two 128-row scale groups cover the B tile
     static constexpr int kStageBytes = kABytes + kBBytes + kSfaBytes + kSfbBytes;
-    static constexpr int kStages = (BN == 192) ? 6 : 5;
+    static constexpr int kStages = (BN == 128) ? 7 : (BN == 192) ? 6 : 5;
     static constexpr int kSmemBytes = kStages * kStageBytes + 1024 + 256;
     static constexpr int kSfaCol = kAcc * BN;               // scale set 0; set 1 follows 48 columns later
     static constexpr int kSfbCol = kSfaCol + 16;

@@ -137,7 +137,9 @@ def test_gemm_kernel_choice_by_shape(L):
     assert plan(64, 4096, 4096) == (6, 1)            # 128x64 tiles
     assert plan(128, 8192, 8192) == (6, 1)
     assert plan(128, 28672, 8192) == (2, 1)          # 128x256 tiles
-    assert plan(256, 8192, 8192)[0] in (1, 4)
+    assert plan(256, 8192, 8192) == (7, 1)           # CTA pairs, 256x128 tiles: a few hundred tokens
+    assert plan(256, 4096, 4096) == (6, 1)
+    assert plan(512, 8192, 8192) == (3, 1)           # CTA pairs, 256x256 tiles
     assert plan(8192, 8192, 8192) == (4, 1)          # CTA pairs, 256x192 tiles
     assert plan(8192, 28672, 8192) == (4, 1)
     # forcing a kernel / K ranges is honoured, larger M than the skinny kernel takes falls back

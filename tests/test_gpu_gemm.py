@@ -68,7 +68,7 @@ def test_gemm_kernel_paths_agree(cuda_lib, oracle, M, N, K_):
     alpha = (gsa * gsb).reshape(1).float()
     outs = []
     try:
-        for path in (1, 2, 3, 4, 6):
+        for path in (1, 2, 3, 4, 6, 7):
             assert cuda_lib.nvfp4_gemm_force_path(path) == 0
             out = torch.full((M, N), float("nan"), dtype=torch.bfloat16, device="cuda")
             K.nvfp4_scaled_mm(qa, qb, sa, sb, alpha, torch.bfloat16, out=out)
@@ -78,7 +78,7 @@ def test_gemm_kernel_paths_agree(cuda_lib, oracle, M, N, K_):
         cuda_lib.nvfp4_gemm_force_path(0)
     ref = oracle.gemm(qa.cpu().numpy(), qb.cpu().numpy(), sa.view(torch.uint8).cpu().numpy().reshape(-1),
                       sb.view(torch.uint8).cpu().numpy().reshape(-1), float(alpha))
-    for path, out in zip((1, 2, 3, 4, 6), outs):
+    for path, out in zip((1, 2, 3, 4, 6, 7), outs):
         _check(out, ref)
     assert all(torch.equal(outs[0], o) for o in outs[1:])
 
@@ -333,7 +333,7 @@ def test_gemm_randomized_shapes_all_kernels(cuda_lib):
             sa = torch.randint(0x28, 0x48, ((M + 127) // 128 * 128, kp), dtype=torch.uint8, device="cuda", generator=gen)
             sb = torch.randint(0x28, 0x48, ((N + 127) // 128 * 128, kp), dtype=torch.uint8, device="cuda", generator=gen)
             alpha = torch.rand(1, device="cuda", generator=gen) + 0.5
-            runs = [(1, 0), (2, 0), (3, 0), (4, 0), (6, 0), (0, 0)]
+            runs = [(1, 0), (2, 0), (3, 0), (4, 0), (6, 0), (7, 0), (0, 0)]
             if M <= 128:
                 runs += [(5, 1), (5, rng.choice([2, 3, 4, 8]))]
             outs = {}
@@ -346,7 +346,7 @@ def test_gemm_randomized_shapes_all_kernels(cuda_lib):
             assert gemm_last_status() == 0
             ref = outs[(1, 0)]
             assert not torch.isnan(ref).any()
-            for key in ((2, 0), (3, 0), (4, 0), (6, 0), (5, 1)):
+            for key in ((2, 0), (3, 0), (4, 0), (6, 0), (7, 0), (5, 1)):
                 if key in outs:
                     assert torch.equal(outs[key], ref), (M, N, K_, key)
             tol = torch.maximum(ref.float().abs() * 2.0 ** -7, ref.float().abs().max() * 2.0 ** -16)
