@@ -126,7 +126,9 @@ static void plan_gemm(int64_t M, int64_t N, int64_t K, int sms, int k_splits, in
         // pair 256x128: 0.6 per wave; the kernel for a few hundred tokens (256 x 8192 x 8192: 13.4 us against 14.8 us
         // with 128x128 tiles): as many CTAs as those, each loading only half of its tile's weight rows
         const double c7 = static_cast<double>((((M + 255) / 256) * ((N + 127) / 128) + 73) / 74) * 0.6;
-        if (M > 128 && N > 128 && k_splits == 1 && c7 < best) {
+        // (with one token tile the second CTA of a pair has no rows, yet from ~20 K stages on sharing the weight
+        // rows still wins: 64 x 8192 x 8192 12.6 us against 13.3 us with 128x64 tiles)
+        if ((M > 128 || k_tiles_total >= 20) && N > 128 && k_splits == 1 && c7 < best) {
             path = 7;
             best = c7;
         }

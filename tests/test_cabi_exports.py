@@ -135,7 +135,8 @@ def test_gemm_kernel_choice_by_shape(L):
     assert plan(64, 4096, 14336) == (5, 4)           # few tiles, long K: still the decode-sized kernel
     assert plan(128, 4096, 14336) == (5, 4)
     assert plan(64, 4096, 4096) == (6, 1)            # 128x64 tiles
-    assert plan(128, 8192, 8192) == (6, 1)
+    assert plan(128, 8192, 8192) == (7, 1)           # long K: CTA pairs with 256x128 tiles even for one token tile
+    assert plan(128, 6144, 4096) == (6, 1)
     assert plan(128, 28672, 8192) == (2, 1)          # 128x256 tiles
     assert plan(256, 8192, 8192) == (7, 1)           # CTA pairs, 256x128 tiles: a few hundred tokens
     assert plan(256, 4096, 4096) == (6, 1)
