@@ -76,7 +76,10 @@ int nvfp4_quant_launch(int variant, const void* x, int x_dtype, const float* imp
  * 5 = 3 with warps that hold only padding rows skipping the sweep, 6 = 3 on a two-dimensional grid (row =
  * blockIdx.x, uniform over the CTA; taken by default when the row is a whole number of 256-block chunks wide,
  * otherwise 6 means 3), 7 = 6 with the reference's candidate count (11 unweighted, 16 weighted) compiled in and
- * the sweep unrolled (default for the unweighted sweep with the reference's window; other windows make it 6).
+ * the sweep unrolled (default for the unweighted sweep with the reference's window; other windows make it 6),
+ * 8 = 7 without any validity predicate, for tensors in which every slot of the scale layout is a real block (m a
+ * multiple of 128 in the tiled layout, padded_n == n, rows a whole number of 256-block chunks wide, the reference's
+ * window); the default there, elsewhere 8 means the default.
  * 4 is the fused form, which has its own entry point below.  All give identical bytes; exposed for testing and
  * timing. */
 int nvfp4_quant_launch_impl(int impl, int variant, const void* x, int x_dtype, const float* importance,
@@ -172,6 +175,14 @@ int nvfp4_gemm_plan(int64_t M, int64_t N, int64_t K, int sms, int* path, int* k_
 int nvfp4_gemm_tune(int k_splits, int k_rotate);
 /* Testing hook (process-wide): m-tiles per band of the persistent kernels' tile numbering (0 = default). */
 int nvfp4_gemm_tune_raster(int group);
+
+/* Tensor-pipe rate probe (no counterpart in the reference; it supplies the measured denominator of the GEMM's
+ * "fraction of FP4 peak"): every SM issues stages x 4 block-scaled FP4 MMAs (the GEMM's instruction, K = 64 each)
+ * back to back on operands resident in shared memory, nothing else.  pair == 0: one CTA per SM, M = 128, N = 256;
+ * pair != 0: CTA pairs (cta_group::2), M = 256, N = 256.  Time the launch with events on `stream`; work done =
+ * *sms_used * stages * 4 * 2 * 128 * 256 * 64 flop.  1 <= stages <= 2^20.  Waits inside are bounded
+ * (nvfp4_gemm_last_status reports an expiry). */
+int nvfp4_gemm_peak_probe(int stages, int pair, int* sms_used_host, void* stream);
 
 /* Device status word of the last GEMM on this device: 0 = ok, else a bounded
  * wait inside the kernel gave up (the kernel returned without hanging).

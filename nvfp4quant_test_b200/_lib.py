@@ -17,7 +17,8 @@ ERR_TOO_LARGE = -8
 
 EXPORTS = (
     "nvfp4_quant_launch", "nvfp4_quant_launch_impl", "nvfp4_quant_fused_launch", "nvfp4_quant_fused_last_status",
-    "nvfp4_global_scale_launch", "nvfp4_channel_sqnorm_launch",
+    "nvfp4_global_scale_launch", "nvfp4_global_scale_launch_static", "nvfp4_global_scale_static_max_bytes",
+    "nvfp4_channel_sqnorm_launch", "nvfp4_gemm_peak_probe",
     "nvfp4_gemm_launch", "nvfp4_gemm_workspace_bytes", "nvfp4_gemm_last_status", "nvfp4_gemm_force_path", "nvfp4_gemm_tune", "nvfp4_gemm_tune_raster", "nvfp4_gemm_plan",
     "nvfp4_probe_div_full_table", "nvfp4_probe_amax_out_scale_table",
     "nvfp4_status_string", "nvfp4_abi_version",
@@ -53,6 +54,12 @@ def lib() -> ctypes.CDLL:
         L.nvfp4_quant_fused_last_status.argtypes = [vp, vp]
         L.nvfp4_global_scale_launch.restype = ci
         L.nvfp4_global_scale_launch.argtypes = [vp, ci, i64, f32, vp, vp, vp]
+        L.nvfp4_global_scale_launch_static.restype = ci
+        L.nvfp4_global_scale_launch_static.argtypes = [vp, ci, i64, f32, vp, vp]
+        L.nvfp4_global_scale_static_max_bytes.restype = i64
+        L.nvfp4_global_scale_static_max_bytes.argtypes = []
+        L.nvfp4_gemm_peak_probe.restype = ci
+        L.nvfp4_gemm_peak_probe.argtypes = [ci, ci, vp, vp]
         L.nvfp4_channel_sqnorm_launch.restype = ci
         L.nvfp4_channel_sqnorm_launch.argtypes = [vp, ci, i64, i64, vp, vp]
         L.nvfp4_gemm_launch.restype = ci

@@ -21,6 +21,7 @@
 #include "gemm_tile.cuh"
 #include "gemm_pair.cuh"
 #include "gemm_skinny.cuh"
+#include "gemm_peak.cuh"
 
 static int g_gemm_force_path = 0;
 constexpr int64_t kSkinnyMaxM = 128;   // what the skinny kernel accepts
@@ -220,3 +221,42 @@ extern "C" int nvfp4_gemm_last_status(void* stream, uint32_t* status_host) {
     return static_cast<int>(e);
 }
 
+
+// Tensor-pipe rate probe: `stages` x 4 block-scaled FP4 MMAs per SM on operands resident in shared memory; time the
+// launch with events on `stream`.  pair == 0: one CTA per SM, M = 128, N = 256, K = 64 per instruction; pair != 0:
+// a CTA pair (cta_group::2) per two SMs, M = 256, N = 256, K = 64 per instruction -- the form the large-shape
+// kernels use.  Work done either way: *sms_out * stages * 4 * 2 * 128 * 256 * 64 flop (*sms_out = SMs used).
+// Bounded: stages <= 1 << 20.
+extern "C" int nvfp4_gemm_peak_probe(int stages, int pair_mode, int* sms_out, void* stream) {
+    using namespace nvfp4::gemm;
+    if (stages <= 0 || stages > (1 << 20)) return NVFP4_ERR_BAD_RANGE;
+    int dev = 0, sms = 0;
+    cudaError_t e = cudaGetDevice(&dev);
+    if (e == cudaSuccess) e = cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev);
+    if (e != cudaSuccess) return static_cast<int>(e);
+    cudaStream_t s = static_cast<cudaStream_t>(stream);
+    if (!pair_mode) {
+        e = cudaFuncSetAttribute(peak::fp4_peak_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, peak::kSmemBytes);
+        if (e != cudaSuccess) return static_cast<int>(e);
+        if (sms_out) *sms_out = sms;
+        peak::fp4_peak_kernel<<<sms, peak::kPeakThreads, peak::kSmemBytes, s>>>(stages);
+        return static_cast<int>(cudaGetLastError());
+    }
+    e = cudaFuncSetAttribute(peak::fp4_peak_pair_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, peak::kPairSmemBytes);
+    if (e != cudaSuccess) return static_cast<int>(e);
+    const int ctas = sms / 2 * 2;
+    if (sms_out) *sms_out = ctas;
+    cudaLaunchConfig_t cfg = {};
+    cfg.gridDim = dim3(ctas, 1, 1);
+    cfg.blockDim = dim3(peak::kPeakThreads, 1, 1);
+    cfg.dynamicSmemBytes = peak::kPairSmemBytes;
+    cfg.stream = s;
+    cudaLaunchAttribute attr[1];
+    attr[0].id = cudaLaunchAttributeClusterDimension;
+    attr[0].val.clusterDim.x = 2;
+    attr[0].val.clusterDim.y = 1;
+    attr[0].val.clusterDim.z = 1;
+    cfg.attrs = attr;
+    cfg.numAttrs = 1;
+    return static_cast<int>(cudaLaunchKernelEx(&cfg, peak::fp4_peak_pair_kernel, stages));
+}

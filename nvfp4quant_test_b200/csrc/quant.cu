@@ -367,7 +367,8 @@ quant_kernel(const QuantParams p) {
     // The row is then uniform over the CTA, so the division below, the row part of the addresses and most of the
     // tiled scale offset leave the per-thread instruction stream.  Used when the slot grid is a whole number of
     // chunks wide (e.g. 512 blocks per row at 8192 columns); narrow or ragged widths keep the flat numbering.
-    constexpr bool GRID2D = IMPL == 6 || IMPL == 7;   // 7 = 6 with the reference's candidate count compiled in
+    constexpr bool GRID2D = IMPL == 6 || IMPL == 7 || IMPL == 8;   // 7 = 6 with the reference's candidate count compiled in
+    constexpr bool WHOLE = IMPL == 8;                              // 8 = 7 on tensors without any padding: no predicates
     const int64_t id = GRID2D ? 0 : static_cast<int64_t>(blockIdx.x) * kThreads + threadIdx.x;
     const bool in_range = GRID2D ? true : id < p.total;
     int64_t row = 0, col = 0;
@@ -384,7 +385,7 @@ quant_kernel(const QuantParams p) {
             col = id - row * p.width;
         }
     }
-    const bool valid = in_range && row < p.m && col < p.bout;
+    const bool valid = WHOLE ? true : (in_range && row < p.m && col < p.bout);
 
     float v[16], w[16];
 #pragma unroll
@@ -392,7 +393,7 @@ quant_kernel(const QuantParams p) {
         v[j] = 0.0f;
         w[j] = 0.0f;
     }
-    if (valid && col < p.bin) {
+    if (WHOLE || (valid && col < p.bin)) {
         load16<DT>(p.x, row * p.n + col * kBlock, v);
         if (VARIANT == NVFP4_VARIANT_WEIGHTED) load16<NVFP4_DT_F32>(p.importance, col * kBlock, w);
     }
@@ -475,7 +476,7 @@ quant_kernel(const QuantParams p) {
         const int first_idx = min(max(base_raw + p.lower, -kTabPad), 127) + kTabPad;
         sbyte = (IMPL == 1)   ? sweep_scalar<W>(v, w, first_idx, p.ncand, tab)
                 : (IMPL == 2) ? sweep_single<W>(v, w, first_idx, p.ncand, tab)
-                : (IMPL == 7) ? sweep_paired<W, W ? 16 : 11>(v, w, first_idx, p.ncand, tab)
+                : (IMPL == 7 || IMPL == 8) ? sweep_paired<W, W ? 16 : 11>(v, w, first_idx, p.ncand, tab)
                               : sweep_paired<W>(v, w, first_idx, p.ncand, tab);
         // sbyte is 0 only when no candidate had a comparable (non-NaN, < inf) error: 1/0 as the reference computes it
         inv = (sbyte == 0) ? div_full(1.0f, 0.0f) : tab[sbyte + kTabPad].x;
@@ -510,9 +511,23 @@ quant_kernel(const QuantParams p) {
     }
 }
 
+
 template <int DT, int VARIANT>
 cudaError_t launch_impl(int impl, const QuantParams& p, cudaStream_t stream) {
     const int64_t grid = (p.total + kThreads - 1) / kThreads;
+    // body 8: tensors without padding whose rows are whole 256-block chunks (every slot of the scale layout is a
+    // real block): body 7 without its validity predicates
+    const bool whole = VARIANT != NVFP4_VARIANT_AMAX && p.rows == p.m && p.bin == p.bout && p.bout == p.width &&
+                       (p.width % kThreads) == 0 && p.width / kThreads <= 65535 && p.rows <= 0x7fffffffLL &&
+                       (VARIANT == NVFP4_VARIANT_MSE ? p.ncand == 11 : p.ncand == 16);
+    if constexpr (VARIANT != NVFP4_VARIANT_AMAX) {
+        if ((impl == 8 || impl == 0) && whole) {
+            const dim3 grid2(static_cast<unsigned>(p.rows), static_cast<unsigned>(p.width / kThreads));
+            quant_kernel<DT, VARIANT, 8><<<grid2, kThreads, 0, stream>>>(p);
+            return cudaGetLastError();
+        }
+    }
+    if (impl >= 8) impl = 0;
     if (impl == 1)
         quant_kernel<DT, VARIANT, 1><<<static_cast<unsigned>(grid), kThreads, 0, stream>>>(p);
     else if (impl == 2)
@@ -552,7 +567,7 @@ extern "C" int nvfp4_quant_launch_impl(int impl, int variant, const void* x, int
     using namespace nvfp4;
     if (variant < NVFP4_VARIANT_MSE || variant > NVFP4_VARIANT_AMAX) return NVFP4_ERR_BAD_ENUM;
     if (x_dtype < NVFP4_DT_BF16 || x_dtype > NVFP4_DT_F32) return NVFP4_ERR_BAD_ENUM;
-    if (impl < 0 || impl > 7 || impl == 4) return NVFP4_ERR_BAD_ENUM;
+    if (impl < 0 || impl > 8 || impl == 4) return NVFP4_ERR_BAD_ENUM;
     if (m < 0 || n < 0 || (n % kBlock) != 0 || (padded_n % kBlock) != 0 || padded_n < n) return NVFP4_ERR_BAD_SHAPE;
     if (variant != NVFP4_VARIANT_AMAX && (upper < lower || upper - lower + 1 > 64)) return NVFP4_ERR_BAD_RANGE;
     QuantParams p;

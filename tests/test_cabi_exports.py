@@ -38,7 +38,7 @@ def test_abi_version_and_status_strings(L):
 
     assert L.nvfp4_abi_version() >= 1
     assert _lib.status_string(0) == "ok"
-    for code in range(-8, 0):
+    for code in range(-9, 0):
         s = _lib.status_string(code)
         assert s and s != "unknown status"
     assert _lib.status_string(-99) == "unknown status"
@@ -60,7 +60,7 @@ def test_quant_launch_rejects_bad_arguments_before_launching(L):
     assert q(0, P + 2, 0, None, P, P, P, 4, 64, 64, -3, 7, 1, None) == -4      # misaligned x
     assert q(0, P, 0, None, P, P + 1, P, 4, 64, 64, -3, 7, 1, None) == -4      # misaligned codes
     assert q(0, P, 0, None, P, P, P, 0, 64, 64, -3, 7, 1, None) == 0           # empty input: nothing to do
-    assert L.nvfp4_quant_launch_impl(9, 0, P, 0, None, P, P, P, 4, 64, 64, -3, 7, 1, None) == -3
+    assert L.nvfp4_quant_launch_impl(12, 0, P, 0, None, P, P, P, 4, 64, 64, -3, 7, 1, None) == -3
 
 
 def test_gemm_launch_rejects_bad_arguments_before_launching(L):

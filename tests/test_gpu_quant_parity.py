@@ -485,3 +485,42 @@ def test_two_dimensional_grid_bodies(cuda_lib, oracle, m, n, padded_n, swizzled)
             assert intact, f"{variant} impl {impl} wrote outside its buffers"
             assert np.array_equal(codes, flat_codes), f"{variant} impl {impl}"
             assert np.array_equal(scales, flat_scales), f"{variant} impl {impl}"
+
+
+def _whole_tile_input(m, n, seed, dtype):
+    """Random rows with the special-value rows of the edge fixture (NaN, inf, zeros, ties, saturation) tiled in."""
+    x = C._laplace((m, n), seed, dtype)
+    e = C._edge_rows(dtype)                       # [16, 64]
+    reps = min(n // 64, 8)
+    k = min(m, 16)
+    x[:k, :64 * reps] = e.repeat(1, reps)[:k]
+    x[m - k:, n - 64:] = e[16 - k:]
+    return x
+
+
+@pytest.mark.parametrize("m,n,dtype,swizzled", [
+    (128, 4096, torch.bfloat16, True),
+    (256, 8192, torch.bfloat16, True),
+    (130, 4096, torch.bfloat16, False),          # linear layout: any row count is a whole tile
+    (1920, 4096, torch.bfloat16, True),          # more rows than resident CTAs: the row loop and its prefetch run
+    (128, 4096, torch.float16, True),
+    (128, 4096, torch.float32, False),
+    (3, 4096, torch.bfloat16, False),            # fewer rows than CTAs
+])
+def test_whole_tile_body(cuda_lib, oracle, m, n, dtype, swizzled):
+    """Body 8 (no validity predicates, for tensors without padding) against the scalar transcription (body 1) and the
+    oracle: both sweeps, both layouts, three dtypes, special values included."""
+    x = _whole_tile_input(m, n, 4000 + m + n, dtype)
+    for gs_inv in (1.0, C.global_scale_cpu(C._laplace((m, n), 4000 + m + n, dtype), 256.0)[1]):
+        for variant, imp in (("mse", None), ("weighted", C._importance("random", n))):
+            c = dict(x=x, variant=variant, importance=imp, swizzled=swizzled, padded_n=None, lower=None, upper=None)
+            ref_codes, ref_scales, ok = _run_cuda(c, gs_inv, 1)
+            assert ok
+            if m <= 256:
+                want_codes, want_scales = util.oracle_quant_case(oracle, c, gs_inv)
+                assert np.array_equal(ref_codes, want_codes) and np.array_equal(ref_scales, want_scales)
+            for impl in (0, 8):
+                codes, scales, intact = _run_cuda(c, gs_inv, impl)
+                assert intact, f"{variant} impl {impl} wrote outside its buffers"
+                assert np.array_equal(codes, ref_codes), f"{variant} impl {impl}: {(codes != ref_codes).sum()} code bytes"
+                assert np.array_equal(scales, ref_scales), f"{variant} impl {impl}: scale bytes"
