@@ -362,3 +362,85 @@ void nvfp4_oracle_offset_histogram(const float* x, int64_t nblocks, int64_t hist
     }
     *skipped = local_skipped;
 }
+
+/*
+ * Pruning study for the unweighted sweep (kernels/kernel_ScaleSweep_MSE.py:326-346), in the kernel's own fp32
+ * arithmetic.  For a candidate scale s whose grid cannot hold the block maximum (x = amax * (1/s) > 6), the block
+ * error is at least the error of that one element: RN(RN(d*d) * RN(s*s)) with d = RN(6 - x).  The bound needs no
+ * rounding margin: every other term of the serial FMA chain is >= 0 and round-to-nearest is monotone, so the
+ * chain can only be larger.  A candidate whose bound is strictly above the least error among the non-saturating
+ * candidates can neither win nor tie and may be skipped.
+ *   surv_hist[k]      blocks that keep k candidates under that rule (k = 0..ncand)
+ *   warp_hist[k]      groups of 32 consecutive blocks whose largest survivor count is k (the trip count of a warp
+ *                     that holds one block per lane)
+ *   pruned_by_off[i]  blocks in which candidate i (offset lower + i) was pruned
+ *   prefix_elems[i]   sum over blocks of the elements of candidate i's chain that have to be accumulated before its
+ *                     partial error exceeds the block's final minimum (16 for a winner): the work a branch-and-bound
+ *                     over chain prefixes with perfect knowledge of the minimum would still do
+ * Returns the number of blocks in which pruning would have changed the chosen scale (must be 0).
+ */
+int64_t nvfp4_oracle_prune_study(const float* x, int64_t nblocks, float gs_inv, int lower, int upper,
+                                 int64_t* surv_hist, int64_t* warp_hist, int64_t* pruned_by_off, int64_t* prefix_elems) {
+    const int nc = upper - lower + 1;
+    if (nc < 1 || nc > 64) return -1;
+    int64_t wrong = 0;
+    int warp_max = 0;
+    for (int64_t b = 0; b < nblocks; ++b) {
+        float v[16];
+        float amax = 0.0f;
+        for (int j = 0; j < 16; ++j) {
+            v[j] = x[b * 16 + j] * gs_inv;
+            amax = fmaxf(amax, fabsf(v[j]));
+        }
+        int base = nvfp4_oracle_f32_to_e4m3(amax * bits_to_f32(0x3E2AAAABu));
+        float err[64], bound[64];
+        int raws[64];
+        float best_ns = INFINITY;    /* least error among candidates that do not saturate the maximum */
+        for (int i = 0; i < nc; ++i) {
+            int raw = base + lower + i;
+            if (raw < 1) raw = 1;
+            if (raw > 126) raw = 126;
+            raws[i] = raw;
+            float s = nvfp4_oracle_e4m3_to_f32((uint8_t)raw), inv = inv_scale_of_raw(raw);
+            err[i] = mse_error(v, inv, s);
+            float xm = amax * inv;
+            if (xm > 6.0f) {
+                float d = 6.0f - xm;
+                bound[i] = (d * d) * (s * s);
+            } else {
+                bound[i] = -1.0f;    /* not a saturating candidate: always evaluated */
+                if (err[i] < best_ns) best_ns = err[i];
+            }
+        }
+        /* reference result */
+        float best = INFINITY;
+        int best_raw = 0;
+        for (int i = 0; i < nc; ++i)
+            if (err[i] < best) { best = err[i]; best_raw = raws[i]; }
+        /* pruned result: saturating candidates are looked at after the others, lowest raw wins ties */
+        float pbest = INFINITY;
+        int praw = 0, kept = 0;
+        for (int i = 0; i < nc; ++i) {
+            if (bound[i] >= 0.0f && bound[i] > best_ns) { ++pruned_by_off[i]; continue; }
+            ++kept;
+            if (err[i] < pbest || (err[i] == pbest && raws[i] < praw)) { pbest = err[i]; praw = raws[i]; }
+        }
+        if (praw != best_raw) ++wrong;
+        ++surv_hist[kept];
+        if (kept > warp_max) warp_max = kept;
+        if ((b & 31) == 31 || b == nblocks - 1) { ++warp_hist[warp_max]; warp_max = 0; }
+        for (int i = 0; i < nc; ++i) {
+            float inv = inv_scale_of_raw(raws[i]), s = nvfp4_oracle_e4m3_to_f32((uint8_t)raws[i]);
+            float acc = 0.0f;
+            int j = 0;
+            for (; j < 16; ++j) {
+                float xx = v[j] * inv;
+                float d = e2m1_to_f32(f32_to_e2m1(xx)) - xx;
+                acc = (j == 0) ? d * d : fmaf(d, d, acc);
+                if (acc * (s * s) > best) { ++j; break; }
+            }
+            prefix_elems[i] += j;
+        }
+    }
+    return wrong;
+}

@@ -58,6 +58,8 @@ def lib() -> ctypes.CDLL:
         L.nvfp4_oracle_swizzled_offset.argtypes = [i64, i64, i64]
         L.nvfp4_oracle_offset_histogram.restype = None
         L.nvfp4_oracle_offset_histogram.argtypes = [vp, i64, vp, vp]
+        L.nvfp4_oracle_prune_study.restype = i64
+        L.nvfp4_oracle_prune_study.argtypes = [vp, i64, f32, ci, ci, vp, vp, vp, vp]
         L.nvfp4_oracle_div_full_table_is_measured.restype = ci
         L.nvfp4_oracle_div_full_bits.restype = ctypes.c_uint32
         L.nvfp4_oracle_div_full_bits.argtypes = [ci]
@@ -158,6 +160,20 @@ def offset_histogram(blocks: np.ndarray):
     skipped = np.zeros(1, dtype=np.int64)
     lib().nvfp4_oracle_offset_histogram(_ptr(x), x.shape[0], _ptr(hist), _ptr(skipped))
     return {i - 64: int(c) for i, c in enumerate(hist) if c}, int(skipped[0])
+
+
+def prune_study(blocks: np.ndarray, gs_inv: float = 1.0, lower: int = -3, upper: int = 7) -> dict:
+    """Survivor statistics of the saturation-bound pruning rule for the unweighted sweep (see the C source)."""
+    x = np.ascontiguousarray(blocks, dtype=np.float32).reshape(-1, 16)
+    nc = upper - lower + 1
+    surv = np.zeros(nc + 1, np.int64)
+    warp = np.zeros(nc + 1, np.int64)
+    pruned = np.zeros(nc, np.int64)
+    prefix = np.zeros(nc, np.int64)
+    wrong = lib().nvfp4_oracle_prune_study(_ptr(x), x.shape[0], float(gs_inv), lower, upper, _ptr(surv), _ptr(warp),
+                                           _ptr(pruned), _ptr(prefix))
+    return {"blocks": int(x.shape[0]), "changed": int(wrong), "survivors": surv, "warp_max": warp,
+            "pruned_by_offset": pruned, "prefix_elements": prefix}
 
 
 def e4m3_to_f32(raw: int) -> float:

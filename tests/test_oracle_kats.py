@@ -173,3 +173,33 @@ def test_sweep_window_covers_the_exhaustive_optimum(oracle):
     assert min(total) >= -3 and max(total) <= 7, total
     assert sum(total.values()) > 285000
     assert total.get(0, 0) > 0 and max(total) >= 3 and min(total) <= -1, total
+
+
+def test_saturation_bound_pruning_is_exact_but_removes_too_few_candidates(oracle):
+    """The only candidates of the unweighted sweep with a cheap rigorous lower bound on their error are those whose
+    grid cannot hold the block maximum (error >= that one element's saturation error, no rounding margin needed:
+    see nvfp4_oracle_prune_study).  Skipping them when the bound is strictly above the best non-saturating error
+    never changes the chosen scale - checked here on random and adversarial blocks - but it removes only ~1.5 of
+    11 candidates per block and almost none per 32-block warp, which is why the CUDA kernels sweep exhaustively."""
+    rng = np.random.default_rng(11)
+    n = 40000
+    gauss = rng.standard_normal((n, 16)).astype(np.float32)
+    adversarial = np.concatenate([
+        np.repeat(rng.uniform(0.1, 50.0, (2000, 1)), 16, axis=1),                       # all elements equal
+        np.eye(16, dtype=np.float64)[rng.integers(0, 16, 2000)] * rng.uniform(0.1, 50.0, (2000, 1)),   # maximum only
+        rng.choice([0.0, 0.5, 1.0, 1.5, 2.0, 3.0, 4.0, 6.0], (4000, 16)) * rng.choice([-1.0, 1.0], (4000, 16)),  # grid values: exact ties
+        np.round(rng.standard_normal((4000, 16)) * 4) / 4,                              # quarter steps: rounding ties
+        np.zeros((32, 16)),
+        rng.laplace(size=(4000, 16)) * np.where(rng.random((4000, 16)) < 0.07, 12.0, 1.0),
+    ]).astype(np.float32)
+    for blocks, gs_inv in ((gauss, 1.0), (gauss, 565.9), (adversarial, 1.0), (adversarial, 37.5)):
+        r = oracle.prune_study(blocks, gs_inv)
+        assert r["changed"] == 0
+    r = oracle.prune_study(gauss, 565.9)
+    mean_survivors = float((r["survivors"] * np.arange(12)).sum()) / r["blocks"]
+    mean_warp_trip = float((r["warp_max"] * np.arange(12)).sum()) / r["warp_max"].sum()
+    assert 9.0 < mean_survivors < 10.0           # ~13 % of the candidates go
+    assert mean_warp_trip > 10.5                  # ... but a warp of 32 blocks still runs ~10.7 of 11 trips
+    assert r["pruned_by_offset"][3:].sum() == 0   # nothing at or above the base code is ever prunable this way
+    # even a branch-and-bound over chain prefixes that knew the final minimum in advance would do ~60 % of the work
+    assert 0.5 < r["prefix_elements"].sum() / (r["blocks"] * 176.0) < 0.7
