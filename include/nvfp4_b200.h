@@ -4,9 +4,10 @@
  *
  * Every pointer is a DEVICE pointer unless its name ends in `_host`.  Launches
  * are asynchronous on `stream` (a cudaStream_t passed as void*; NULL = the
- * legacy default stream).  No call synchronises the device, copies to the host
- * or allocates memory.  Return value: 0 = ok, < 0 = NVFP4_ERR_* (nothing was
- * launched), > 0 = a cudaError_t reported by the launch.
+ * legacy default stream).  Launch calls never synchronise the device, copy to the
+ * host or allocate memory; the few calls that do synchronise (the *_last_status
+ * readers and the set_wait_limit hooks) say so.  Return value: 0 = ok, < 0 =
+ * NVFP4_ERR_* (nothing was launched), > 0 = a cudaError_t reported by the launch.
  *
  * The "replaces" notes name the interface of efsotr/nvfp4quant_test (paths
  * inside that project) or of vllm 0.22.0, which that project calls.
@@ -106,7 +107,8 @@ int nvfp4_global_scale_launch(const void* x, int x_dtype, int64_t numel, float f
  * so x crosses HBM once.  The tensor must fit the resident grid of the device (about 3 M elements on a B200):
  * otherwise NVFP4_ERR_TOO_LARGE is returned, nothing is launched, and the caller issues the two launches.
  * `scratch` = 4 uint32, zero before the first call; the kernel leaves them zero.  Calls that share a scratch
- * must be ordered on one stream.
+ * must be ordered on one stream.  (Testing hook: a non-zero scratch[3] makes CTA 0 withhold its arrival, so the
+ * grid-wide wait runs into its limit and the status word is set.)
  */
 int nvfp4_quant_fused_launch(int variant, const void* x, int x_dtype, const float* importance, float fp8_max,
                              float* gs_out, uint32_t* scratch, uint8_t* codes, uint8_t* scales, int64_t m, int64_t n,
@@ -151,8 +153,10 @@ int64_t nvfp4_global_scale_static_max_bytes(void);
  * replaces vllm `_C::cutlass_scaled_fp4_mm` (vllm/_custom_ops.py:741-752;
  * named at README.md:68).
  * workspace: nvfp4_gemm_workspace_bytes(M, N, K) bytes, 16-byte aligned (may be NULL when that is 0).
- * It is non-zero only for small M, where K is cut into ranges whose fp32 partial tiles are summed by a
- * second kernel; contents need no initialisation.
+ * It is 0 for every shape unless K ranges were switched on through nvfp4_gemm_tune (a testing hook: the tile
+ * kernels then write fp32 partial tiles that a second kernel sums); contents need no initialisation.
+ * Launches of this library's GEMM kernels may overlap on the GPU (several streams): every kernel reserves shared
+ * memory in proportion to the TMEM columns it takes, so CTAs that share an SM never wait for one another's TMEM.
  */
 int nvfp4_gemm_launch(const uint8_t* a, const uint8_t* b, const uint8_t* sfa, const uint8_t* sfb,
                       const float* alpha, void* out_bf16, int64_t M, int64_t N, int64_t K,
@@ -179,21 +183,22 @@ int nvfp4_gemm_tune_raster(int group);
 /* Tensor-pipe rate probe (no counterpart in the reference; it supplies the measured denominator of the GEMM's
  * "fraction of FP4 peak"): every SM issues stages x 4 block-scaled FP4 MMAs (the GEMM's instruction, K = 64 each)
  * back to back on operands resident in shared memory, nothing else.  pair == 0: one CTA per SM, M = 128, N = 256;
- * pair != 0: CTA pairs (cta_group::2), M = 256, N = 256.  Time the launch with events on `stream`; work done =
+ * pair == 1: CTA pairs (cta_group::2), M = 256, N = 256; pair == 2 (testing hook): the pair == 0 kernel with its
+ * last commit left out, so that its final wait ends at the wait limit and sets the status word.  Time the launch with events on `stream`; work done =
  * *sms_used * stages * 4 * 2 * 128 * 256 * 64 flop.  1 <= stages <= 2^20.  Waits inside are bounded
  * (nvfp4_gemm_last_status reports an expiry). */
 int nvfp4_gemm_peak_probe(int stages, int pair, int* sms_used_host, void* stream);
 
-/* Device status word of the last GEMM on this device: 0 = ok, else a bounded
- * wait inside the kernel gave up (the kernel returned without hanging).
- * Synchronises `stream`. */
+/* Device status word of the GEMMs on the current device: 0 = ok, else a bounded wait inside a kernel gave up
+ * (the kernel returned without hanging).  One word per device: it tells that some launch since the last read
+ * failed, not which one or on which stream.  Synchronises `stream`; reading a non-zero word clears it. */
 int nvfp4_gemm_last_status(void* stream, uint32_t* status_host);
 
-/* Diagnostics used by the tests: out[raw] = bits of div.full.f32(1, e4m3(raw))
- * for raw = 0..127 (no counterpart in the reference; it pins the CPU oracle's table). */
-int nvfp4_probe_div_full_table(uint32_t* out128, void* stream);
-/* out[raw] = the AMAX variant's multiplier for scale byte raw = 0..127 given gs_inv. */
-int nvfp4_probe_amax_out_scale_table(const float* gs_inv, float* out128, void* stream);
+/* Testing hooks: the time (nanoseconds, 1 us .. 10 s; 0 = the default of 2 s) after which a wait inside the GEMM
+ * kernels, or the grid-wide wait of the fused quantizer, gives up on the current device and records its status
+ * word instead of waiting on.  Synchronous calls.  No counterpart in the reference. */
+int nvfp4_gemm_set_wait_limit_ns(uint64_t ns);
+int nvfp4_quant_fused_set_wait_limit_ns(uint64_t ns);
 
 const char* nvfp4_status_string(int status);
 int nvfp4_abi_version(void);

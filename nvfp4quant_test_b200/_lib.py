@@ -18,9 +18,8 @@ ERR_TOO_LARGE = -8
 EXPORTS = (
     "nvfp4_quant_launch", "nvfp4_quant_launch_impl", "nvfp4_quant_fused_launch", "nvfp4_quant_fused_last_status",
     "nvfp4_global_scale_launch", "nvfp4_global_scale_launch_static", "nvfp4_global_scale_static_max_bytes",
-    "nvfp4_channel_sqnorm_launch", "nvfp4_gemm_peak_probe",
+    "nvfp4_channel_sqnorm_launch", "nvfp4_gemm_peak_probe", "nvfp4_gemm_set_wait_limit_ns", "nvfp4_quant_fused_set_wait_limit_ns",
     "nvfp4_gemm_launch", "nvfp4_gemm_workspace_bytes", "nvfp4_gemm_last_status", "nvfp4_gemm_force_path", "nvfp4_gemm_tune", "nvfp4_gemm_tune_raster", "nvfp4_gemm_plan",
-    "nvfp4_probe_div_full_table", "nvfp4_probe_amax_out_scale_table",
     "nvfp4_status_string", "nvfp4_abi_version",
 )
 
@@ -60,6 +59,10 @@ def lib() -> ctypes.CDLL:
         L.nvfp4_global_scale_static_max_bytes.argtypes = []
         L.nvfp4_gemm_peak_probe.restype = ci
         L.nvfp4_gemm_peak_probe.argtypes = [ci, ci, vp, vp]
+        L.nvfp4_gemm_set_wait_limit_ns.restype = ci
+        L.nvfp4_gemm_set_wait_limit_ns.argtypes = [ctypes.c_uint64]
+        L.nvfp4_quant_fused_set_wait_limit_ns.restype = ci
+        L.nvfp4_quant_fused_set_wait_limit_ns.argtypes = [ctypes.c_uint64]
         L.nvfp4_channel_sqnorm_launch.restype = ci
         L.nvfp4_channel_sqnorm_launch.argtypes = [vp, ci, i64, i64, vp, vp]
         L.nvfp4_gemm_launch.restype = ci
@@ -76,10 +79,6 @@ def lib() -> ctypes.CDLL:
         L.nvfp4_gemm_tune.argtypes = [ci, ci]
         L.nvfp4_gemm_force_path.restype = ci
         L.nvfp4_gemm_force_path.argtypes = [ci]
-        L.nvfp4_probe_div_full_table.restype = ci
-        L.nvfp4_probe_div_full_table.argtypes = [vp, vp]
-        L.nvfp4_probe_amax_out_scale_table.restype = ci
-        L.nvfp4_probe_amax_out_scale_table.argtypes = [vp, vp, vp]
         L.nvfp4_status_string.restype = ctypes.c_char_p
         L.nvfp4_status_string.argtypes = [ci]
         L.nvfp4_abi_version.restype = ci
@@ -140,3 +139,31 @@ def device_guard(device):
     if device.index is None or device.index == torch.cuda.current_device():
         return _NO_GUARD
     return torch.cuda.device(device)
+
+
+class StreamScratch:
+    """Small zero-initialised device buffers keyed by (device, stream): launches on one stream may share a scratch
+    (the kernels leave it zeroed), launches that may overlap need their own.  Holds at most `capacity` entries and
+    drops the least recently used one beyond that, so a process that keeps creating streams does not grow it without
+    bound (a dropped buffer goes back to torch's caching allocator, which only hands it out again in stream order)."""
+
+    def __init__(self, words: int, capacity: int = 32):
+        from collections import OrderedDict
+
+        self.words, self.capacity, self._d = words, capacity, OrderedDict()
+
+    def get(self, device, stream: int):
+        import torch
+
+        key = (device, stream)
+        buf = self._d.get(key)
+        if buf is None:
+            buf = self._d[key] = torch.zeros(self.words, dtype=torch.int32, device=device)
+            while len(self._d) > self.capacity:
+                self._d.popitem(last=False)
+        else:
+            self._d.move_to_end(key)
+        return buf
+
+    def __len__(self):
+        return len(self._d)

@@ -15,7 +15,7 @@ CSRC = PKG / "csrc"
 INCLUDE = PKG.parent / "include"
 LIB = PKG / "libnvfp4_b200.so"
 
-SOURCES = ["quant.cu", "global_scale.cu", "global_scale_static.cu", "importance.cu", "gemm.cu", "probe.cu"]
+SOURCES = ["quant.cu", "global_scale.cu", "global_scale_static.cu", "importance.cu", "gemm.cu", "status.cu"]
 NVCC_FLAGS = [
     "-gencode", "arch=compute_100a,code=sm_100a", "-lineinfo", "-O3", "-std=c++17",
     "-fmad=false",  # every fused multiply-add in the kernels is written explicitly
@@ -48,7 +48,7 @@ def build(force: bool = False, verbose: bool = False) -> pathlib.Path:
     if verbose:
         cmd.insert(1, "-Xptxas=-v")
     env = dict(os.environ)
-    # the image exports CC/CXX pointing at a compiler driver without its spec files
+    # nvcc picks its host compiler itself; a CC/CXX meant for another toolchain would only mislead it
     env.pop("CC", None)
     env.pop("CXX", None)
     res = subprocess.run(cmd, capture_output=True, text=True, env=env)

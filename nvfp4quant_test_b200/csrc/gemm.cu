@@ -98,15 +98,16 @@ static void plan_gemm(int64_t M, int64_t N, int64_t K, int sms, int k_splits, in
         return;
     }
     // Kernel choice by a small cost model fitted to measurements on B200: time ~ waves x cost of one tile, where a
-    // wave is 148 single-CTA tiles or 74 CTA-pair tiles.  Relative tile costs: 128x64 -> 0.45, 128x128 -> 0.7, 128x256 -> 1.0,
+    // wave is one single-CTA tile per SM or one CTA-pair tile per two SMs (148 / 74 on a B200).  Relative tile costs: 128x64 -> 0.45, 128x128 -> 0.7, 128x256 -> 1.0,
     // pair 256x192 -> 0.68 (0.75 of the MMA work per SM, and its epilogue overlaps the next tile), pair 256x256 -> 0.96,
     // pair 256x128 -> 0.6.
     int path = g_gemm_force_path == 5 ? 0 : g_gemm_force_path;   // 0 = choose by shape
     if (path == 0) {
         const int64_t mt = (M + 127) / 128;
-        const double c1 = static_cast<double>((mt * ((N + 127) / 128) + 147) / 148) * 0.7;
-        const double c2 = static_cast<double>((mt * ((N + 255) / 256) + 147) / 148) * 1.0;
-        const double c4 = static_cast<double>((((M + 255) / 256) * ((N + 191) / 192) + 73) / 74) * 0.68;
+        const int64_t wave1 = sms, wave2 = sms / 2 > 0 ? sms / 2 : 1;   // tiles per wave: single CTAs, CTA pairs
+        const double c1 = static_cast<double>((mt * ((N + 127) / 128) + wave1 - 1) / wave1) * 0.7;
+        const double c2 = static_cast<double>((mt * ((N + 255) / 256) + wave1 - 1) / wave1) * 1.0;
+        const double c4 = static_cast<double>((((M + 255) / 256) * ((N + 191) / 192) + wave2 - 1) / wave2) * 0.68;
         path = (c1 <= c2) ? 1 : 2;
         double best = c1 <= c2 ? c1 : c2;
         // the pair kernels need a clear margin: at equal wave counts the single-CTA kernels put more CTAs on the
@@ -119,14 +120,14 @@ static void plan_gemm(int64_t M, int64_t N, int64_t K, int sms, int k_splits, in
         }
         // pair 256x256: 0.96 per wave of 74 pairs; wins where it needs fewer waves than the others (1024 x 4096 x
         // 14336: 25.4 us against 28.1 us with 128x256 tiles)
-        const double c3 = static_cast<double>((((M + 255) / 256) * ((N + 255) / 256) + 73) / 74) * 0.96;
+        const double c3 = static_cast<double>((((M + 255) / 256) * ((N + 255) / 256) + wave2 - 1) / wave2) * 0.96;
         if (M > 128 && N > 128 && k_splits == 1 && c3 < best) {
             path = 3;
             best = c3;
         }
         // pair 256x128: 0.6 per wave; the kernel for a few hundred tokens (256 x 8192 x 8192: 13.4 us against 14.8 us
         // with 128x128 tiles): as many CTAs as those, each loading only half of its tile's weight rows
-        const double c7 = static_cast<double>((((M + 255) / 256) * ((N + 127) / 128) + 73) / 74) * 0.6;
+        const double c7 = static_cast<double>((((M + 255) / 256) * ((N + 127) / 128) + wave2 - 1) / wave2) * 0.6;
         // (with one token tile the second CTA of a pair has no rows, yet from ~20 K stages on sharing the weight
         // rows still wins: 64 x 8192 x 8192 12.6 us against 13.3 us with 128x64 tiles)
         if ((M > 128 || k_tiles_total >= 20) && N > 128 && k_splits == 1 && c7 < best) {
@@ -136,7 +137,7 @@ static void plan_gemm(int64_t M, int64_t N, int64_t K, int sms, int k_splits, in
         // few tiles (one or two token tiles): 64 weight rows per CTA put twice as many SMs on the weight stream; every
         // CTA re-reads the token tile, which costs per K stage, so from ~20 stages on it is rated 1.4x
         // (256 x 4096 x 14336: 20.0 us against 16.6 us with pair 256x128)
-        const double c6 = static_cast<double>((mt * ((N + 63) / 64) + 147) / 148) * 0.45 * (k_tiles_total >= 20 ? 1.4 : 1.0);
+        const double c6 = static_cast<double>((mt * ((N + 63) / 64) + wave1 - 1) / wave1) * 0.45 * (k_tiles_total >= 20 ? 1.4 : 1.0);
         if (mt <= 2 && c6 < best) path = 6;
     }
     if (k_splits > 1 && path != 1 && path != 2 && path != 6) path = 1;
@@ -225,31 +226,34 @@ extern "C" int nvfp4_gemm_last_status(void* stream, uint32_t* status_host) {
 // Tensor-pipe rate probe: `stages` x 4 block-scaled FP4 MMAs per SM on operands resident in shared memory; time the
 // launch with events on `stream`.  pair == 0: one CTA per SM, M = 128, N = 256, K = 64 per instruction; pair != 0:
 // a CTA pair (cta_group::2) per two SMs, M = 256, N = 256, K = 64 per instruction -- the form the large-shape
-// kernels use.  Work done either way: *sms_out * stages * 4 * 2 * 128 * 256 * 64 flop (*sms_out = SMs used).
+// kernels use; pair == 2 (testing hook): the pair == 0 kernel with its last tcgen05.commit left out, so that its
+// final wait ends at the wait limit and the status word is set (nothing faults, TMEM is freed).  Work done either way: *sms_out * stages * 4 * 2 * 128 * 256 * 64 flop (*sms_out = SMs used).
 // Bounded: stages <= 1 << 20.
 extern "C" int nvfp4_gemm_peak_probe(int stages, int pair_mode, int* sms_out, void* stream) {
     using namespace nvfp4::gemm;
     if (stages <= 0 || stages > (1 << 20)) return NVFP4_ERR_BAD_RANGE;
+    if (pair_mode < 0 || pair_mode > 2) return NVFP4_ERR_BAD_ENUM;
     int dev = 0, sms = 0;
     cudaError_t e = cudaGetDevice(&dev);
     if (e == cudaSuccess) e = cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev);
     if (e != cudaSuccess) return static_cast<int>(e);
     cudaStream_t s = static_cast<cudaStream_t>(stream);
-    if (!pair_mode) {
-        e = cudaFuncSetAttribute(peak::fp4_peak_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, peak::kSmemBytes);
+    if (pair_mode != 1) {
+        e = cudaFuncSetAttribute(peak::fp4_peak_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, kGemmDynSmemBytes);
         if (e != cudaSuccess) return static_cast<int>(e);
         if (sms_out) *sms_out = sms;
-        peak::fp4_peak_kernel<<<sms, peak::kPeakThreads, peak::kSmemBytes, s>>>(stages);
+        // whole SM: it takes all TMEM columns
+        peak::fp4_peak_kernel<<<sms, peak::kPeakThreads, kGemmDynSmemBytes, s>>>(stages, pair_mode == 2 ? 1 : 0);
         return static_cast<int>(cudaGetLastError());
     }
-    e = cudaFuncSetAttribute(peak::fp4_peak_pair_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, peak::kPairSmemBytes);
+    e = cudaFuncSetAttribute(peak::fp4_peak_pair_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, kGemmDynSmemBytes);
     if (e != cudaSuccess) return static_cast<int>(e);
     const int ctas = sms / 2 * 2;
     if (sms_out) *sms_out = ctas;
     cudaLaunchConfig_t cfg = {};
     cfg.gridDim = dim3(ctas, 1, 1);
     cfg.blockDim = dim3(peak::kPeakThreads, 1, 1);
-    cfg.dynamicSmemBytes = peak::kPairSmemBytes;
+    cfg.dynamicSmemBytes = kGemmDynSmemBytes;
     cfg.stream = s;
     cudaLaunchAttribute attr[1];
     attr[0].id = cudaLaunchAttributeClusterDimension;
@@ -260,3 +264,18 @@ extern "C" int nvfp4_gemm_peak_probe(int stages, int pair_mode, int* sms_out, vo
     cfg.numAttrs = 1;
     return static_cast<int>(cudaLaunchKernelEx(&cfg, peak::fp4_peak_pair_kernel, stages));
 }
+
+// Testing hook: the limit (nanoseconds, 1 us .. 10 s) after which a wait inside the GEMM kernels of the current device
+// gives up and records a status word; 0 restores the default of 2 s.  Synchronous (it copies to a device symbol).
+extern "C" int nvfp4_gemm_set_wait_limit_ns(uint64_t ns) {
+    if (ns == 0) ns = nvfp4::gemm::kWaitLimitNs;
+    if (ns < 1000ull || ns > 10000000000ull) return NVFP4_ERR_BAD_RANGE;
+    return static_cast<int>(cudaMemcpyToSymbol(nvfp4::gemm::g_gemm_wait_limit_ns, &ns, sizeof(ns)));
+}
+
+#ifdef NVFP4_GEMM_TRACE
+// Debugging builds only: device buffer of 64 counters the kernels add their progress marks to (NULL = off).
+extern "C" int nvfp4_gemm_set_trace(uint32_t* counters) {
+    return static_cast<int>(cudaMemcpyToSymbol(nvfp4::gemm::g_gemm_trace, &counters, sizeof(counters)));
+}
+#endif

@@ -105,6 +105,7 @@ gemm_pair_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_consta
     const uint32_t rank = cluster_ctarank();           // 0 = leader (issues the MMAs)
     const int pair_id = blockIdx.x >> 1;
     const int num_pairs = gridDim.x >> 1;
+    if (threadIdx.x == 0) trace_mark(1, 0);
 
     if (threadIdx.x == 0) {
         for (int s = 0; s < C::kStages; ++s) {
@@ -124,13 +125,15 @@ gemm_pair_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_consta
                          smem_u32(const_cast<uint32_t*>(tmem_slot))),
                      "r"(kTmemCols)
                      : "memory");
-        asm volatile("tcgen05.relinquish_alloc_permit.cta_group::2.sync.aligned;" ::: "memory");
+        if (lane == 0) trace_mark(1, 1);
     }
     tc_fence_before();
     __syncthreads();
+    if (threadIdx.x == 0) trace_mark(1, 9);
     cluster_sync_all();   // the peer's barriers exist before anything is signalled across CTAs
     tc_fence_after();
     const uint32_t tmem_base = *tmem_slot;
+    if (threadIdx.x == 0) trace_mark(1, 2);
 
     const int m_tiles = (p.M + 255) / 256;
     const int n_tiles = (p.N + BN - 1) / BN;
@@ -297,6 +300,7 @@ gemm_pair_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_consta
         }
     }
 
+    if (lane == 0) trace_mark(1, warp == 0 ? 3 : warp == 1 ? 4 : 5);
     // ---------------------------------------------------------------------- teardown
     if (*abort_flag) {
         const uint64_t t0 = global_timer_ns();
@@ -304,11 +308,20 @@ gemm_pair_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_consta
     }
     tc_fence_before();
     __syncthreads();
+    if (threadIdx.x == 0) trace_mark(1, 6);
     cluster_sync_all();   // neither CTA leaves while its partner may still signal or read it
+    if (threadIdx.x == 0) trace_mark(1, 7);
     if (warp == 1) {
         tc_fence_after();
+        asm volatile("tcgen05.relinquish_alloc_permit.cta_group::2.sync.aligned;" ::: "memory");
         asm volatile("tcgen05.dealloc.cta_group::2.sync.aligned.b32 %0, %1;" ::"r"(tmem_base), "r"(kTmemCols) : "memory");
+        if (lane == 0) trace_mark(1, 8);
     }
+    // cta_group::2 allocation state spans both SMs of the pair.  If one CTA left right after its own dealloc, another
+    // kernel's CTA could start on that SM and allocate while the partner's dealloc for the pair is still to come;
+    // with several GEMM kernels running at once that left a later tcgen05.alloc waiting for ever.  Both CTAs
+    // therefore stay until both deallocations have been issued.
+    cluster_sync_all();
 }
 
 // Scale buffer as a 2-D array of 8-byte words: row = 128-row group, 2048 B (one K tile) per box.
@@ -334,7 +347,8 @@ static int launch_pair(const uint8_t* a, const uint8_t* b, const GemmParams& p, 
     if (st == NVFP4_OK) st = make_scale_map(&msa, p.sfa, p.sfa_groups, p.sf_group_stride);
     if (st == NVFP4_OK) st = make_scale_map(&msb, p.sfb, p.sfb_groups, p.sf_group_stride);
     if (st != NVFP4_OK) return st;
-    cudaError_t e = cudaFuncSetAttribute(gemm_pair_kernel<BN>, cudaFuncAttributeMaxDynamicSharedMemorySize, C::kSmemBytes);
+    static_assert(C::kSmemBytes <= kGemmDynSmemBytes, "ring does not fit");
+    cudaError_t e = cudaFuncSetAttribute(gemm_pair_kernel<BN>, cudaFuncAttributeMaxDynamicSharedMemorySize, kGemmDynSmemBytes);
     if (e != cudaSuccess) return static_cast<int>(e);
     int dev = 0, sms = 148;
     cudaGetDevice(&dev);
@@ -344,7 +358,7 @@ static int launch_pair(const uint8_t* a, const uint8_t* b, const GemmParams& p, 
     cudaLaunchConfig_t cfg = {};
     cfg.gridDim = dim3(2 * pairs, 1, 1);
     cfg.blockDim = dim3(kThreads, 1, 1);
-    cfg.dynamicSmemBytes = C::kSmemBytes;
+    cfg.dynamicSmemBytes = kGemmDynSmemBytes;
     cfg.stream = stream;
     cudaLaunchAttribute attr[1];
     attr[0].id = cudaLaunchAttributeClusterDimension;

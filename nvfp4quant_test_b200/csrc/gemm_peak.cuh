@@ -19,7 +19,10 @@ constexpr int kSfBytes = 2048 + 4096;            // scales of A (one 128-row gro
 constexpr int kSmemBytes = kABytes + kBBytes + kSfBytes + 1024 + 64;
 constexpr int kBatch = 16;                       // K stages (4 MMAs each) per commit
 
-__global__ void __launch_bounds__(kPeakThreads, 1) fp4_peak_kernel(int stages) {
+// skip_last_commit != 0 (testing hook): the last batch is issued without its tcgen05.commit, so the wait for it can
+// only end by running into the wait limit; the kernel then records its status word, lets the queued MMAs finish,
+// frees its TMEM and returns like any other launch.
+__global__ void __launch_bounds__(kPeakThreads, 1) fp4_peak_kernel(int stages, int skip_last_commit) {
     extern __shared__ uint8_t smem_raw[];
     const uint32_t raw_addr = smem_u32(smem_raw);
     const uint32_t base = (raw_addr + 1023u) & ~1023u;
@@ -98,7 +101,7 @@ __global__ void __launch_bounds__(kPeakThreads, 1) fp4_peak_kernel(int stages) {
                         tc_mma_lohi(tmem_base, a_lo + 2 * kb, b_lo + 2 * kb, idesc, sfa_t + 4 * kb, sfb_t + 8 * kb,
                                     (s0 + s + kb) > 0 ? 1u : 0u);
                 }
-                tc_commit(bar_base + 8u * b);
+                if (!(skip_last_commit && s0 + kBatch >= stages)) tc_commit(bar_base + 8u * b);
             }
             __syncwarp();
         }
@@ -164,7 +167,6 @@ __global__ void __launch_bounds__(kPeakThreads, 1) fp4_peak_pair_kernel(int stag
                          smem_u32(const_cast<uint32_t*>(tmem_slot))),
                      "r"(kTmemCols)
                      : "memory");
-        asm volatile("tcgen05.relinquish_alloc_permit.cta_group::2.sync.aligned;" ::: "memory");
     }
     tc_fence_before();
     __syncthreads();
@@ -208,7 +210,10 @@ __global__ void __launch_bounds__(kPeakThreads, 1) fp4_peak_pair_kernel(int stag
                         tc_mma_pair(tmem_base, a_lo + 2 * kb, b_lo + 2 * kb, idesc, sfa_t + 4 * kb, sfb_t + 8 * kb,
                                     (s0 + s + kb) > 0 ? 1u : 0u);
                 }
-                tc_commit_pair(bar_base + 8u * b);   // arrives on this barrier in both CTAs; only the leader waits
+                // arrive on the leader's barrier only: the peer waits on nothing, and an arrival it never observes
+                // could still be on its way when it leaves
+                asm volatile("tcgen05.commit.cta_group::2.mbarrier::arrive::one.shared::cluster.b64 [%0];" ::"r"(bar_base + 8u * b)
+                             : "memory");
             }
             __syncwarp();
         }
@@ -227,8 +232,10 @@ __global__ void __launch_bounds__(kPeakThreads, 1) fp4_peak_pair_kernel(int stag
     cluster_sync_all();   // the leader's MMAs read the peer's shared memory and TMEM: nobody leaves before they are done
     if (warp == 1) {
         tc_fence_after();
+        asm volatile("tcgen05.relinquish_alloc_permit.cta_group::2.sync.aligned;" ::: "memory");
         asm volatile("tcgen05.dealloc.cta_group::2.sync.aligned.b32 %0, %1;" ::"r"(tmem_base), "r"(kTmemCols) : "memory");
     }
+    cluster_sync_all();   // both CTAs stay until both deallocations of the pair have been issued (see gemm_pair_kernel)
 }
 
 }  // namespace peak

@@ -362,9 +362,15 @@ static int launch_skinny(const uint8_t* x, const uint8_t* w, const GemmParams& g
     // the ring doubles as the reduce-scatter buffers: the partial tile plus one slot per rank of the owned columns
     while (ranks > 1 && (2 * BT + 8) * 512 > p.stages * C::kStageBytes) ++p.stages;
     if (p.stages > C::kMaxStages) return NVFP4_ERR_UNSUPPORTED;
-    const int smem = p.stages * C::kStageBytes + 1024 + 256;
-    cudaError_t e = cudaFuncSetAttribute(skinny_kernel<BT>, cudaFuncAttributeMaxDynamicSharedMemorySize,
-                                         C::kMaxStages * C::kStageBytes + 1024 + 256);
+    // Co-resident CTAs must never want more than the 512 TMEM columns of an SM between them (a CTA that waits in
+    // tcgen05.alloc while its cluster peers wait for it is a deadlock).  Shared memory is what bounds co-residency, so
+    // every CTA asks for at least the share of the SM's shared memory that matches its share of the TMEM columns
+    // (1 KiB per CTA is reserved by the system): whatever mix of these kernels fits an SM then fits its TMEM too.
+    constexpr int kMinSmem = 233472 / (kTmemCols / C::kTmemCols) - 1024;   // 128 columns: 57344 (4 CTAs), 256: 115712 (2)
+    int smem = p.stages * C::kStageBytes + 1024 + 256;
+    if (smem < kMinSmem) smem = kMinSmem;
+    static_assert(C::kMaxStages * C::kStageBytes + 1024 + 256 <= kGemmDynSmemBytes, "ring does not fit");
+    cudaError_t e = cudaFuncSetAttribute(skinny_kernel<BT>, cudaFuncAttributeMaxDynamicSharedMemorySize, kGemmDynSmemBytes);
     if (e != cudaSuccess) return static_cast<int>(e);
     cudaLaunchConfig_t cfg = {};
     cfg.gridDim = dim3(n_tiles * ranks, 1, 1);

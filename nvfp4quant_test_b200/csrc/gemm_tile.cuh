@@ -75,6 +75,7 @@ gemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant__ 
 
     const int warp = __shfl_sync(0xffffffffu, threadIdx.x >> 5, 0);
     const int lane = threadIdx.x & 31;
+    if (threadIdx.x == 0) trace_mark(0, 0);
 
     if (threadIdx.x == 0) {
         for (int s = 0; s < C::kStages; ++s) {
@@ -95,6 +96,7 @@ gemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant__ 
                      "r"(kTmemCols)
                      : "memory");
         asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;" ::: "memory");
+        if (lane == 0) trace_mark(0, 1);
     }
     // The producer warp initialised the mbarriers itself (thread 0) and needs neither TMEM nor the other warps, so it
     // only ARRIVES on the prologue barrier and starts its copies at once; the first HBM round trip then overlaps the
@@ -108,6 +110,7 @@ gemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant__ 
     }
     tc_fence_after();
     const uint32_t tmem_base = *tmem_slot;   // meaningful in warps 1..5 only
+    if (threadIdx.x == 32) trace_mark(0, 2);
 
     const int m_tiles = (p.M + kBM - 1) / kBM;
     const int n_tiles = (p.N + BN - 1) / BN;
@@ -314,6 +317,7 @@ gemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant__ 
         }
     }
 
+    if (lane == 0) trace_mark(0, warp == 0 ? 3 : warp == 1 ? 4 : 5);
     // ---------------------------------------------------------------------- teardown
     if (*abort_flag) {
         // give any bulk copy still in flight time to land before shared memory is released
@@ -322,9 +326,11 @@ gemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant__ 
     }
     tc_fence_before();
     __syncthreads();
+    if (threadIdx.x == 0) trace_mark(0, 6);
     if (warp == 1) {
         tc_fence_after();
         asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(tmem_base), "r"(kTmemCols) : "memory");
+        if (lane == 0) trace_mark(0, 8);
     }
 }
 
@@ -382,14 +388,15 @@ static int launch(const uint8_t* a, const uint8_t* b, const GemmParams& p, cudaS
     st = make_operand_map(&mb, b, p.N, p.K / 2, BN);
     if (st != NVFP4_OK) return st;
     // function attributes are per device; setting it on every launch keeps multi-device processes correct
-    cudaError_t e = cudaFuncSetAttribute(gemm_kernel<BN>, cudaFuncAttributeMaxDynamicSharedMemorySize, C::kSmemBytes);
+    static_assert(C::kSmemBytes <= kGemmDynSmemBytes, "ring does not fit");
+    cudaError_t e = cudaFuncSetAttribute(gemm_kernel<BN>, cudaFuncAttributeMaxDynamicSharedMemorySize, kGemmDynSmemBytes);
     if (e != cudaSuccess) return static_cast<int>(e);
     int dev = 0, sms = 148;
     cudaGetDevice(&dev);
     cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev);
     const int tiles = ((p.M + kBM - 1) / kBM) * ((p.N + BN - 1) / BN) * p.k_splits;
     const int grid = tiles < sms ? tiles : sms;
-    gemm_kernel<BN><<<grid, kThreads, C::kSmemBytes, stream>>>(ma, mb, p);
+    gemm_kernel<BN><<<grid, kThreads, kGemmDynSmemBytes, stream>>>(ma, mb, p);
     e = cudaGetLastError();
     if (e != cudaSuccess || p.k_splits == 1) return static_cast<int>(e);
     const int64_t mn = static_cast<int64_t>(p.M) * p.N;

@@ -105,7 +105,9 @@ extern "C" int nvfp4_global_scale_launch(const void* x, int x_dtype, int64_t num
     int64_t blocks = (nvec + kGsThreads - 1) / kGsThreads;
     // a few resident blocks per SM is enough to keep HBM busy; more only adds atomics
     // measured at 8192 x 8192 bf16: 1 CTA per SM 29.0 us, 2: 25.4, 3: 25.0, 4: 25.2-26.5, 8: 27.5, 16: 29.2
-    const int64_t cap = 148 * 3;
+    int dev = 0, sms = 148;
+    if (cudaGetDevice(&dev) == cudaSuccess) cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev);
+    const int64_t cap = static_cast<int64_t>(sms) * 3;
     if (blocks > cap) blocks = cap;
     if (blocks < 1) blocks = 1;
     cudaStream_t s = static_cast<cudaStream_t>(stream);

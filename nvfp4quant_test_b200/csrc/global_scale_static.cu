@@ -27,6 +27,8 @@
 // the same two fp32 operations).
 #include <cuda_fp16.h>
 
+#include <atomic>
+
 #include "common.cuh"
 
 namespace nvfp4 {
@@ -113,9 +115,12 @@ __global__ void __launch_bounds__(kThreads) global_scale_static_kernel(const voi
     }
 }
 
-// Device address of g_static_scratch, looked up once per device with that device current.
+// Device address of g_static_scratch, looked up once per device with that device current.  The address belongs to
+// the device's primary context: it stays valid until that context is destroyed (cudaDeviceReset), after which this
+// library must not be used from the old process state anyway.  Entries are atomics: two host threads making their
+// first call at once both look the address up and store the same value.
 uint32_t* static_scratch_for_current_device(cudaError_t* err) {
-    static uint32_t* cache[kMaxDevices] = {};
+    static std::atomic<uint32_t*> cache[kMaxDevices] = {};
     int dev = -1;
     *err = cudaGetDevice(&dev);
     if (*err != cudaSuccess) return nullptr;
@@ -123,13 +128,15 @@ uint32_t* static_scratch_for_current_device(cudaError_t* err) {
         *err = cudaErrorInvalidDevice;
         return nullptr;
     }
-    if (!cache[dev]) {
+    uint32_t* addr = cache[dev].load(std::memory_order_acquire);
+    if (!addr) {
         void* p = nullptr;
         *err = cudaGetSymbolAddress(&p, g_static_scratch);
         if (*err != cudaSuccess) return nullptr;
-        cache[dev] = static_cast<uint32_t*>(p);
+        addr = static_cast<uint32_t*>(p);
+        cache[dev].store(addr, std::memory_order_release);
     }
-    return cache[dev];
+    return addr;
 }
 
 }  // namespace

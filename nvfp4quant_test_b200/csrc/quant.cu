@@ -73,6 +73,7 @@ struct QuantParams {
 
 __device__ uint32_t g_quant_status;   // 0 = ok; 1 = the grid-wide wait of the fused kernel gave up
 constexpr uint64_t kFusedWaitLimitNs = 2000000000ull;
+__device__ uint64_t g_fused_wait_limit_ns = kFusedWaitLimitNs;   // settable from the host (nvfp4_quant_fused_set_wait_limit_ns)
 
 template <int DT>
 __device__ __forceinline__ void load16(const void* base, int64_t elem, float v[16]);
@@ -344,25 +345,6 @@ quant_kernel(const QuantParams p) {
     constexpr bool FUSED = IMPL == 4;
     static_assert(!FUSED || VARIANT != NVFP4_VARIANT_AMAX, "the fused variant covers the two sweeps");
     float gs_inv = FUSED ? 0.0f : __ldg(p.gs_inv);
-    {
-        float4 e;
-        if (VARIANT == NVFP4_VARIANT_AMAX) {   // tab[raw].x = multiplier for scale byte raw (entries 0..127 used)
-            const uint32_t raw = threadIdx.x & 127;
-            const float s = e4m3_to_f32(raw);
-            e.x = e.y = (raw == 0) ? 0.0f : rcp_approx_ftz(__fmul_rn(s, rcp_approx_ftz(gs_inv)));
-            e.z = 0.0f;
-            e.w = __uint_as_float(raw);
-        } else {
-            const uint32_t raw = static_cast<uint32_t>(min(max(static_cast<int>(threadIdx.x) - kTabPad, 1), 126));
-            const float s = e4m3_to_f32(raw);
-            e.x = e.y = div_full(1.0f, s);
-            e.z = __fmul_rn(s, s);
-            e.w = __uint_as_float(raw);
-        }
-        tab[threadIdx.x] = e;
-    }
-    __syncthreads();
-
     // Body 6 = body 3 with a two-dimensional grid: blockIdx.x is the row, blockIdx.y the 256-block column chunk.
     // The row is then uniform over the CTA, so the division below, the row part of the addresses and most of the
     // tiled scale offset leave the per-thread instruction stream.  Used when the slot grid is a whole number of
@@ -398,6 +380,21 @@ quant_kernel(const QuantParams p) {
         if (VARIANT == NVFP4_VARIANT_WEIGHTED) load16<NVFP4_DT_F32>(p.importance, col * kBlock, w);
     }
 
+    // The global scale and the block's elements were requested above; the candidate table is built while they are
+    // on their way (at small batch sizes nothing else hides a trip to memory).  The amax variant needs no table: its
+    // one multiplier per block is two reciprocals away from the scale byte, and without the table there is no
+    // CTA-wide barrier between the loads and their use.
+    if (VARIANT != NVFP4_VARIANT_AMAX) {
+        const uint32_t raw = static_cast<uint32_t>(min(max(static_cast<int>(threadIdx.x) - kTabPad, 1), 126));
+        const float s = e4m3_to_f32(raw);
+        float4 e;
+        e.x = e.y = div_full(1.0f, s);
+        e.z = __fmul_rn(s, s);
+        e.w = __uint_as_float(raw);
+        tab[threadIdx.x] = e;
+        __syncthreads();
+    }
+
     if (FUSED) {
         // tensor-wide maximum on fp32 magnitude bit patterns (a NaN pattern is larger than +inf, as torch's max wants)
         __shared__ uint32_t warp_max[kThreads / 32];
@@ -415,14 +412,16 @@ quant_kernel(const QuantParams p) {
             volatile uint32_t* sc = p.fused_scratch;
             atomicMax(p.fused_scratch, b);
             __threadfence();
-            atomicAdd(p.fused_scratch + 1, 1u);
+            // scratch[3] != 0 is a testing hook: CTA 0 then withholds its arrival, so that every wait below runs into
+            // the limit and the error path (status word, no hang) can be exercised
+            if (!(blockIdx.x == 0 && sc[3] != 0u)) atomicAdd(p.fused_scratch + 1, 1u);
             // every CTA of a cooperative launch is resident, so the others will arrive; bounded all the same
             uint64_t t0 = 0;
             asm volatile("mov.u64 %0, %globaltimer;" : "=l"(t0));
             while (sc[1] < gridDim.x) {
                 uint64_t t1;
                 asm volatile("mov.u64 %0, %globaltimer;" : "=l"(t1));
-                if (t1 - t0 > kFusedWaitLimitNs) {
+                if (t1 - t0 > g_fused_wait_limit_ns) {
                     atomicExch(&g_quant_status, 1u);
                     break;
                 }
@@ -460,7 +459,8 @@ quant_kernel(const QuantParams p) {
         const float amax = max_abs16(v);
         const float sf = __fmul_rn(gs_inv, __fmul_rn(amax, rcp_approx_ftz(6.0f)));
         sbyte = f32_to_e4m3(sf);
-        inv = tab[sbyte & 0x7f].x;
+        const uint32_t raw = sbyte & 0x7fu;
+        inv = (raw == 0) ? 0.0f : rcp_approx_ftz(__fmul_rn(e4m3_to_f32(raw), rcp_approx_ftz(gs_inv)));
     } else {
         const uint64_t gs2 = pack_f32x2(gs_inv, gs_inv);
 #pragma unroll
@@ -705,4 +705,12 @@ extern "C" int nvfp4_quant_launch(int variant, const void* x, int x_dtype, const
                                   int64_t padded_n, int lower, int upper, int swizzled, void* stream) {
     return nvfp4_quant_launch_impl(0, variant, x, x_dtype, importance, gs_inv, codes, scales, m, n, padded_n, lower,
                                    upper, swizzled, stream);
+}
+
+// Testing hook: the limit (nanoseconds, 1 us .. 10 s) of the fused kernel's grid-wide wait on the current device;
+// 0 restores the default of 2 s.  Synchronous.
+extern "C" int nvfp4_quant_fused_set_wait_limit_ns(uint64_t ns) {
+    if (ns == 0) ns = nvfp4::kFusedWaitLimitNs;
+    if (ns < 1000ull || ns > 10000000000ull) return NVFP4_ERR_BAD_RANGE;
+    return static_cast<int>(cudaMemcpyToSymbol(nvfp4::g_fused_wait_limit_ns, &ns, sizeof(ns)));
 }

@@ -16,9 +16,25 @@ constexpr int kBKBytes = 128;     // bytes of K per stage row (= 256 FP4 element
 constexpr int kBK = 256;          // elements of K per stage
 constexpr int kThreads = 192;
 constexpr int kTmemCols = 512;
+// Every tile / pair kernel asks for the whole shared memory of an SM (227 KiB), whatever its ring needs: a CTA that
+// takes all 512 TMEM columns must be alone on its SM, and identical footprints keep concurrently running GEMM
+// kernels from being placed differently.
+constexpr int kGemmDynSmemBytes = 232448;
 constexpr uint64_t kWaitLimitNs = 2000000000ull;  // 2 s: far above any legitimate wait
+__device__ uint64_t g_gemm_wait_limit_ns = kWaitLimitNs;   // what the waits use; settable from the host (nvfp4_gemm_set_wait_limit_ns)
 
 __device__ uint32_t g_gemm_status;  // 0 = ok; else (role << 24) | detail of the wait that expired
+
+// Progress counters for debugging builds (-DNVFP4_GEMM_TRACE): how many CTAs of each kernel family passed each point.
+#ifdef NVFP4_GEMM_TRACE
+__device__ uint32_t* g_gemm_trace = nullptr;
+__device__ __forceinline__ void trace_mark(int family, int point) {
+    uint32_t* t = g_gemm_trace;
+    if (t) atomicAdd(t + family * 16 + point, 1u);
+}
+#else
+__device__ __forceinline__ void trace_mark(int, int) {}
+#endif
 
 // ---------------------------------------------------------------------------------------------
 // PTX wrappers
@@ -56,7 +72,7 @@ __device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t parity, volatil
     for (;;) {
         if (mbar_try_wait(bar, parity)) return true;
         if (*abort_flag) return false;
-        if (global_timer_ns() - t0 > kWaitLimitNs) {
+        if (global_timer_ns() - t0 > g_gemm_wait_limit_ns) {
             *abort_flag = 1;
             atomicCAS(&g_gemm_status, 0u, code);
             return false;

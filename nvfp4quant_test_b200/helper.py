@@ -14,7 +14,7 @@ FP4_E2M1_MAX = 6.0
 FP8_E4M3_MAX_NVFP4 = 448.0
 FP8_E4M3_MAX_4OVER6 = 256.0
 
-_scratch: dict = {}
+_scratch = _lib.StreamScratch(2)
 
 
 def get_nvfp4_global_scale(x: torch.Tensor, FP8_MAX: float = FP8_E4M3_MAX_NVFP4):
@@ -23,11 +23,13 @@ def get_nvfp4_global_scale(x: torch.Tensor, FP8_MAX: float = FP8_E4M3_MAX_NVFP4)
         raise ValueError("x must be a CUDA tensor")
     if not x.is_contiguous():
         x = x.contiguous()
+    if x.data_ptr() & 15:
+        # the kernel reads 16-byte vectors; a view that starts in the middle of one (x.view(-1)[1:], a row slice of a
+        # matrix with an odd width) is copied to aligned storage, so that any tensor the reference's
+        # x.abs().max() accepts works here too
+        x = x.clone()
     stream = _lib.current_stream_ptr(x.device)
-    key = (x.device, stream)
-    scratch = _scratch.get(key)
-    if scratch is None:
-        scratch = _scratch[key] = torch.zeros(2, dtype=torch.int32, device=x.device)
+    scratch = _scratch.get(x.device, stream)
     out = torch.empty(2, dtype=torch.float32, device=x.device)
     with _lib.device_guard(x.device):
         st = _lib.lib().nvfp4_global_scale_launch(x.data_ptr(), _lib.dtype_code(x.dtype), x.numel(), float(FP8_MAX),

@@ -44,6 +44,7 @@ class HostQuantizer:
         self.ev_up = [torch.cuda.Event() for _ in range(depth)]
         self.ev_run = [torch.cuda.Event() for _ in range(depth)]
         self.ev_down = [torch.cuda.Event() for _ in range(depth)]
+        self._used = [False] * depth      # slot j's events have been recorded by an earlier chunk (of this or a previous call)
 
     def __call__(self, x_host: torch.Tensor, gs_inv: torch.Tensor, codes_host: torch.Tensor,
                  scales_host: torch.Tensor, importance: torch.Tensor | None = None) -> None:
@@ -60,13 +61,13 @@ class HostQuantizer:
             j = i % self.depth
             n = b - a
             with torch.cuda.stream(self.s_up):
-                if i >= self.depth:
+                if self._used[j]:
                     self.s_up.wait_event(self.ev_run[j])      # staging input free once its kernel ran
                 self.stage_in[j][:n].copy_(x_host[a:b], non_blocking=True)
                 self.ev_up[j].record(self.s_up)
             with torch.cuda.stream(self.s_run):
                 self.s_run.wait_event(self.ev_up[j])
-                if i >= self.depth:
+                if self._used[j]:
                     self.s_run.wait_event(self.ev_down[j])    # staging outputs free once downloaded
                 _launch.quant_out(self.variant, self.stage_in[j][:n], importance, gs_inv, True,
                                   self.stage_codes[j][:n], self.stage_scales[j], self.lower, self.upper)
@@ -77,5 +78,6 @@ class HostQuantizer:
                 lo, hi = scale_slab(a, b, self.blocks)
                 flat_scales[lo:hi].copy_(self.stage_scales[j][: hi - lo], non_blocking=True)
                 self.ev_down[j].record(self.s_down)
+            self._used[j] = True
         cur.wait_stream(self.s_down)
         cur.wait_stream(self.s_run)

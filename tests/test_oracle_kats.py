@@ -203,3 +203,62 @@ def test_saturation_bound_pruning_is_exact_but_removes_too_few_candidates(oracle
     assert r["pruned_by_offset"][3:].sum() == 0   # nothing at or above the base code is ever prunable this way
     # even a branch-and-bound over chain prefixes that knew the final minimum in advance would do ~60 % of the work
     assert 0.5 < r["prefix_elements"].sum() / (r["blocks"] * 176.0) < 0.7
+
+
+# Offset tables the reference's proof prints (proof/nvfp4_upper_bound.py:6-31 -> main(), proof/nvfp4_lower_bound.py:447-484
+# -> main(); also proof/proof.md:98-113, 230-236), per mantissa field b of the base code q0.
+UPPER_NORMAL = [6, 7, 6, 6, 6, 6, 6, 6]
+UPPER_SUBNORMAL = {1: 1, 2: 2, 3: 2, 4: 3, 5: 4, 6: 5, 7: 5}
+LOWER_NORMAL = [-3, -3, -2, -2, -2, -3, -3, -3]
+
+
+def test_upper_offset_table_rederived(oracle):
+    """Upper table: the largest E4M3 code strictly below 12/7 x (right end of q0's rounding cell), re-derived here
+    with exact rationals from the oracle's own E4M3 decoder, must be the table the proof prints; its maximum is the
+    +7 end of the sweep window."""
+    from fractions import Fraction
+
+    val = [Fraction(oracle.e4m3_to_f32(r)) for r in range(127)]
+
+    def upper(bits):
+        edge = (val[bits] + val[bits + 1]) / 2
+        return max(u for u in range(1, 127) if val[u] < Fraction(12, 7) * edge)
+
+    for exp in (1, 7, 13):                                   # any normal binade away from saturation gives the same offsets
+        assert [upper((exp << 3) | b) - ((exp << 3) | b) for b in range(8)] == UPPER_NORMAL
+    assert {b: upper(b) - b for b in range(1, 8)} == UPPER_SUBNORMAL
+    assert max(UPPER_NORMAL) == 7
+
+
+def test_offset_tables_hold_and_are_tight_per_mantissa_class(oracle):
+    """Per mantissa class of the base code: the fp32 exhaustive optimum over all 126 scales never leaves
+    [lower(b), upper(b)] on 120k random blocks, and the reference's own examples reach both ends of every class -
+    so neither end of the -3..+7 window (nor the round-to-nearest base) can change without this failing."""
+    rows = json.loads((GOLDEN / "proof_kats.json").read_text())
+    seen_lo, seen_hi = {}, {}
+    for k in rows:
+        if k["part"] != "normal":
+            continue
+        x = np.array(k["x_f64"], dtype=np.float32)
+        off = oracle.best_raw_exhaustive(x) - k["q0_bits"]
+        b = k["q0_bits"] & 7
+        seen_lo[b] = min(seen_lo.get(b, 99), off)
+        seen_hi[b] = max(seen_hi.get(b, -99), off)
+    assert [seen_lo[b] for b in range(8)] == LOWER_NORMAL
+    assert [seen_hi[b] for b in range(8)] == UPPER_NORMAL
+    rng = np.random.default_rng(3)
+    blocks = np.concatenate([
+        rng.standard_normal((40000, 16)), rng.laplace(size=(40000, 16)),
+        rng.standard_normal((40000, 16)) * np.where(rng.random((40000, 16)) < 0.07, 12.0, 1.0)]).astype(np.float32)
+    blocks *= np.exp2(rng.integers(-2, 5, (blocks.shape[0], 1))).astype(np.float32)
+    sixth = np.float32(1 / 6)
+    counted = 0
+    for v in blocks:
+        base = oracle.f32_to_e4m3(float(np.float32(np.abs(v).max()) * sixth))
+        if base < 16 or base >= 120:
+            continue
+        off = oracle.best_raw_exhaustive(v) - base
+        b = base & 7
+        assert LOWER_NORMAL[b] <= off <= UPPER_NORMAL[b], (base, off, v.tolist())
+        counted += 1
+    assert counted > 110000

@@ -74,3 +74,35 @@ def test_static_scratch_entry_point_rejects_what_it_cannot_serve(cuda_lib):
     assert L.nvfp4_global_scale_launch_static(None, 0, 16, 448.0, P, None) == -1
     assert L.nvfp4_global_scale_launch_static(P, 0, 16, 448.0, None, None) == -1
     torch.cuda.synchronize()
+
+
+def test_static_scratch_entry_point_allocates_nothing_and_chains_on_a_stream(cuda_lib):
+    """The property the entry point exists for: device memory in use does not change across calls (cudaMemGetInfo
+    before and after), and calls issued back to back on one stream - no synchronisation between them, the case the
+    header promises is safe because each call re-clears its counter in stream order - all give the right bits."""
+    from nvfp4quant_test_b200 import _lib
+
+    L = _bind(cuda_lib)
+    stream = torch.cuda.current_stream().cuda_stream
+    gen = torch.Generator(device="cuda")
+    gen.manual_seed(9)
+    xs = [torch.randn((2048, 4096), generator=gen, device="cuda").to(torch.bfloat16) * (i + 1) for i in range(6)]
+    xs.append(torch.randn((777, 1001), generator=gen, device="cuda"))                    # fp32, ragged
+    outs = torch.full((len(xs), 2), -1.0, dtype=torch.float32, device="cuda")
+    want = torch.empty((len(xs), 2), dtype=torch.float32, device="cuda")
+    scratch = torch.zeros(2, dtype=torch.int32, device="cuda")
+    for i, x in enumerate(xs):
+        _lib.check(L.nvfp4_global_scale_launch(x.data_ptr(), _lib.dtype_code(x.dtype), x.numel(), 448.0,
+                                               want[i].data_ptr(), scratch.data_ptr(), stream), "regular")
+    _lib.check(L.nvfp4_global_scale_launch_static(xs[0].data_ptr(), 0, xs[0].numel(), 448.0, outs[0].data_ptr(), stream),
+               "static")            # first call on this device (if no earlier test made it): resolves the symbol address
+    torch.cuda.synchronize()
+    free_before, _ = torch.cuda.mem_get_info()
+    for i, x in enumerate(xs):      # back to back, one stream, no synchronisation in between
+        st = L.nvfp4_global_scale_launch_static(x.data_ptr(), _lib.dtype_code(x.dtype), x.numel(), 448.0,
+                                                outs[i].data_ptr(), stream)
+        assert st == 0
+    torch.cuda.synchronize()
+    free_after, _ = torch.cuda.mem_get_info()
+    assert free_after == free_before, (free_before, free_after)
+    assert torch.equal(outs.view(torch.int32), want.view(torch.int32))
