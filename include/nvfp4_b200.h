@@ -162,6 +162,22 @@ int nvfp4_gemm_launch(const uint8_t* a, const uint8_t* b, const uint8_t* sfa, co
                       const float* alpha, void* out_bf16, int64_t M, int64_t N, int64_t K,
                       void* workspace, size_t workspace_bytes, void* stream);
 size_t nvfp4_gemm_workspace_bytes(int64_t M, int64_t N, int64_t K);
+
+/*
+ * The same GEMM for a weight that is used many times (a model's linear layer; no counterpart in vllm's op, which
+ * takes raw tensors on every call).  nvfp4_gemm_prepare encodes the weight's tensor maps once and returns a handle;
+ * nvfp4_gemm_launch_prepared(handle, a, sfa, alpha, out, M, ...) then computes out[M, N] exactly as
+ * nvfp4_gemm_launch(a, b, sfa, sfb, alpha, out, M, N, K, ...) would, with less host work per call.
+ * Ownership: the handle is a small HOST object owned by the caller and freed with nvfp4_gemm_release (NULL is
+ * accepted).  It refers to b / sfb without owning them: keep both allocated at the same addresses with the same
+ * shape while the handle lives (their contents may be rewritten in place).  A handle belongs to the device that was
+ * current in nvfp4_gemm_prepare; launching it with another device current returns NVFP4_ERR_UNSUPPORTED.  Handles may
+ * be used from several host threads at once (they are read-only after creation).
+ */
+int nvfp4_gemm_prepare(const uint8_t* b, const uint8_t* sfb, int64_t N, int64_t K, void** handle_host);
+int nvfp4_gemm_launch_prepared(void* handle, const uint8_t* a, const uint8_t* sfa, const float* alpha, void* out_bf16,
+                               int64_t M, void* workspace, size_t workspace_bytes, void* stream);
+int nvfp4_gemm_release(void* handle);
 /* Testing hook (process-wide): 0 = pick the GEMM kernel by shape (default), 1 = 128x128 tiles,
  * 2 = 128x256 tiles, 3 = CTA-pair 256x256 tiles, 4 = CTA-pair 256x192 tiles, 5 = skinny kernel for
  * M <= 128 (weights on the MMA rows, K ranges across a thread-block cluster; the default up to 32 tokens),

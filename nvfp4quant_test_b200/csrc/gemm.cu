@@ -18,6 +18,8 @@
 // This file holds the C entry points and the kernel choice; the kernels live in gemm_tile.cuh (one CTA per tile),
 // gemm_pair.cuh (CTA pairs, cta_group::2) and gemm_skinny.cuh (decode-sized batches, K ranges across a cluster),
 // all on the PTX wrappers of tc_ptx.cuh.  One translation unit, so that there is one status word.
+#include <new>
+
 #include "gemm_tile.cuh"
 #include "gemm_pair.cuh"
 #include "gemm_skinny.cuh"
@@ -153,9 +155,9 @@ extern "C" int nvfp4_gemm_plan(int64_t M, int64_t N, int64_t K, int sms, int* pa
     return NVFP4_OK;
 }
 
-extern "C" int nvfp4_gemm_launch(const uint8_t* a, const uint8_t* b, const uint8_t* sfa, const uint8_t* sfb,
-                                 const float* alpha, void* out_bf16, int64_t M, int64_t N, int64_t K, void* workspace,
-                                 size_t workspace_bytes, void* stream) {
+static int gemm_launch_impl(const uint8_t* a, const uint8_t* b, const uint8_t* sfa, const uint8_t* sfb,
+                            const float* alpha, void* out_bf16, int64_t M, int64_t N, int64_t K, void* workspace,
+                            size_t workspace_bytes, void* stream, const nvfp4::gemm::WeightHandle* wh) {
     using namespace nvfp4;
     if (M < 0 || N < 0 || K < 0 || (K % 64) != 0) return NVFP4_ERR_BAD_SHAPE;
     if (M == 0 || N == 0) return NVFP4_OK;
@@ -186,29 +188,85 @@ extern "C" int nvfp4_gemm_launch(const uint8_t* a, const uint8_t* b, const uint8
     // default: one band over all m-tiles (band sizes 1..16 measured within noise of it on B200)
     p.raster_group = g_gemm_raster_group > 0 ? g_gemm_raster_group : (1 << 20);
     cudaStream_t s = static_cast<cudaStream_t>(stream);
-    int dev = 0, sms = 148;
-    cudaGetDevice(&dev);
-    cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev);
+    const int sms = gemm::device_info().sms;
     int path = 0, ranges = 1;
     plan_gemm(M, N, K, sms, p.k_splits, &path, &ranges);
     if (path == 5) {
         const int forced = g_gemm_force_path == 5 ? g_gemm_force_splits : 0;
-        if (M <= 16) return gemm::skinny::launch_skinny<16>(a, b, p, forced, s);
-        if (M <= 32) return gemm::skinny::launch_skinny<32>(a, b, p, forced, s);
-        if (M <= 64) return gemm::skinny::launch_skinny<64>(a, b, p, forced, s);
-        return gemm::skinny::launch_skinny<128>(a, b, p, forced, s);
+        if (M <= 16) return gemm::skinny::launch_skinny<16>(a, b, p, forced, s, wh);
+        if (M <= 32) return gemm::skinny::launch_skinny<32>(a, b, p, forced, s, wh);
+        if (M <= 64) return gemm::skinny::launch_skinny<64>(a, b, p, forced, s, wh);
+        return gemm::skinny::launch_skinny<128>(a, b, p, forced, s, wh);
     }
     if (p.k_splits > 1) {
         const size_t need = static_cast<size_t>(p.k_splits) * static_cast<size_t>(M) * static_cast<size_t>(N) * sizeof(float);
         if (!workspace || workspace_bytes < need) return NVFP4_ERR_WORKSPACE;
         if (reinterpret_cast<uintptr_t>(workspace) & 15) return NVFP4_ERR_MISALIGNED;
     }
-    if (path == 3) return gemm::pair::launch_pair<256>(a, b, p, s);
-    if (path == 4) return gemm::pair::launch_pair<192>(a, b, p, s);
-    if (path == 7) return gemm::pair::launch_pair<128>(a, b, p, s);
-    if (path == 2) return gemm::launch<256>(a, b, p, s);
-    if (path == 6) return gemm::launch<64>(a, b, p, s);
-    return gemm::launch<128>(a, b, p, s);
+    if (path == 3) return gemm::pair::launch_pair<256>(a, b, p, s, wh);
+    if (path == 4) return gemm::pair::launch_pair<192>(a, b, p, s, wh);
+    if (path == 7) return gemm::pair::launch_pair<128>(a, b, p, s, wh);
+    if (path == 2) return gemm::launch<256>(a, b, p, s, wh);
+    if (path == 6) return gemm::launch<64>(a, b, p, s, wh);
+    return gemm::launch<128>(a, b, p, s, wh);
+}
+
+extern "C" int nvfp4_gemm_launch(const uint8_t* a, const uint8_t* b, const uint8_t* sfa, const uint8_t* sfb,
+                                 const float* alpha, void* out_bf16, int64_t M, int64_t N, int64_t K, void* workspace,
+                                 size_t workspace_bytes, void* stream) {
+    return gemm_launch_impl(a, b, sfa, sfb, alpha, out_bf16, M, N, K, workspace, workspace_bytes, stream, nullptr);
+}
+
+// A weight matrix used by many GEMM calls (a model's linear layer): its tensor maps are encoded once here instead
+// of on every launch.  The handle is a small host object; it refers to `b` / `sfb`, which the caller keeps alive and
+// unchanged in place (their contents may change, their addresses and shape may not) until nvfp4_gemm_release.
+extern "C" int nvfp4_gemm_prepare(const uint8_t* b, const uint8_t* sfb, int64_t N, int64_t K, void** handle_out) {
+    using namespace nvfp4;
+    if (!handle_out) return NVFP4_ERR_NULL_POINTER;
+    *handle_out = nullptr;
+    if (N <= 0 || K <= 0 || (K % 64) != 0) return NVFP4_ERR_BAD_SHAPE;
+    if (N > 0x7fffff00LL || K > 0x7fffff00LL) return NVFP4_ERR_TOO_LARGE;
+    if (!b || !sfb) return NVFP4_ERR_NULL_POINTER;
+    if ((reinterpret_cast<uintptr_t>(b) & 15) || (reinterpret_cast<uintptr_t>(sfb) & 15)) return NVFP4_ERR_MISALIGNED;
+    gemm::WeightHandle* h = new (std::nothrow) gemm::WeightHandle();
+    if (!h) return NVFP4_ERR_UNSUPPORTED;
+    h->magic = gemm::kWeightMagic;
+    h->device = gemm::device_info().device;
+    h->b = b;
+    h->sfb = sfb;
+    h->N = N;
+    h->K = K;
+    int st = gemm::make_operand_map(&h->rows64, b, N, K / 2, 64);
+    if (st == NVFP4_OK) st = gemm::make_operand_map(&h->rows96, b, N, K / 2, 96);
+    if (st == NVFP4_OK) st = gemm::make_operand_map(&h->rows128, b, N, K / 2, 128);
+    if (st == NVFP4_OK) st = gemm::make_operand_map(&h->rows256, b, N, K / 2, 256);
+    if (st == NVFP4_OK)
+        st = gemm::pair::make_scale_map(&h->scales, sfb, (N + 127) / 128, round_up_i64(K / 16, 4) * 128);
+    if (st != NVFP4_OK) {
+        delete h;
+        return st;
+    }
+    *handle_out = h;
+    return NVFP4_OK;
+}
+
+extern "C" int nvfp4_gemm_release(void* handle) {
+    auto* h = static_cast<nvfp4::gemm::WeightHandle*>(handle);
+    if (!h) return NVFP4_OK;
+    if (h->magic != nvfp4::gemm::kWeightMagic) return NVFP4_ERR_BAD_ENUM;
+    h->magic = 0;
+    delete h;
+    return NVFP4_OK;
+}
+
+// out[M, N] = alpha * dq(a) dq(weight)^T with a prepared weight: the same kernels and bits as nvfp4_gemm_launch.
+extern "C" int nvfp4_gemm_launch_prepared(void* handle, const uint8_t* a, const uint8_t* sfa, const float* alpha,
+                                          void* out_bf16, int64_t M, void* workspace, size_t workspace_bytes, void* stream) {
+    auto* h = static_cast<const nvfp4::gemm::WeightHandle*>(handle);
+    if (!h) return NVFP4_ERR_NULL_POINTER;
+    if (h->magic != nvfp4::gemm::kWeightMagic) return NVFP4_ERR_BAD_ENUM;
+    if (h->device != nvfp4::gemm::device_info().device) return NVFP4_ERR_UNSUPPORTED;   // prepared on another device
+    return gemm_launch_impl(a, h->b, sfa, h->sfb, alpha, out_bf16, M, h->N, h->K, workspace, workspace_bytes, stream, h);
 }
 
 extern "C" int nvfp4_gemm_last_status(void* stream, uint32_t* status_host) {

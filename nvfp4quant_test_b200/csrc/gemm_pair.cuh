@@ -339,20 +339,22 @@ static int make_scale_map(CUtensorMap* map, const void* ptr, int64_t groups, int
 }
 
 template <int BN>
-static int launch_pair(const uint8_t* a, const uint8_t* b, const GemmParams& p, cudaStream_t stream) {
+static int launch_pair(const uint8_t* a, const uint8_t* b, const GemmParams& p, cudaStream_t stream, const WeightHandle* wh) {
     using C = PairCfg<BN>;
-    CUtensorMap ma, mb, msa, msb;
+    CUtensorMap ma, msa, mb_local, msb_local;
     int st = make_operand_map(&ma, a, p.M, p.K / 2, 128);
-    if (st == NVFP4_OK) st = make_operand_map(&mb, b, p.N, p.K / 2, BN / 2);
     if (st == NVFP4_OK) st = make_scale_map(&msa, p.sfa, p.sfa_groups, p.sf_group_stride);
-    if (st == NVFP4_OK) st = make_scale_map(&msb, p.sfb, p.sfb_groups, p.sf_group_stride);
+    if (st == NVFP4_OK && !wh) st = make_operand_map(&mb_local, b, p.N, p.K / 2, BN / 2);
+    if (st == NVFP4_OK && !wh) st = make_scale_map(&msb_local, p.sfb, p.sfb_groups, p.sf_group_stride);
     if (st != NVFP4_OK) return st;
+    const CUtensorMap& mb = wh ? *wh->by_rows(BN / 2) : mb_local;
+    const CUtensorMap& msb = wh ? wh->scales : msb_local;
     static_assert(C::kSmemBytes <= kGemmDynSmemBytes, "ring does not fit");
-    cudaError_t e = cudaFuncSetAttribute(gemm_pair_kernel<BN>, cudaFuncAttributeMaxDynamicSharedMemorySize, kGemmDynSmemBytes);
+    const DeviceInfo di = device_info();
+    static bool attr_done[64] = {false};
+    cudaError_t e = allow_full_smem(gemm_pair_kernel<BN>, attr_done, di.device);
     if (e != cudaSuccess) return static_cast<int>(e);
-    int dev = 0, sms = 148;
-    cudaGetDevice(&dev);
-    cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev);
+    const int sms = di.sms;
     const int tiles = ((p.M + 255) / 256) * ((p.N + BN - 1) / BN);
     const int pairs = tiles < sms / 2 ? tiles : sms / 2;
     cudaLaunchConfig_t cfg = {};

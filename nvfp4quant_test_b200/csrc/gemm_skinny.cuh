@@ -333,15 +333,16 @@ static int choose_ranks(int n_tiles, int k_tiles, int sms, int forced, int bt) {
 }
 
 template <int BT>
-static int launch_skinny(const uint8_t* x, const uint8_t* w, const GemmParams& g, int forced_ranks, cudaStream_t stream) {
+static int launch_skinny(const uint8_t* x, const uint8_t* w, const GemmParams& g, int forced_ranks, cudaStream_t stream,
+                         const WeightHandle* wh) {
     using C = SkinnyCfg<BT>;
-    CUtensorMap mw, mx;
-    int st = make_operand_map(&mw, w, g.N, g.K / 2, 128);
-    if (st == NVFP4_OK) st = make_operand_map(&mx, x, g.M, g.K / 2, BT);
+    CUtensorMap mw_local, mx;
+    int st = make_operand_map(&mx, x, g.M, g.K / 2, BT);
+    if (st == NVFP4_OK && !wh) st = make_operand_map(&mw_local, w, g.N, g.K / 2, 128);
     if (st != NVFP4_OK) return st;
-    int dev = 0, sms = 148;
-    cudaGetDevice(&dev);
-    cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev);
+    const CUtensorMap& mw = wh ? wh->rows128 : mw_local;
+    const DeviceInfo di = device_info();
+    const int sms = di.sms;
     const int n_tiles = (g.N + 127) / 128;
     const int k_tiles = (g.K + kBK - 1) / kBK;
     int ranks = choose_ranks(n_tiles, k_tiles, sms, forced_ranks, BT);
@@ -370,7 +371,8 @@ static int launch_skinny(const uint8_t* x, const uint8_t* w, const GemmParams& g
     int smem = p.stages * C::kStageBytes + 1024 + 256;
     if (smem < kMinSmem) smem = kMinSmem;
     static_assert(C::kMaxStages * C::kStageBytes + 1024 + 256 <= kGemmDynSmemBytes, "ring does not fit");
-    cudaError_t e = cudaFuncSetAttribute(skinny_kernel<BT>, cudaFuncAttributeMaxDynamicSharedMemorySize, kGemmDynSmemBytes);
+    static bool attr_done[64] = {false};
+    cudaError_t e = allow_full_smem(skinny_kernel<BT>, attr_done, di.device);
     if (e != cudaSuccess) return static_cast<int>(e);
     cudaLaunchConfig_t cfg = {};
     cfg.gridDim = dim3(n_tiles * ranks, 1, 1);

@@ -379,21 +379,63 @@ static int make_operand_map(CUtensorMap* map, const void* ptr, int64_t rows, int
     return r == CUDA_SUCCESS ? NVFP4_OK : NVFP4_ERR_UNSUPPORTED;
 }
 
+// Per-device facts the launchers need on every call, looked up once per device.
+struct DeviceInfo {
+    int device;
+    int sms;
+};
+static DeviceInfo device_info() {
+    static int sm_count[64] = {0};
+    DeviceInfo d{0, 148};
+    if (cudaGetDevice(&d.device) != cudaSuccess || d.device < 0 || d.device >= 64) return d;
+    if (sm_count[d.device] == 0) {
+        int v = 0;
+        if (cudaDeviceGetAttribute(&v, cudaDevAttrMultiProcessorCount, d.device) == cudaSuccess && v > 0) sm_count[d.device] = v;
+    }
+    if (sm_count[d.device] > 0) d.sms = sm_count[d.device];
+    return d;
+}
+// cudaFuncSetAttribute(MaxDynamicSharedMemorySize) is per device and sticky: once per (kernel, device) is enough.
+template <class Kernel>
+static cudaError_t allow_full_smem(Kernel kernel, bool* done_per_device, int device) {
+    if (device >= 0 && device < 64 && done_per_device[device]) return cudaSuccess;
+    cudaError_t e = cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, kGemmDynSmemBytes);
+    if (e == cudaSuccess && device >= 0 && device < 64) done_per_device[device] = true;
+    return e;
+}
+
+// A weight matrix prepared once for many GEMM calls: its tensor maps for every tile height the kernels use.
+struct WeightHandle {
+    uint32_t magic;
+    int device;
+    const uint8_t* b;
+    const uint8_t* sfb;
+    int64_t N, K;
+    CUtensorMap rows64, rows96, rows128, rows256;   // operand maps by box height
+    CUtensorMap scales;                             // scale groups as rows of 8-byte words (pair kernels)
+    const CUtensorMap* by_rows(int rows) const {
+        return rows == 64 ? &rows64 : rows == 96 ? &rows96 : rows == 128 ? &rows128 : &rows256;
+    }
+};
+constexpr uint32_t kWeightMagic = 0x4e56463u;
+
 template <int BN>
-static int launch(const uint8_t* a, const uint8_t* b, const GemmParams& p, cudaStream_t stream) {
+static int launch(const uint8_t* a, const uint8_t* b, const GemmParams& p, cudaStream_t stream, const WeightHandle* wh) {
     using C = Cfg<BN>;
-    CUtensorMap ma, mb;
+    CUtensorMap ma, mb_local;
     int st = make_operand_map(&ma, a, p.M, p.K / 2, kBM);
     if (st != NVFP4_OK) return st;
-    st = make_operand_map(&mb, b, p.N, p.K / 2, BN);
-    if (st != NVFP4_OK) return st;
-    // function attributes are per device; setting it on every launch keeps multi-device processes correct
+    if (!wh) {
+        st = make_operand_map(&mb_local, b, p.N, p.K / 2, BN);
+        if (st != NVFP4_OK) return st;
+    }
+    const CUtensorMap& mb = wh ? *wh->by_rows(BN) : mb_local;
     static_assert(C::kSmemBytes <= kGemmDynSmemBytes, "ring does not fit");
-    cudaError_t e = cudaFuncSetAttribute(gemm_kernel<BN>, cudaFuncAttributeMaxDynamicSharedMemorySize, kGemmDynSmemBytes);
+    const DeviceInfo di = device_info();
+    static bool attr_done[64] = {false};
+    cudaError_t e = allow_full_smem(gemm_kernel<BN>, attr_done, di.device);
     if (e != cudaSuccess) return static_cast<int>(e);
-    int dev = 0, sms = 148;
-    cudaGetDevice(&dev);
-    cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev);
+    const int sms = di.sms;
     const int tiles = ((p.M + kBM - 1) / kBM) * ((p.N + BN - 1) / BN) * p.k_splits;
     const int grid = tiles < sms ? tiles : sms;
     gemm_kernel<BN><<<grid, kThreads, kGemmDynSmemBytes, stream>>>(ma, mb, p);

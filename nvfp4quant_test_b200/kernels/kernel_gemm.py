@@ -53,14 +53,93 @@ def nvfp4_scaled_mm(a: torch.Tensor, b: torch.Tensor, block_scale_a: torch.Tenso
     if m == 0 or n == 0:
         return out
     L = _lib.lib()
-    ws_bytes = L.nvfp4_gemm_workspace_bytes(m, n, k)
-    ws = torch.empty(ws_bytes, dtype=torch.uint8, device=a.device) if ws_bytes else None   # caching allocator
+    stream = _lib.current_stream_ptr(a.device)
+    args = (a.data_ptr(), b.data_ptr(), sfa.data_ptr(), sfb.data_ptr(), alpha.data_ptr(), out.data_ptr(), m, n, k)
     with _lib.device_guard(a.device):
-        st = L.nvfp4_gemm_launch(a.data_ptr(), b.data_ptr(), sfa.data_ptr(), sfb.data_ptr(),
-                                 alpha.data_ptr(), out.data_ptr(), m, n, k,
-                                 ws.data_ptr() if ws is not None else None, ws_bytes,
-                                 _lib.current_stream_ptr(a.device))
+        st = L.nvfp4_gemm_launch(*args, None, 0, stream)
+        if st == _ERR_WORKSPACE:
+            # only when K ranges were switched on through the tuning hook: ask for the size, then launch again
+            ws_bytes = L.nvfp4_gemm_workspace_bytes(m, n, k)
+            ws = torch.empty(ws_bytes, dtype=torch.uint8, device=a.device)
+            st = L.nvfp4_gemm_launch(*args, ws.data_ptr(), ws_bytes, stream)
     _lib.check(st, "nvfp4_gemm_launch")
+    return out
+
+
+_ERR_WORKSPACE = -6
+
+
+class PreparedWeight:
+    """A quantized weight [N, K] that will be multiplied many times (a model's linear layer).  Its tensor maps are
+    encoded once (nvfp4_gemm_prepare); `nvfp4_scaled_mm_prepared` then costs less host time per call than
+    `nvfp4_scaled_mm` and gives the same bits.  Keeps references to the two tensors, which must not be resized or
+    moved while this object lives (their contents may be overwritten in place)."""
+
+    def __init__(self, b: torch.Tensor, block_scale_b: torch.Tensor):
+        import ctypes
+
+        if b.ndim != 2 or b.dtype != torch.uint8 or not b.is_cuda or not b.is_contiguous():
+            raise ValueError("b must be a contiguous CUDA uint8 tensor [N, K/2]")
+        if block_scale_b.device != b.device or not block_scale_b.is_contiguous():
+            raise ValueError("block_scale_b must be a contiguous tensor on b's device")
+        self.n, self.k = b.shape[0], b.shape[1] * 2
+        if self.k % 64 != 0:
+            raise ValueError(f"K must be a multiple of 64, got {self.k}")
+        have = block_scale_b.numel() * block_scale_b.element_size()
+        if have < _scale_bytes(self.n, self.k):
+            raise ValueError(f"block_scale_b holds {have} bytes, the tiled layout needs {_scale_bytes(self.n, self.k)}")
+        self.b, self.block_scale_b, self.device = b, block_scale_b, b.device
+        self._handle = ctypes.c_void_p()
+        with _lib.device_guard(b.device):
+            st = _lib.lib().nvfp4_gemm_prepare(b.data_ptr(), block_scale_b.data_ptr(), self.n, self.k, ctypes.byref(self._handle))
+        _lib.check(st, "nvfp4_gemm_prepare")
+
+    def close(self) -> None:
+        if getattr(self, "_handle", None):
+            _lib.lib().nvfp4_gemm_release(self._handle)
+            self._handle = None
+
+    def __del__(self):
+        try:
+            self.close()
+        except Exception:  # noqa: BLE001 - interpreter shutdown
+            pass
+
+
+def nvfp4_scaled_mm_prepared(a: torch.Tensor, block_scale_a: torch.Tensor, alpha: torch.Tensor, weight: PreparedWeight,
+                             out: torch.Tensor | None = None) -> torch.Tensor:
+    """out[M, N] (bf16) = alpha * dq(a) @ dq(weight).T; same bits as nvfp4_scaled_mm(a, weight.b, ...)."""
+    if a.ndim != 2 or a.dtype != torch.uint8 or a.device != weight.device:
+        raise ValueError("a must be a uint8 [M, K/2] tensor on the weight's device")
+    if a.shape[1] * 2 != weight.k:
+        raise ValueError(f"a and the weight disagree on K: {a.shape[1] * 2} vs {weight.k}")
+    if alpha.dtype != torch.float32 or alpha.device != a.device:
+        raise ValueError("alpha must be a float32 tensor on a's device")
+    if not a.is_contiguous():
+        a = a.contiguous()
+    sfa = block_scale_a if block_scale_a.is_contiguous() else block_scale_a.contiguous()
+    m = a.shape[0]
+    if sfa.numel() * sfa.element_size() < _scale_bytes(m, weight.k):
+        raise ValueError("block_scale_a is smaller than the tiled layout of a needs")
+    if out is None:
+        out = torch.empty((m, weight.n), dtype=torch.bfloat16, device=a.device)
+    elif out.shape != (m, weight.n) or out.dtype != torch.bfloat16 or not out.is_contiguous():
+        raise ValueError("out must be a contiguous bfloat16 [M, N] tensor")
+    if m == 0:
+        return out
+    if not weight._handle:
+        raise ValueError("the prepared weight has been closed")
+    L = _lib.lib()
+    stream = _lib.current_stream_ptr(a.device)
+    with _lib.device_guard(a.device):
+        st = L.nvfp4_gemm_launch_prepared(weight._handle, a.data_ptr(), sfa.data_ptr(), alpha.data_ptr(), out.data_ptr(),
+                                          m, None, 0, stream)
+        if st == _ERR_WORKSPACE:
+            ws_bytes = L.nvfp4_gemm_workspace_bytes(m, weight.n, weight.k)
+            ws = torch.empty(ws_bytes, dtype=torch.uint8, device=a.device)
+            st = L.nvfp4_gemm_launch_prepared(weight._handle, a.data_ptr(), sfa.data_ptr(), alpha.data_ptr(),
+                                              out.data_ptr(), m, ws.data_ptr(), ws_bytes, stream)
+    _lib.check(st, "nvfp4_gemm_launch_prepared")
     return out
 
 

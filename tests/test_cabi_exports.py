@@ -156,3 +156,17 @@ def test_gemm_kernel_choice_by_shape(L):
     assert L.nvfp4_gemm_plan(1, 4096, 100, 148, None, None) < 0
     p_, r_ = ctypes.c_int(), ctypes.c_int()
     assert L.nvfp4_gemm_plan(1, 4096, 100, 148, ctypes.byref(p_), ctypes.byref(r_)) == -2
+
+
+def test_gemm_prepare_rejects_bad_arguments_and_release_is_safe(L):
+    h = ctypes.c_void_p()
+    P = 0x1000   # fake, aligned, never dereferenced: tensor maps only record the address
+    assert L.nvfp4_gemm_prepare(P, P, 256, 100, ctypes.byref(h)) == -2 and not h.value       # K % 64
+    assert L.nvfp4_gemm_prepare(None, P, 256, 128, ctypes.byref(h)) == -1
+    assert L.nvfp4_gemm_prepare(P + 8, P, 256, 128, ctypes.byref(h)) == -4
+    assert L.nvfp4_gemm_prepare(P, P, 256, 128, None) == -1
+    assert L.nvfp4_gemm_release(None) == 0
+    assert L.nvfp4_gemm_launch_prepared(None, P, P, P, P, 16, None, 0, None) == -1
+    bogus = (ctypes.c_uint32 * 64)()
+    assert L.nvfp4_gemm_launch_prepared(ctypes.addressof(bogus), P, P, P, P, 16, None, 0, None) == -3   # not a handle
+    assert L.nvfp4_gemm_set_wait_limit_ns(1) == -5 and L.nvfp4_quant_fused_set_wait_limit_ns(1) == -5

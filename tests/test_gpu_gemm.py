@@ -407,3 +407,36 @@ def test_llama_stack_run_end_to_end(cuda_lib):
     from nvfp4quant_test_b200.kernels.kernel_gemm import gemm_last_status
 
     assert gemm_last_status() == 0
+
+
+def test_prepared_weight_gives_the_same_bits_on_every_kernel_path(cuda_lib):
+    """nvfp4_gemm_prepare + nvfp4_gemm_launch_prepared == nvfp4_gemm_launch, for token counts that take the skinny,
+    the tile and the CTA-pair kernels, with one handle reused across all of them and across streams."""
+    import nvfp4quant_test_b200.kernels as K
+    from nvfp4quant_test_b200.kernels.kernel_gemm import gemm_last_status
+
+    g = torch.Generator(device="cuda")
+    g.manual_seed(11)
+    n, k = 4096 + 192, 2048
+    w = torch.randint(0, 256, (n, k // 2), dtype=torch.uint8, device="cuda", generator=g)
+    sw = torch.randint(0x28, 0x48, ((n + 127) // 128 * 128, k // 16), dtype=torch.uint8, device="cuda", generator=g)
+    alpha = torch.full((1,), 0.37, dtype=torch.float32, device="cuda")
+    pw = K.PreparedWeight(w, sw)
+    side = torch.cuda.Stream()
+    for m in (1, 16, 48, 128, 200, 256, 512, 1024, 2304):
+        a = torch.randint(0, 256, (m, k // 2), dtype=torch.uint8, device="cuda", generator=g)
+        sa = torch.randint(0x28, 0x48, ((m + 127) // 128 * 128, k // 16), dtype=torch.uint8, device="cuda", generator=g)
+        want = K.nvfp4_scaled_mm(a, w, sa, sw, alpha, torch.bfloat16)
+        got = K.nvfp4_scaled_mm_prepared(a, sa, alpha, pw)
+        side.wait_stream(torch.cuda.current_stream())
+        with torch.cuda.stream(side):
+            got_side = K.nvfp4_scaled_mm_prepared(a, sa, alpha, pw)
+        torch.cuda.current_stream().wait_stream(side)
+        assert torch.equal(got, want) and torch.equal(got_side, want), m
+    assert gemm_last_status() == 0
+    with pytest.raises(ValueError):
+        K.nvfp4_scaled_mm_prepared(a[:, :512], sa, alpha, pw)             # K mismatch
+    pw.close()
+    pw.close()                                                             # idempotent
+    with pytest.raises(ValueError):
+        K.nvfp4_scaled_mm_prepared(a, sa, alpha, pw)
