@@ -193,6 +193,10 @@ int nvfp4_gemm_plan(int64_t M, int64_t N, int64_t K, int sms, int* path, int* k_
  * weight tile, 1..8) of the skinny kernel instead.  nvfp4_gemm_workspace_bytes reflects the current setting
  * (the skinny kernel itself never needs a workspace). */
 int nvfp4_gemm_tune(int k_splits, int k_rotate);
+/* Testing hook (process-wide): 1 (default) = the decode-sized kernel is launched as a programmatic dependent launch
+ * (it may start while the kernel before it on the stream is finishing: its weight stream does not depend on that
+ * kernel; everything that does waits), 0 = plain stream order. */
+int nvfp4_gemm_tune_pdl(int enabled);
 /* Testing hook (process-wide): m-tiles per band of the persistent kernels' tile numbering (0 = default). */
 int nvfp4_gemm_tune_raster(int group);
 

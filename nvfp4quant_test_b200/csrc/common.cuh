@@ -94,6 +94,14 @@ __device__ __forceinline__ uint64_t fma_f32x2(uint64_t a, uint64_t b, uint64_t c
     return r;
 }
 
+// Programmatic dependent launch.  A kernel launched with the programmatic-stream-serialization attribute may start
+// while the kernel before it on the stream is still running; griddep_wait() is where it stops until that kernel has
+// finished and its writes are visible (it returns at once when there is nothing to wait for).  griddep_launch() is
+// the other half: the running kernel says that the next one may start being scheduled (a hint; harmless when the
+// next launch did not ask for it).
+__device__ __forceinline__ void griddep_wait() { asm volatile("griddepcontrol.wait;" ::: "memory"); }
+__device__ __forceinline__ void griddep_launch() { asm volatile("griddepcontrol.launch_dependents;" ::: "memory"); }
+
 // Byte offset of block (row, col) in the 128x4-tiled scale layout.
 __host__ __device__ inline int64_t swizzled_scale_offset(int64_t row, int64_t col, int64_t k_pad) {
     return (row >> 7) * (k_pad * 128) + (col >> 2) * 512 + (row & 31) * 16 + ((row & 127) >> 5) * 4 + (col & 3);

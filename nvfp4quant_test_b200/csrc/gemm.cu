@@ -55,6 +55,12 @@ extern "C" int nvfp4_gemm_tune_raster(int group) {
     return NVFP4_OK;
 }
 
+// Testing hook: 0 = launch the decode-sized kernel without the programmatic-dependent-launch attribute, 1 = with (default).
+extern "C" int nvfp4_gemm_tune_pdl(int enabled) {
+    nvfp4::gemm::skinny::g_skinny_pdl = enabled ? 1 : 0;
+    return NVFP4_OK;
+}
+
 extern "C" int nvfp4_gemm_tune(int k_splits, int k_rotate) {
     if (k_splits < 0 || k_splits > 16 || k_rotate < -1 || k_rotate > 1) return NVFP4_ERR_BAD_ENUM;
     g_gemm_force_splits = k_splits;

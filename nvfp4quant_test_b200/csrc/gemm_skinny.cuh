@@ -26,6 +26,7 @@ using pair::cluster_sync_all;
 using pair::map_to_cta;
 
 constexpr int kMaxStages = 8;
+static int g_skinny_pdl = 1;   // launch with the programmatic-stream-serialization attribute (testing hook: nvfp4_gemm_tune_pdl)
 // TMEM: accumulator in columns 0..BT-1, then two scale sets of 32 columns
 
 template <int BT>
@@ -155,7 +156,38 @@ skinny_kernel(const __grid_constant__ CUtensorMap tmap_w, const __grid_constant_
             asm volatile("prefetch.tensormap [%0];" ::"l"(&tmap_w) : "memory");
             asm volatile("prefetch.tensormap [%0];" ::"l"(&tmap_x) : "memory");
         }
-        produce(min(kcount, nstages));
+        // First ring-full.  The weights do not depend on whatever ran before this kernel on the stream, the token tile
+        // and its scales (the quantizer's output) do: with a programmatic dependent launch the weight copies go out
+        // at once, the rest after griddep_wait().
+        const int first = min(kcount, nstages);
+        const bool issuer = elect_one();
+        if (issuer) {
+            for (int i = 0; i < first; ++i) {
+                const int kt = kt_begin + i;
+                const uint32_t sf_bytes = 512u * min(4, (p.K - kt * kBK + 63) / 64);
+                const uint32_t sbase = base + i * C::kStageBytes;
+                mbar_expect_tx(full_bar(i), C::kWBytes + C::kXBytes + 2 * sf_bytes);
+                tma_load_2d(sbase, &tmap_w, kt * kBKBytes, nt * 128, full_bar(i));
+                bulk_load_1d(sbase + C::kWBytes + C::kXBytes,
+                             p.sfw + static_cast<int64_t>(nt) * p.sf_group_stride + static_cast<int64_t>(kt) * 2048, sf_bytes,
+                             full_bar(i));
+            }
+        }
+        griddep_wait();
+        if (issuer) {
+            for (int i = 0; i < first; ++i) {
+                const int kt = kt_begin + i;
+                const uint32_t sf_bytes = 512u * min(4, (p.K - kt * kBK + 63) / 64);
+                const uint32_t sbase = base + i * C::kStageBytes;
+                tma_load_2d(sbase + C::kWBytes, &tmap_x, kt * kBKBytes, 0, full_bar(i));
+                bulk_load_1d(sbase + C::kWBytes + C::kXBytes + C::kSfBytes, p.sfx + static_cast<int64_t>(kt) * 2048, sf_bytes,
+                             full_bar(i));
+            }
+        }
+        __syncwarp();
+        p_next = first;
+        p_stage = first == nstages ? 0 : first;
+        p_phase = first == nstages ? 1u : 0u;
     }
     if (warp == 1) {
         asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(
@@ -168,6 +200,8 @@ skinny_kernel(const __grid_constant__ CUtensorMap tmap_w, const __grid_constant_
     __syncthreads();
     tc_fence_after();
     const uint32_t tmem_base = *tmem_slot;
+    griddep_launch();   // a GEMM queued behind this one may begin: its weight stream does not depend on our output
+    if (warp >= 2) griddep_wait();   // the epilogue reads alpha (and writes out): only once the previous kernel is done
 
     if (warp == 0) {
         // ------------------------------------------------------------------ producer, stages after the first ring-full
@@ -379,13 +413,17 @@ static int launch_skinny(const uint8_t* x, const uint8_t* w, const GemmParams& g
     cfg.blockDim = dim3(kThreads, 1, 1);
     cfg.dynamicSmemBytes = smem;
     cfg.stream = stream;
-    cudaLaunchAttribute attr[1];
+    cudaLaunchAttribute attr[2];
     attr[0].id = cudaLaunchAttributeClusterDimension;
     attr[0].val.clusterDim.x = ranks;
     attr[0].val.clusterDim.y = 1;
     attr[0].val.clusterDim.z = 1;
+    // programmatic dependent launch: this kernel may be scheduled while its predecessor on the stream is finishing
+    // (it stops at griddep_wait() before touching anything the predecessor may have written)
+    attr[1].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+    attr[1].val.programmaticStreamSerializationAllowed = 1;
     cfg.attrs = attr;
-    cfg.numAttrs = 1;
+    cfg.numAttrs = g_skinny_pdl ? 2 : 1;
     e = cudaLaunchKernelEx(&cfg, skinny_kernel<BT>, mw, mx, p);
     return static_cast<int>(e);
 }

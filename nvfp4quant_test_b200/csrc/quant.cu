@@ -380,6 +380,7 @@ quant_kernel(const QuantParams p) {
         if (VARIANT == NVFP4_VARIANT_WEIGHTED) load16<NVFP4_DT_F32>(p.importance, col * kBlock, w);
     }
 
+    griddep_launch();   // a kernel queued behind this one with a programmatic dependency may start its own prologue
     // The global scale and the block's elements were requested above; the candidate table is built while they are
     // on their way (at small batch sizes nothing else hides a trip to memory).  The amax variant needs no table: its
     // one multiplier per block is two reciprocals away from the scale byte, and without the table there is no
