@@ -34,7 +34,7 @@ def _stale() -> bool:
     if not LIB.exists():
         return True
     t = LIB.stat().st_mtime
-    deps = [CSRC / s for s in SOURCES] + list(CSRC.glob("*.cuh")) + list(INCLUDE.glob("*.h"))
+    deps = [CSRC / s for s in SOURCES] + list(CSRC.glob("*.cuh")) + list(CSRC.glob("*.inc")) + list(INCLUDE.glob("*.h"))
     return any(d.stat().st_mtime > t for d in deps if d.exists())
 
 

@@ -18,6 +18,7 @@
 // This file holds the C entry points and the kernel choice; the kernels live in gemm_tile.cuh (one CTA per tile),
 // gemm_pair.cuh (CTA pairs, cta_group::2) and gemm_skinny.cuh (decode-sized batches, K ranges across a cluster),
 // all on the PTX wrappers of tc_ptx.cuh.  One translation unit, so that there is one status word.
+#include <cstdint>
 #include <new>
 
 #include "gemm_tile.cuh"
@@ -55,9 +56,9 @@ extern "C" int nvfp4_gemm_tune_raster(int group) {
     return NVFP4_OK;
 }
 
-// Testing hook: 0 = launch the decode-sized kernel without the programmatic-dependent-launch attribute, 1 = with (default).
+// Testing hook: 0 = launch the GEMM kernels without the programmatic-dependent-launch attribute, 1 = with (default).
 extern "C" int nvfp4_gemm_tune_pdl(int enabled) {
-    nvfp4::gemm::skinny::g_skinny_pdl = enabled ? 1 : 0;
+    nvfp4::gemm::g_gemm_pdl = enabled ? 1 : 0;
     return NVFP4_OK;
 }
 
@@ -78,6 +79,25 @@ extern "C" int nvfp4_gemm_force_path(int path) {
     return NVFP4_OK;
 }
 
+// Measured kernel choice (generated file, see its first lines): {M, N, K, path} for a grid of shapes on a 148-SM B200.
+struct PlanRow {
+    int M, N, K, path;
+};
+static const PlanRow kPlanTable[] = {
+#include "gemm_plan_table.inc"
+};
+// Fastest measured kernel for (N, K) at the smallest tabulated M >= the launch's M; 0 when the shape is not tabulated.
+static int table_path(int64_t M, int64_t N, int64_t K) {
+    int64_t best_m = INT64_MAX;
+    int path = 0;
+    for (const PlanRow& r : kPlanTable)
+        if (r.N == N && r.K == K && r.M >= M && r.M < best_m) {
+            best_m = r.M;
+            path = r.path;
+        }
+    return path;
+}
+
 // Kernel choice for one shape: host arithmetic only.  *path: 1 = 128x128 tiles, 2 = 128x256, 3 = pair 256x256,
 // 4 = pair 256x192, 5 = skinny, 6 = 128x64, 7 = pair 256x128; *k_ranges: cluster size of the skinny kernel (1 for the others).
 static void plan_gemm(int64_t M, int64_t N, int64_t K, int sms, int k_splits, int* path_out, int* ranges_out) {
@@ -93,7 +113,11 @@ static void plan_gemm(int64_t M, int64_t N, int64_t K, int sms, int k_splits, in
         skinny = M <= kSkinnyMaxM;
     } else if (g_gemm_force_path == 0 && g_gemm_force_splits == 0 && M <= kSkinnyMaxM) {
         const int ranks = nvfp4::gemm::skinny::choose_ranks(n_tiles, k_tiles_total, sms, 0, M <= 64 ? 64 : 128);
-        skinny = M <= kSkinnyAutoM || (ranks >= 4 && k_tiles_total / ranks >= 12);
+        // measured with the weights streaming from HBM (microseconds, decode-sized kernel against the best tile / pair
+        // kernel): 48 x 4096 x 4096 6.5 / 7.3, 48 x 6144 x 4096 7.6 / 8.8, 48 x 8192 x 8192 11.7 / 12.1, but 48 x 28672 x
+        // 8192 33.9 / 27.4; 64 x 1024 x 4096 5.0 / 6.3, 64 x 6144 x 4096 8.1 / 7.7
+        skinny = M <= kSkinnyAutoM || (M <= 48 && n_tiles <= 64) || (M <= 64 && n_tiles <= 8) ||
+                 (ranks >= 4 && k_tiles_total / ranks >= 12);
     }
     if (skinny) {
         const int forced = g_gemm_force_path == 5 ? g_gemm_force_splits : 0;
@@ -110,6 +134,8 @@ static void plan_gemm(int64_t M, int64_t N, int64_t K, int sms, int k_splits, in
     // pair 256x192 -> 0.68 (0.75 of the MMA work per SM, and its epilogue overlaps the next tile), pair 256x256 -> 0.96,
     // pair 256x128 -> 0.6.
     int path = g_gemm_force_path == 5 ? 0 : g_gemm_force_path;   // 0 = choose by shape
+    // shapes of the measured table (on the GPU it was measured on) take the kernel that was fastest there
+    if (path == 0 && k_splits == 1 && sms == 148) path = table_path(M, N, K);
     if (path == 0) {
         const int64_t mt = (M + 127) / 128;
         const int64_t wave1 = sms, wave2 = sms / 2 > 0 ? sms / 2 : 1;   // tiles per wave: single CTAs, CTA pairs

@@ -134,6 +134,8 @@ gemm_pair_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_consta
     tc_fence_after();
     const uint32_t tmem_base = *tmem_slot;
     if (threadIdx.x == 0) trace_mark(1, 2);
+    griddep_launch();                 // a GEMM queued behind this one may start on its weights
+    if (warp >= 2) griddep_wait();    // the epilogue reads alpha and writes the output: only after the previous kernel
 
     const int m_tiles = (p.M + 255) / 256;
     const int n_tiles = (p.N + BN - 1) / BN;
@@ -153,22 +155,40 @@ gemm_pair_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_consta
             int stage = 0;
             uint32_t phase = 0;
             bool ok = true;
+            // weight half (B rows and their scales: independent of whatever ran before this kernel) and token half (A rows
+            // and their scales) of a stage; the weight halves of the first ring-full are issued before griddep_wait()
+            auto issue = [&](int st, int mt, int nt, int kt, bool weights, bool tokens) {
+                const uint32_t lead_full = map_to_cta(full_bar(st), 0);
+                const uint32_t sbase = base + st * C::kStageBytes;
+                if (weights) {
+                    if (rank == 0) mbar_expect_tx(full_bar(st), 2u * C::kStageBytes);
+                    tma_load_2d_pair(sbase + C::kABytes, &tmap_b, kt * kBKBytes, nt * BN + static_cast<int>(rank) * (BN / 2), lead_full);
+                    // scale tiles: x counts 8-byte elements (2048 B per K tile), y = 128-row group
+                    tma_load_2d_pair(sbase + C::kABytes + C::kBBytes + C::kSfaBytes, &tmap_sfb, kt * 256, (nt * BN) / 128, lead_full);
+                    tma_load_2d_pair(sbase + C::kABytes + C::kBBytes + C::kSfaBytes + 2048, &tmap_sfb, kt * 256, (nt * BN) / 128 + 1, lead_full);
+                }
+                if (tokens) {
+                    tma_load_2d_pair(sbase, &tmap_a, kt * kBKBytes, mt * 256 + static_cast<int>(rank) * 128, lead_full);
+                    tma_load_2d_pair(sbase + C::kABytes + C::kBBytes, &tmap_sfa, kt * 256, mt * 2 + static_cast<int>(rank), lead_full);
+                }
+            };
+            int early = 0;
+            if (pair_id < total_tiles) {
+                int mt, nt;
+                tile_to_mn(pair_id, m_tiles, n_tiles, p.raster_group, mt, nt);
+                early = min(k_tiles, C::kStages);
+                if (issuer)
+                    for (int i = 0; i < early; ++i) issue(i, mt, nt, i, true, false);
+                __syncwarp();
+            }
+            griddep_wait();
             for (int tile = pair_id; ok && tile < total_tiles; tile += num_pairs) {
                 int mt, nt;
                 tile_to_mn(tile, m_tiles, n_tiles, p.raster_group, mt, nt);
                 for (int kt = 0; kt < k_tiles; ++kt) {
                     if (!(ok = mbar_wait_warp(empty_bar(stage), phase ^ 1u, abort_flag, (1u << 24) | kt))) break;
-                    if (issuer) {
-                    if (rank == 0) mbar_expect_tx(full_bar(stage), 2u * C::kStageBytes);
-                    const uint32_t lead_full = map_to_cta(full_bar(stage), 0);
-                    const uint32_t sbase = base + stage * C::kStageBytes;
-                    tma_load_2d_pair(sbase, &tmap_a, kt * kBKBytes, mt * 256 + static_cast<int>(rank) * 128, lead_full);
-                    tma_load_2d_pair(sbase + C::kABytes, &tmap_b, kt * kBKBytes, nt * BN + static_cast<int>(rank) * (BN / 2), lead_full);
-                    // scale tiles: x counts 8-byte elements (2048 B per K tile), y = 128-row group
-                    tma_load_2d_pair(sbase + C::kABytes + C::kBBytes, &tmap_sfa, kt * 256, mt * 2 + static_cast<int>(rank), lead_full);
-                    tma_load_2d_pair(sbase + C::kABytes + C::kBBytes + C::kSfaBytes, &tmap_sfb, kt * 256, (nt * BN) / 128, lead_full);
-                    tma_load_2d_pair(sbase + C::kABytes + C::kBBytes + C::kSfaBytes + 2048, &tmap_sfb, kt * 256, (nt * BN) / 128 + 1, lead_full);
-                    }
+                    if (issuer) issue(stage, mt, nt, kt, early == 0, true);
+                    if (early > 0) --early;
                     __syncwarp();
                     if (++stage == C::kStages) {
                         stage = 0;
@@ -362,13 +382,15 @@ static int launch_pair(const uint8_t* a, const uint8_t* b, const GemmParams& p, 
     cfg.blockDim = dim3(kThreads, 1, 1);
     cfg.dynamicSmemBytes = kGemmDynSmemBytes;
     cfg.stream = stream;
-    cudaLaunchAttribute attr[1];
+    cudaLaunchAttribute attr[2];
     attr[0].id = cudaLaunchAttributeClusterDimension;
     attr[0].val.clusterDim.x = 2;
     attr[0].val.clusterDim.y = 1;
     attr[0].val.clusterDim.z = 1;
+    attr[1].id = cudaLaunchAttributeProgrammaticStreamSerialization;   // may start while its predecessor finishes
+    attr[1].val.programmaticStreamSerializationAllowed = 1;
     cfg.attrs = attr;
-    cfg.numAttrs = 1;
+    cfg.numAttrs = g_gemm_pdl ? 2 : 1;
     e = cudaLaunchKernelEx(&cfg, gemm_pair_kernel<BN>, ma, mb, msa, msb, p);
     return static_cast<int>(e);
 }

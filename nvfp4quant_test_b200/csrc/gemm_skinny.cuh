@@ -26,7 +26,6 @@ using pair::cluster_sync_all;
 using pair::map_to_cta;
 
 constexpr int kMaxStages = 8;
-static int g_skinny_pdl = 1;   // launch with the programmatic-stream-serialization attribute (testing hook: nvfp4_gemm_tune_pdl)
 // TMEM: accumulator in columns 0..BT-1, then two scale sets of 32 columns
 
 template <int BT>
@@ -423,7 +422,7 @@ static int launch_skinny(const uint8_t* x, const uint8_t* w, const GemmParams& g
     attr[1].id = cudaLaunchAttributeProgrammaticStreamSerialization;
     attr[1].val.programmaticStreamSerializationAllowed = 1;
     cfg.attrs = attr;
-    cfg.numAttrs = g_skinny_pdl ? 2 : 1;
+    cfg.numAttrs = g_gemm_pdl ? 2 : 1;
     e = cudaLaunchKernelEx(&cfg, skinny_kernel<BT>, mw, mx, p);
     return static_cast<int>(e);
 }

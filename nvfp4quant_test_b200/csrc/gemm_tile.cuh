@@ -111,6 +111,8 @@ gemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant__ 
     tc_fence_after();
     const uint32_t tmem_base = *tmem_slot;   // meaningful in warps 1..5 only
     if (threadIdx.x == 32) trace_mark(0, 2);
+    griddep_launch();                 // a GEMM queued behind this one may start on its weights
+    if (warp >= 2) griddep_wait();    // alpha, and the output buffer, belong to whatever ran before: epilogue only after it
 
     const int m_tiles = (p.M + kBM - 1) / kBM;
     const int n_tiles = (p.N + BN - 1) / BN;
@@ -129,6 +131,49 @@ gemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant__ 
             int stage = 0;
             uint32_t phase = 0;
             bool ok = true;
+            // Stage copies come in two halves: the weight half (B tile and its scales) depends on nothing that ran
+            // before this kernel, the token half (A tile and its scales) may be the previous kernel's output.  The
+            // weight halves of the first ring-full go out before griddep_wait(), so that with a programmatic dependent
+            // launch the weight stream starts while the previous kernel is still finishing; `early` counts them.
+            auto issue = [&](int st, int mt, int nt, int kt, bool weights, bool tokens) {
+                const int kb_count = min(4, (p.K - kt * kBK + 63) / 64);  // 64-element K blocks in this stage
+                const uint32_t sf_bytes = 512u * kb_count;
+                int sfb_present = 0;
+                const int grp0 = BN == 64 ? (nt >> 1) : nt * C::kNG;   // first 128-row scale group of this B tile
+                for (int g = 0; g < C::kNG; ++g) sfb_present += (grp0 + g < p.sfb_groups) ? 1 : 0;
+                const uint32_t sbase = base + st * C::kStageBytes;
+                if (weights) {
+                    mbar_expect_tx(full_bar(st), C::kABytes + C::kBBytes + sf_bytes * (1 + sfb_present));
+                    tma_load_2d(sbase + C::kABytes, &tmap_b, kt * kBKBytes, nt * BN, full_bar(st));
+                    for (int g = 0; g < C::kNG; ++g) {
+                        const int grp = grp0 + g;
+                        if (grp < p.sfb_groups)
+                            bulk_load_1d(sbase + C::kABytes + C::kBBytes + C::kSfaBytes + g * 2048,
+                                         p.sfb + static_cast<int64_t>(grp) * p.sf_group_stride +
+                                             static_cast<int64_t>(kt) * 2048,
+                                         sf_bytes, full_bar(st));
+                    }
+                }
+                if (tokens) {
+                    tma_load_2d(sbase, &tmap_a, kt * kBKBytes, mt * kBM, full_bar(st));
+                    bulk_load_1d(sbase + C::kABytes + C::kBBytes,
+                                 p.sfa + static_cast<int64_t>(mt) * p.sf_group_stride + static_cast<int64_t>(kt) * 2048,
+                                 sf_bytes, full_bar(st));
+                }
+            };
+            int early = 0;
+            if (static_cast<int>(blockIdx.x) < total_tiles && !p.k_rotate) {
+                const int ks = blockIdx.x / mn_tiles, t2 = blockIdx.x - ks * mn_tiles;
+                int mt, nt;
+                tile_to_mn(t2, m_tiles, n_tiles, p.raster_group, mt, nt);
+                const int kt_begin = ks * p.k_tiles_per_split;
+                const int kcount = min(k_tiles, kt_begin + p.k_tiles_per_split) - kt_begin;
+                early = min(kcount, C::kStages);
+                if (issuer)
+                    for (int i = 0; i < early; ++i) issue(i, mt, nt, kt_begin + i, true, false);
+                __syncwarp();
+            }
+            griddep_wait();
             for (int tile = blockIdx.x; ok && tile < total_tiles; tile += gridDim.x) {
                 const int ks = tile / mn_tiles, t2 = tile - ks * mn_tiles;
                 int mt, nt;
@@ -139,29 +184,8 @@ gemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant__ 
                 for (int i = 0; i < kcount; ++i) {
                     const int kt = kt_begin + (i + rot) % kcount;
                     if (!(ok = mbar_wait_warp(empty_bar(stage), phase ^ 1u, abort_flag, (1u << 24) | kt))) break;
-                    const int kb_count = min(4, (p.K - kt * kBK + 63) / 64);  // 64-element K blocks in this stage
-                    const uint32_t sf_bytes = 512u * kb_count;
-                    int sfb_present = 0;
-                    const int grp0 = BN == 64 ? (nt >> 1) : nt * C::kNG;   // first 128-row scale group of this B tile
-                    for (int g = 0; g < C::kNG; ++g) sfb_present += (grp0 + g < p.sfb_groups) ? 1 : 0;
-                    const uint32_t tx = C::kABytes + C::kBBytes + sf_bytes * (1 + sfb_present);
-                    const uint32_t sbase = base + stage * C::kStageBytes;
-                    if (issuer) {
-                    mbar_expect_tx(full_bar(stage), tx);
-                    tma_load_2d(sbase, &tmap_a, kt * kBKBytes, mt * kBM, full_bar(stage));
-                    tma_load_2d(sbase + C::kABytes, &tmap_b, kt * kBKBytes, nt * BN, full_bar(stage));
-                    bulk_load_1d(sbase + C::kABytes + C::kBBytes,
-                                 p.sfa + static_cast<int64_t>(mt) * p.sf_group_stride + static_cast<int64_t>(kt) * 2048,
-                                 sf_bytes, full_bar(stage));
-                    for (int g = 0; g < C::kNG; ++g) {
-                        const int grp = grp0 + g;
-                        if (grp < p.sfb_groups)
-                            bulk_load_1d(sbase + C::kABytes + C::kBBytes + C::kSfaBytes + g * 2048,
-                                         p.sfb + static_cast<int64_t>(grp) * p.sf_group_stride +
-                                             static_cast<int64_t>(kt) * 2048,
-                                         sf_bytes, full_bar(stage));
-                    }
-                    }
+                    if (issuer) issue(stage, mt, nt, kt, early == 0, true);
+                    if (early > 0) --early;
                     __syncwarp();
                     if (++stage == C::kStages) {
                         stage = 0;
@@ -380,6 +404,8 @@ static int make_operand_map(CUtensorMap* map, const void* ptr, int64_t rows, int
 }
 
 // Per-device facts the launchers need on every call, looked up once per device.
+static int g_gemm_pdl = 1;   // programmatic dependent launch of the GEMM kernels (testing hook: nvfp4_gemm_tune_pdl)
+
 struct DeviceInfo {
     int device;
     int sms;
@@ -438,8 +464,17 @@ static int launch(const uint8_t* a, const uint8_t* b, const GemmParams& p, cudaS
     const int sms = di.sms;
     const int tiles = ((p.M + kBM - 1) / kBM) * ((p.N + BN - 1) / BN) * p.k_splits;
     const int grid = tiles < sms ? tiles : sms;
-    gemm_kernel<BN><<<grid, kThreads, kGemmDynSmemBytes, stream>>>(ma, mb, p);
-    e = cudaGetLastError();
+    cudaLaunchConfig_t cfg = {};
+    cfg.gridDim = dim3(grid, 1, 1);
+    cfg.blockDim = dim3(kThreads, 1, 1);
+    cfg.dynamicSmemBytes = kGemmDynSmemBytes;
+    cfg.stream = stream;
+    cudaLaunchAttribute attr[1];
+    attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;   // may start while its predecessor finishes
+    attr[0].val.programmaticStreamSerializationAllowed = 1;
+    cfg.attrs = attr;
+    cfg.numAttrs = g_gemm_pdl ? 1 : 0;
+    e = cudaLaunchKernelEx(&cfg, gemm_kernel<BN>, ma, mb, p);
     if (e != cudaSuccess || p.k_splits == 1) return static_cast<int>(e);
     const int64_t mn = static_cast<int64_t>(p.M) * p.N;
     int64_t rblocks = (mn + 255) / 256;

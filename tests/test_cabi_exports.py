@@ -134,15 +134,21 @@ def test_gemm_kernel_choice_by_shape(L):
     assert plan(16, 128, 64) == (5, 1)
     assert plan(64, 4096, 14336) == (5, 4)           # few tiles, long K: still the decode-sized kernel
     assert plan(128, 4096, 14336) == (5, 4)
-    assert plan(64, 4096, 4096) == (6, 1)            # 128x64 tiles
-    assert plan(128, 8192, 8192) == (7, 1)           # long K: CTA pairs with 256x128 tiles even for one token tile
-    assert plan(128, 6144, 4096) == (6, 1)
-    assert plan(128, 28672, 8192) == (2, 1)          # 128x256 tiles
-    assert plan(256, 8192, 8192) == (7, 1)           # CTA pairs, 256x128 tiles: a few hundred tokens
-    assert plan(256, 4096, 4096) == (6, 1)
-    assert plan(512, 8192, 8192) == (3, 1)           # CTA pairs, 256x256 tiles
-    assert plan(8192, 8192, 8192) == (4, 1)          # CTA pairs, 256x192 tiles
-    assert plan(8192, 28672, 8192) == (4, 1)
+    # shapes outside the measured table: the cost model (128x64 tiles for one or two token tiles and few weight tiles,
+    # CTA pairs for large shapes)
+    assert plan(64, 2048, 2048) == (6, 1)
+    assert plan(8192, 16384, 4096) == (4, 1)
+    assert plan(20000, 8192, 8192) == (4, 1)         # beyond the largest tabulated M
+    assert plan(256, 8192, 8192, sms=132) == (7, 1)  # another SM count: the table does not apply, the model does
+    # shapes of the measured table take the kernel that was fastest when it was generated
+    table = ROOT / "nvfp4quant_test_b200" / "csrc" / "gemm_plan_table.inc"
+    rows = [tuple(int(v) for v in m.groups()) for m in re.finditer(r"^\{(\d+), (\d+), (\d+), (\d+)\}", table.read_text(), re.M)]
+    assert len(rows) >= 40
+    for M, N, K, path in rows:
+        got = plan(M, N, K)
+        assert got == (path, 1) or (M <= 128 and got[0] == 5), (M, N, K, path, got)   # up to 128 tokens the decode kernel may take it
+        if M > 128:
+            assert plan(M - 60, N, K) == (path, 1)    # a launch uses the row with the smallest tabulated M >= its own
     # forcing a kernel / K ranges is honoured, larger M than the skinny kernel takes falls back
     try:
         assert L.nvfp4_gemm_force_path(5) == 0 and L.nvfp4_gemm_tune(8, -1) == 0
