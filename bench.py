@@ -45,9 +45,9 @@ METRIC = "ScaleSweep_MSE NVFP4 quantization throughput, bf16 [8192, 8192] per GP
 WORKLOAD = "configs[1] bsz=8192: ScaleSweep_MSE quant of bf16 [8192,8192] N(0,1), FP8_MAX=256, swizzled scales"
 NOMINAL_FP4_TFLOPS = 9000.0
 # dram__bytes_read.sum + dram__bytes_write.sum of one quant_kernel launch on this workload (ncu capture,
-# summarised under profiles/): 135.14 MB read + 21.24 MB written (the rest of the 37.7 MB of
+# summarised under profiles/): 135.14 MB read + 21.00 MB written (the rest of the 37.7 MB of
 # outputs is still in L2 when the kernel ends).
-NCU_TRAFFIC_BYTES_PER_LAUNCH = 156_381_696
+NCU_TRAFFIC_BYTES_PER_LAUNCH = 156_140_800
 
 
 def measured_peaks():

@@ -40,7 +40,9 @@ def laplace(shape, seed: int, device="cuda") -> torch.Tensor:
     g = torch.Generator(device=device)
     g.manual_seed(seed)
     u = torch.rand(shape, generator=g, device=device, dtype=torch.float32) - 0.5
-    return (-torch.sign(u) * torch.log1p(-2.0 * u.abs())).to(torch.bfloat16)
+    # rand() can return exactly 0, i.e. |u| = 0.5 and an infinite sample: keep |u| one fp32 step inside
+    mag = torch.clamp(u.abs(), max=0.5 - 2.0 ** -25)
+    return (-torch.sign(u) * torch.log1p(-2.0 * mag)).to(torch.bfloat16)
 
 
 def quantize_operand(name: str, x: torch.Tensor, other: torch.Tensor):
