@@ -154,7 +154,10 @@ def third_party(dev, xs, gs448_inv, torch, B):
         return a, sa, bs, sbs
 
     gem = {}
-    for (m, n, k, copies) in ((8192, 8192, 8192, 1), (16, 8192, 8192, 8), (256, 4096, 4096, 32)):
+    # the headline shape, a decode batch, and the few-hundred-token cells of the Llama-shaped layers
+    shapes = ((8192, 8192, 8192, 1), (16, 8192, 8192, 8), (256, 4096, 4096, 32), (128, 4096, 4096, 32), (128, 1024, 4096, 32),
+              (128, 6144, 4096, 20), (256, 14336, 4096, 8), (256, 8192, 8192, 8), (512, 14336, 4096, 8), (2048, 4096, 4096, 32))
+    for (m, n, k, copies) in shapes:
         a, sa, bs, sbs = operands(m, n, k, copies)
         f8 = torch.float8_e4m3fn
 
