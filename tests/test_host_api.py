@@ -3,7 +3,11 @@ contract and error behaviour (no kernel is launched here)."""
 import inspect
 
 import pytest
+import pathlib
+
 import torch
+
+ROOT = pathlib.Path(__file__).resolve().parents[1]
 
 
 def test_module_surface_matches_the_reference():
@@ -205,3 +209,23 @@ def test_stream_scratch_is_bounded():
     assert len(sc) == 4                               # older streams were dropped
     assert sc.get(dev, 100) is not first              # ... including the first one, which gets a fresh buffer
     assert sc.get(dev, 109) is sc.get(dev, 109)
+
+
+def test_bench_reference_arm_prints_one_schema_complete_line():
+    """`bench.py --impl reference` (the CPU port on all host threads over the full 8192 rows) prints exactly one JSON
+    line with the keys of the benchmark contract."""
+    import json
+    import subprocess
+    import sys
+
+    res = subprocess.run([sys.executable, str(ROOT / "bench.py"), "--impl", "reference", "--steps", "1", "--warmup", "1"],
+                         capture_output=True, text=True, timeout=600)
+    assert res.returncode == 0, res.stderr[-2000:]
+    lines = [l for l in res.stdout.splitlines() if l.strip()]
+    assert len(lines) == 1
+    d = json.loads(lines[0])
+    assert d["impl"] == "reference" and d["unit"] == "GB/s" and d["higher_is_better"] is True and d["vs_baseline"] is None
+    assert d["config"]["rows_per_gpu"] == 8192 and "configs[1]" in d["config"]["workload"]
+    assert d["cpu_baseline"]["kind"] == "port" and d["cpu_baseline"]["cores"] >= 1 and d["cpu_baseline"]["value"] == d["value"]
+    assert d["e2e"] == {"value": d["value"], "unit": "GB/s", "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0}
+    assert d["gpu_launches"] == 0 and d["steps"] == 1 and 0.01 < d["value"] < 50.0
