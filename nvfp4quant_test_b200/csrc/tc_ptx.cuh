@@ -119,7 +119,7 @@ __device__ __forceinline__ bool elect_one() {
     asm volatile("{ .reg .b32 rx; .reg .pred px; elect.sync rx|px, 0xffffffff; selp.u32 %0, 1, 0, px; }" : "=r"(pred));
     return pred != 0;
 }
-// Bounded wait executed by the whole warp; the verdict is lane 0's, so it is uniform.
+// Bounded wait executed by the whole warp; the answer is lane 0's, so it is uniform.
 __device__ __forceinline__ bool mbar_wait_warp(uint32_t bar, uint32_t parity, volatile uint32_t* abort_flag, uint32_t code) {
     const bool ok = mbar_wait(bar, parity, abort_flag, code);
     return __shfl_sync(0xffffffffu, ok ? 1 : 0, 0) != 0;
