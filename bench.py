@@ -167,14 +167,22 @@ def third_party(dev, xs, gs448_inv, torch, B):
 
         o = torch.empty((m, n), dtype=torch.bfloat16, device=dev)
 
-        def mine():
+        def mine_raw():
             for i in range(copies):
                 K.nvfp4_scaled_mm(a, bs[i], sa, sbs[i], one, torch.bfloat16, out=o)
 
+        pws = [K.PreparedWeight(bs[i], sbs[i]) for i in range(copies)]
+
+        def mine():
+            for i in range(copies):
+                K.nvfp4_scaled_mm_prepared(a, sa, one, pws[i], out=o)
+
         gem[f"{m}x{n}x{k}"] = {"cutlass_scaled_fp4_mm": B.time_graph(theirs, copies), "ours": B.time_graph(mine, copies),
-                               "weight_copies": copies}
-        del a, sa, bs, sbs
-    out["gemm_us"] = dict(gem, method="CUDA graph replay over rotating weight copies")
+                               "ours_raw_pointers": B.time_graph(mine_raw, copies), "weight_copies": copies}
+        del a, sa, bs, sbs, pws
+    out["gemm_us"] = dict(gem, method="CUDA graph replay over rotating weight copies; `ours` = prepared weights (the "
+                                      "GEMM streams them while its predecessor finishes), `ours_raw_pointers` = the "
+                                      "drop-in call, which waits for its predecessor before reading either operand")
     return out
 
 
@@ -406,9 +414,11 @@ def main():
             one = torch.ones(1, dtype=torch.float32, device=dev)
             dout = torch.empty((tokens, ROWS), dtype=torch.bfloat16, device=dev)
 
+            pws = [K.PreparedWeight(wq[i], ws[i]) for i in range(n_w)]
+
             def record():
                 for i in range(n_w):
-                    K.nvfp4_scaled_mm(xq, wq[i], xs_, ws[i], one, torch.bfloat16, out=dout)
+                    K.nvfp4_scaled_mm_prepared(xq, xs_, one, pws[i], out=dout)
 
             barrier()
             dus = max_over_ranks(B.time_graph(record, n_w))
@@ -416,9 +426,9 @@ def main():
             gemm["decode"] = {"shape_per_gpu": [tokens, ROWS, DIM], "us": dus,
                               "weight_stream_gbs": wbytes / (dus * 1e-6) / 1e9,
                               "frac_of_measured_hbm": wbytes / (dus * 1e-6) / 1e9 / hbm_peak,
-                              "note": "16 weight matrices rotate (600 MB > L2); CUDA graph replay",
+                              "note": "16 prepared weight matrices rotate (600 MB > L2); CUDA graph replay",
                               "status": K.kernel_gemm.gemm_last_status(dev)}
-            del wq, ws
+            del wq, ws, pws
         except Exception as exc:  # the headline number must not depend on this extra
             gemm["decode"] = {"error": repr(exc)}
         if extras:

@@ -170,7 +170,11 @@ size_t nvfp4_gemm_workspace_bytes(int64_t M, int64_t N, int64_t K);
  * nvfp4_gemm_launch(a, b, sfa, sfb, alpha, out, M, N, K, ...) would, with less host work per call.
  * Ownership: the handle is a small HOST object owned by the caller and freed with nvfp4_gemm_release (NULL is
  * accepted).  It refers to b / sfb without owning them: keep both allocated at the same addresses with the same
- * shape while the handle lives (their contents may be rewritten in place).  A handle belongs to the device that was
+ * shape while the handle lives.  A prepared weight is treated as a constant: a launch with the handle starts reading
+ * b / sfb while kernels queued before it on the stream are still finishing (see nvfp4_gemm_tune_pdl), so their
+ * contents must be complete before such a launch is issued - written before nvfp4_gemm_prepare, or rewritten in place
+ * later and followed by a stream / event synchronisation on the host.  (nvfp4_gemm_launch, with raw pointers, makes no
+ * such assumption: its weights may come from the kernel just before it.)  A handle belongs to the device that was
  * current in nvfp4_gemm_prepare; launching it with another device current returns NVFP4_ERR_UNSUPPORTED.  Handles may
  * be used from several host threads at once (they are read-only after creation).
  */
@@ -178,6 +182,23 @@ int nvfp4_gemm_prepare(const uint8_t* b, const uint8_t* sfb, int64_t N, int64_t 
 int nvfp4_gemm_launch_prepared(void* handle, const uint8_t* a, const uint8_t* sfa, const float* alpha, void* out_bf16,
                                int64_t M, void* workspace, size_t workspace_bytes, void* stream);
 int nvfp4_gemm_release(void* handle);
+/*
+ * One activation against several prepared weights of equal K in one call (a layer's q / k / v projections, or gate /
+ * up: what serving stacks fuse into one wider linear layer; no counterpart in the reference, whose weights are
+ * multiplied one by one):
+ *   outs_bf16[i][M, N_i] = alpha_w[i][0] * alpha_a[0] * dq(a) dq(weight_i)^T,   i < n_weights <= 64.
+ * alpha_w[i] points at one float on the device (the weight's global scale, or the finished output scale); alpha_a at
+ * the common factor (the activation's global scale) or is NULL (factor 1).  The product is one fp32 multiplication,
+ * so with alpha_a the result equals nvfp4_gemm_launch_prepared with alpha = alpha_w[i][0] * alpha_a[0] computed by a
+ * separate fp32 multiplication, without that extra launch.  handles / alpha_w / outs_bf16 are HOST arrays read during the call.
+ * For decode-sized M on shapes the decode-sized kernel serves, up to 8 weights go out as ONE launch whose weight tiles
+ * are numbered through the group (fixed costs paid once, every SM on the combined weight stream); otherwise one
+ * launch per weight.  Outputs agree with the one-by-one calls to fp32 rounding before the bf16 store (bit for bit when
+ * the K ranges per tile agree; they are chosen from the group's total tile count).  No workspace.
+ */
+int nvfp4_gemm_launch_grouped(void* const* handles, int n_weights, const uint8_t* a, const uint8_t* sfa,
+                              const float* alpha_a, const float* const* alpha_w, void* const* outs_bf16, int64_t M,
+                              void* stream);
 /* Testing hook (process-wide): 0 = pick the GEMM kernel by shape (default), 1 = 128x128 tiles,
  * 2 = 128x256 tiles, 3 = CTA-pair 256x256 tiles, 4 = CTA-pair 256x192 tiles, 5 = skinny kernel for
  * M <= 128 (weights on the MMA rows, K ranges across a thread-block cluster; the default up to 32 tokens),
@@ -193,9 +214,10 @@ int nvfp4_gemm_plan(int64_t M, int64_t N, int64_t K, int sms, int* path, int* k_
  * weight tile, 1..8) of the skinny kernel instead.  nvfp4_gemm_workspace_bytes reflects the current setting
  * (the skinny kernel itself never needs a workspace). */
 int nvfp4_gemm_tune(int k_splits, int k_rotate);
-/* Testing hook (process-wide): 1 (default) = the decode-sized kernel is launched as a programmatic dependent launch
- * (it may start while the kernel before it on the stream is finishing: its weight stream does not depend on that
- * kernel; everything that does waits), 0 = plain stream order. */
+/* Testing hook (process-wide): 1 (default) = the GEMM kernels, the quantizer and the global-scale kernel are launched
+ * as programmatic dependent launches (each may be scheduled while the kernel before it on the stream is finishing;
+ * a GEMM starts on its weight stream, which does not depend on that kernel, and everything that does depend on it
+ * waits), 0 = plain stream order. */
 int nvfp4_gemm_tune_pdl(int enabled);
 /* Testing hook (process-wide): m-tiles per band of the persistent kernels' tile numbering (0 = default). */
 int nvfp4_gemm_tune_raster(int group);

@@ -4,6 +4,8 @@
 #include <cuda_runtime.h>
 #include <stdint.h>
 
+#include <utility>
+
 #include "nvfp4_b200.h"
 
 namespace nvfp4 {
@@ -101,6 +103,28 @@ __device__ __forceinline__ uint64_t fma_f32x2(uint64_t a, uint64_t b, uint64_t c
 // next launch did not ask for it).
 __device__ __forceinline__ void griddep_wait() { asm volatile("griddepcontrol.wait;" ::: "memory"); }
 __device__ __forceinline__ void griddep_launch() { asm volatile("griddepcontrol.launch_dependents;" ::: "memory"); }
+
+// 1 (default): the library's kernels are launched with the programmatic-stream-serialization attribute; 0: plain
+// launches.  One switch for the whole library (testing hook: nvfp4_gemm_tune_pdl); defined in status.cu.
+extern int g_dependent_launch;
+
+// kernel<<<grid, block, smem, stream>>>(args...) as a programmatic dependent launch.  The kernel must call
+// griddep_wait() before its first access to global memory that an earlier kernel on the stream may write or read.
+template <typename... Params, typename... Args>
+inline cudaError_t launch_dependent(void (*kernel)(Params...), dim3 grid, dim3 block, size_t smem, cudaStream_t stream,
+                                    Args&&... args) {
+    cudaLaunchConfig_t cfg = {};
+    cfg.gridDim = grid;
+    cfg.blockDim = block;
+    cfg.dynamicSmemBytes = smem;
+    cfg.stream = stream;
+    cudaLaunchAttribute attr[1];
+    attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+    attr[0].val.programmaticStreamSerializationAllowed = 1;
+    cfg.attrs = attr;
+    cfg.numAttrs = g_dependent_launch ? 1 : 0;
+    return cudaLaunchKernelEx(&cfg, kernel, std::forward<Args>(args)...);
+}
 
 // Byte offset of block (row, col) in the 128x4-tiled scale layout.
 __host__ __device__ inline int64_t swizzled_scale_offset(int64_t row, int64_t col, int64_t k_pad) {

@@ -56,9 +56,10 @@ extern "C" int nvfp4_gemm_tune_raster(int group) {
     return NVFP4_OK;
 }
 
-// Testing hook: 0 = launch the GEMM kernels without the programmatic-dependent-launch attribute, 1 = with (default).
+// Testing hook: 0 = launch the library's kernels (GEMM, quantizer, global scale) without the programmatic-dependent-launch
+// attribute, 1 = with (default).
 extern "C" int nvfp4_gemm_tune_pdl(int enabled) {
-    nvfp4::gemm::g_gemm_pdl = enabled ? 1 : 0;
+    nvfp4::g_dependent_launch = enabled ? 1 : 0;
     return NVFP4_OK;
 }
 
@@ -189,7 +190,8 @@ extern "C" int nvfp4_gemm_plan(int64_t M, int64_t N, int64_t K, int sms, int* pa
 
 static int gemm_launch_impl(const uint8_t* a, const uint8_t* b, const uint8_t* sfa, const uint8_t* sfb,
                             const float* alpha, void* out_bf16, int64_t M, int64_t N, int64_t K, void* workspace,
-                            size_t workspace_bytes, void* stream, const nvfp4::gemm::WeightHandle* wh) {
+                            size_t workspace_bytes, void* stream, const nvfp4::gemm::WeightHandle* wh,
+                            const float* alpha2 = nullptr) {
     using namespace nvfp4;
     if (M < 0 || N < 0 || K < 0 || (K % 64) != 0) return NVFP4_ERR_BAD_SHAPE;
     if (M == 0 || N == 0) return NVFP4_OK;
@@ -198,12 +200,15 @@ static int gemm_launch_impl(const uint8_t* a, const uint8_t* b, const uint8_t* s
     if (K == 0) return NVFP4_ERR_BAD_SHAPE;
     if ((reinterpret_cast<uintptr_t>(a) & 15) || (reinterpret_cast<uintptr_t>(b) & 15) ||
         (reinterpret_cast<uintptr_t>(sfa) & 15) || (reinterpret_cast<uintptr_t>(sfb) & 15) ||
-        (reinterpret_cast<uintptr_t>(out_bf16) & 15) || (reinterpret_cast<uintptr_t>(alpha) & 3))
+        (reinterpret_cast<uintptr_t>(out_bf16) & 15) || (reinterpret_cast<uintptr_t>(alpha) & 3) ||
+        (reinterpret_cast<uintptr_t>(alpha2) & 3))
         return NVFP4_ERR_MISALIGNED;
     gemm::GemmParams p;
     p.sfa = sfa;
     p.sfb = sfb;
     p.alpha = alpha;
+    p.alpha2 = alpha2;
+    p.weights_ready = wh ? 1 : 0;
     p.out = static_cast<__nv_bfloat16*>(out_bf16);
     p.M = static_cast<int>(M);
     p.N = static_cast<int>(N);
@@ -299,6 +304,75 @@ extern "C" int nvfp4_gemm_launch_prepared(void* handle, const uint8_t* a, const 
     if (h->magic != nvfp4::gemm::kWeightMagic) return NVFP4_ERR_BAD_ENUM;
     if (h->device != nvfp4::gemm::device_info().device) return NVFP4_ERR_UNSUPPORTED;   // prepared on another device
     return gemm_launch_impl(a, h->b, sfa, h->sfb, alpha, out_bf16, M, h->N, h->K, workspace, workspace_bytes, stream, h);
+}
+
+// One activation against several prepared weights of equal K, e.g. a layer's q / k / v projections:
+//   outs[i][M, N_i] = alpha_w[i][0] * alpha_a[0] * dq(a) dq(weight_i)^T      (alpha_a may be NULL: factor 1)
+// Decode-sized batches on shapes the decode-sized kernel is chosen for go out as ONE launch per 8 weights; everything
+// else as one launch per weight.  Each output has the bits nvfp4_gemm_launch_prepared gives for the same weight with
+// alpha = alpha_w[i][0] * alpha_a[0] whenever the K ranges per tile agree (they are chosen from the group's total tile count).
+extern "C" int nvfp4_gemm_launch_grouped(void* const* handles, int n_weights, const uint8_t* a, const uint8_t* sfa,
+                                         const float* alpha_a, const float* const* alpha_w, void* const* outs_bf16,
+                                         int64_t M, void* stream) {
+    using namespace nvfp4;
+    if (n_weights < 0 || n_weights > 64) return NVFP4_ERR_BAD_RANGE;
+    if (n_weights == 0) return NVFP4_OK;
+    if (!handles || !alpha_w || !outs_bf16) return NVFP4_ERR_NULL_POINTER;
+    if (M < 0) return NVFP4_ERR_BAD_SHAPE;
+    const int device = gemm::device_info().device;
+    int64_t K = 0, n_total = 0;
+    for (int i = 0; i < n_weights; ++i) {
+        auto* h = static_cast<const gemm::WeightHandle*>(handles[i]);
+        if (!h || !alpha_w[i] || !outs_bf16[i]) return NVFP4_ERR_NULL_POINTER;
+        if (h->magic != gemm::kWeightMagic) return NVFP4_ERR_BAD_ENUM;
+        if (h->device != device) return NVFP4_ERR_UNSUPPORTED;
+        if (i == 0) K = h->K;
+        else if (h->K != K) return NVFP4_ERR_BAD_SHAPE;
+        if ((reinterpret_cast<uintptr_t>(outs_bf16[i]) & 15) || (reinterpret_cast<uintptr_t>(alpha_w[i]) & 3))
+            return NVFP4_ERR_MISALIGNED;
+        n_total += (h->N + 127) / 128 * 128;
+    }
+    if (M == 0) return NVFP4_OK;
+    if (!a || !sfa) return NVFP4_ERR_NULL_POINTER;
+    if ((reinterpret_cast<uintptr_t>(a) & 15) || (reinterpret_cast<uintptr_t>(sfa) & 15) ||
+        (reinterpret_cast<uintptr_t>(alpha_a) & 3))
+        return NVFP4_ERR_MISALIGNED;
+    if (M > 0x7fffff00LL || n_total > 0x7fffff00LL) return NVFP4_ERR_TOO_LARGE;
+    cudaStream_t s = static_cast<cudaStream_t>(stream);
+    int path = 0, ranges = 1;
+    if (n_weights > 1) plan_gemm(M, n_total, K, gemm::device_info().sms, choose_k_splits(M, n_total, K), &path, &ranges);
+    if (path == 5) {
+        const int forced = g_gemm_force_path == 5 ? g_gemm_force_splits : 0;
+        const int64_t stride = round_up_i64(K / 16, 4) * 128;
+        for (int first = 0; first < n_weights; first += gemm::skinny::kMaxGroup) {
+            const int n = n_weights - first < gemm::skinny::kMaxGroup ? n_weights - first : gemm::skinny::kMaxGroup;
+            gemm::skinny::SkinnyItem items[gemm::skinny::kMaxGroup];
+            for (int i = 0; i < n; ++i) {
+                auto* h = static_cast<const gemm::WeightHandle*>(handles[first + i]);
+                items[i].w = h->b;
+                items[i].sfw = h->sfb;
+                items[i].alpha = alpha_w[first + i];
+                items[i].out = static_cast<__nv_bfloat16*>(outs_bf16[first + i]);
+                items[i].N = h->N;
+                items[i].wh = h;
+            }
+            const int m = static_cast<int>(M), k = static_cast<int>(K);
+            int st;
+            if (M <= 16) st = gemm::skinny::launch_skinny_group<16>(a, sfa, alpha_a, m, k, stride, items, n, forced, s);
+            else if (M <= 32) st = gemm::skinny::launch_skinny_group<32>(a, sfa, alpha_a, m, k, stride, items, n, forced, s);
+            else if (M <= 64) st = gemm::skinny::launch_skinny_group<64>(a, sfa, alpha_a, m, k, stride, items, n, forced, s);
+            else st = gemm::skinny::launch_skinny_group<128>(a, sfa, alpha_a, m, k, stride, items, n, forced, s);
+            if (st != NVFP4_OK) return st;
+        }
+        return NVFP4_OK;
+    }
+    for (int i = 0; i < n_weights; ++i) {
+        auto* h = static_cast<const gemm::WeightHandle*>(handles[i]);
+        const int st = gemm_launch_impl(a, h->b, sfa, h->sfb, alpha_w[i], outs_bf16[i], M, h->N, h->K, nullptr, 0, stream, h,
+                                        alpha_a);
+        if (st != NVFP4_OK) return st;
+    }
+    return NVFP4_OK;
 }
 
 extern "C" int nvfp4_gemm_last_status(void* stream, uint32_t* status_host) {

@@ -173,6 +173,7 @@ gemm_pair_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_consta
                 }
             };
             int early = 0;
+            if (!p.weights_ready) griddep_wait();
             if (pair_id < total_tiles) {
                 int mt, nt;
                 tile_to_mn(pair_id, m_tiles, n_tiles, p.raster_group, mt, nt);
@@ -270,7 +271,7 @@ gemm_pair_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_consta
     } else {
         // ------------------------------------------------------------------ epilogue (both CTAs)
         const int sp = warp & 3;
-        const float alpha = __ldg(p.alpha);
+        const float alpha = load_alpha(p.alpha, p.alpha2);
         uint32_t acc_phase = 0;
         int acc = 0;
         bool ok = true;
@@ -390,7 +391,7 @@ static int launch_pair(const uint8_t* a, const uint8_t* b, const GemmParams& p, 
     attr[1].id = cudaLaunchAttributeProgrammaticStreamSerialization;   // may start while its predecessor finishes
     attr[1].val.programmaticStreamSerializationAllowed = 1;
     cfg.attrs = attr;
-    cfg.numAttrs = g_gemm_pdl ? 2 : 1;
+    cfg.numAttrs = g_dependent_launch ? 2 : 1;
     e = cudaLaunchKernelEx(&cfg, gemm_pair_kernel<BN>, ma, mb, msa, msb, p);
     return static_cast<int>(e);
 }

@@ -57,20 +57,38 @@ __device__ __forceinline__ void bulk_copy_to_cta(uint32_t dst_cluster, uint32_t 
                  : "memory");
 }
 
+// One launch may multiply the same token tile with several weight matrices of equal K (a layer's q / k / v, or gate /
+// up projections): the weight tiles of all of them are numbered through, and a CTA looks up whose tile it owns.  The
+// launch's fixed costs (prologue, ramp-up and drain of the weight stream) are then paid once per group.
+constexpr int kMaxGroup = 8;
+
+struct SkinnyWeight {
+    const uint8_t* sfw;   // weight scales
+    const float* alpha;   // output scale of this weight (times alpha_x when that is given)
+    __nv_bfloat16* out;   // [M, N]
+    int N;
+    int tile_end;         // number of 128-row tiles of this and all earlier weights of the group
+};
+
 struct SkinnyParams {
     const uint8_t* sfx;   // token scales (group 0 of the tiled layout)
-    const uint8_t* sfw;   // weight scales
-    const float* alpha;
-    __nv_bfloat16* out;   // [M, N]
-    int M, N, K;
+    const float* alpha_x; // optional common factor of every output scale
+    int M, K;
     int64_t sf_group_stride;
     int k_tiles_per_rank;
     int stages;
+    int n_weights;
+    int weights_ready;    // != 0: all weights are prepared weights (constant while in use): read them before griddep_wait()
+    SkinnyWeight w[kMaxGroup];
+};
+
+struct SkinnyMaps {
+    CUtensorMap m[kMaxGroup];   // one per weight: [N, K/2] bytes in boxes of 128 rows x 128 bytes
 };
 
 template <int BT>
 __global__ void __launch_bounds__(kThreads)
-skinny_kernel(const __grid_constant__ CUtensorMap tmap_w, const __grid_constant__ CUtensorMap tmap_x, const SkinnyParams p) {
+skinny_kernel(const __grid_constant__ SkinnyMaps maps, const __grid_constant__ CUtensorMap tmap_x, const SkinnyParams p) {
     using C = SkinnyCfg<BT>;
     extern __shared__ uint8_t smem_raw[];
     const uint32_t raw_addr = smem_u32(smem_raw);
@@ -91,7 +109,14 @@ skinny_kernel(const __grid_constant__ CUtensorMap tmap_w, const __grid_constant_
     const uint32_t rank = cluster_ctarank();
     uint32_t ranks;
     asm volatile("mov.u32 %0, %%cluster_nctarank;" : "=r"(ranks));
-    const int nt = blockIdx.x / ranks;                  // 128-row weight tile (clusters run along x)
+    // clusters run along x: cluster index = 128-row weight tile, numbered through the weights of the group
+    const int tile = blockIdx.x / ranks;
+    int gi = 0;
+    while (gi + 1 < p.n_weights && tile >= p.w[gi].tile_end) ++gi;
+    const int nt = tile - (gi > 0 ? p.w[gi - 1].tile_end : 0);
+    const CUtensorMap* tmap_w = &maps.m[gi];
+    const uint8_t* const sfw = p.w[gi].sfw;
+    const int N = p.w[gi].N;
     // reduce-scatter: token column c belongs to rank c / cols_per_rank
     const uint32_t m_cols = static_cast<uint32_t>(min(p.M, BT));
     const uint32_t cols_per_rank = (m_cols + ranks - 1) / ranks;
@@ -134,10 +159,10 @@ skinny_kernel(const __grid_constant__ CUtensorMap tmap_w, const __grid_constant_
             const uint32_t sbase = base + stage * C::kStageBytes;
             if (issuer) {
                 mbar_expect_tx(full_bar(stage), C::kWBytes + C::kXBytes + 2 * sf_bytes);
-                tma_load_2d(sbase, &tmap_w, kt * kBKBytes, nt * 128, full_bar(stage));
+                tma_load_2d(sbase, tmap_w, kt * kBKBytes, nt * 128, full_bar(stage));
                 tma_load_2d(sbase + C::kWBytes, &tmap_x, kt * kBKBytes, 0, full_bar(stage));
                 bulk_load_1d(sbase + C::kWBytes + C::kXBytes,
-                             p.sfw + static_cast<int64_t>(nt) * p.sf_group_stride + static_cast<int64_t>(kt) * 2048, sf_bytes,
+                             sfw + static_cast<int64_t>(nt) * p.sf_group_stride + static_cast<int64_t>(kt) * 2048, sf_bytes,
                              full_bar(stage));
                 bulk_load_1d(sbase + C::kWBytes + C::kXBytes + C::kSfBytes, p.sfx + static_cast<int64_t>(kt) * 2048, sf_bytes,
                              full_bar(stage));
@@ -152,7 +177,7 @@ skinny_kernel(const __grid_constant__ CUtensorMap tmap_w, const __grid_constant_
     if (warp == 0) {
         __syncwarp();   // thread 0's barrier initialisation above, before any lane of this warp uses the barriers
         if (elect_one()) {
-            asm volatile("prefetch.tensormap [%0];" ::"l"(&tmap_w) : "memory");
+            asm volatile("prefetch.tensormap [%0];" ::"l"(tmap_w) : "memory");
             asm volatile("prefetch.tensormap [%0];" ::"l"(&tmap_x) : "memory");
         }
         // First ring-full.  The weights do not depend on whatever ran before this kernel on the stream, the token tile
@@ -160,15 +185,16 @@ skinny_kernel(const __grid_constant__ CUtensorMap tmap_w, const __grid_constant_
         // at once, the rest after griddep_wait().
         const int first = min(kcount, nstages);
         const bool issuer = elect_one();
+        if (!p.weights_ready) griddep_wait();   // raw weight pointers: they may be the previous kernel's output too
         if (issuer) {
             for (int i = 0; i < first; ++i) {
                 const int kt = kt_begin + i;
                 const uint32_t sf_bytes = 512u * min(4, (p.K - kt * kBK + 63) / 64);
                 const uint32_t sbase = base + i * C::kStageBytes;
                 mbar_expect_tx(full_bar(i), C::kWBytes + C::kXBytes + 2 * sf_bytes);
-                tma_load_2d(sbase, &tmap_w, kt * kBKBytes, nt * 128, full_bar(i));
+                tma_load_2d(sbase, tmap_w, kt * kBKBytes, nt * 128, full_bar(i));
                 bulk_load_1d(sbase + C::kWBytes + C::kXBytes,
-                             p.sfw + static_cast<int64_t>(nt) * p.sf_group_stride + static_cast<int64_t>(kt) * 2048, sf_bytes,
+                             sfw + static_cast<int64_t>(nt) * p.sf_group_stride + static_cast<int64_t>(kt) * 2048, sf_bytes,
                              full_bar(i));
             }
         }
@@ -258,17 +284,18 @@ skinny_kernel(const __grid_constant__ CUtensorMap tmap_w, const __grid_constant_
     const uint32_t t_lane = tmem_base + (static_cast<uint32_t>(sp * 32) << 16);
     if (ranks == 1) {
         if (warp >= 2 && have) {
-            const float alpha = __ldg(p.alpha);
+            const float alpha = load_alpha(p.w[gi].alpha, p.alpha_x);
+            __nv_bfloat16* const out = p.w[gi].out;
 #pragma unroll 1
             for (int c = 0; c < BT / 16 && c * 16 < p.M; ++c) {
                 uint32_t v[16];
                 tc_ld_32x32b_x16(t_lane + c * 16, v);
                 tc_ld_wait();
-                if (n < p.N) {
+                if (n < N) {
 #pragma unroll
                     for (int e = 0; e < 16; ++e)
                         if (c * 16 + e < p.M)
-                            p.out[static_cast<int64_t>(c * 16 + e) * p.N + n] =
+                            out[static_cast<int64_t>(c * 16 + e) * N + n] =
                                 __float2bfloat16_rn(__fmul_rn(__uint_as_float(v[e]), alpha));
                 }
             }
@@ -304,12 +331,12 @@ skinny_kernel(const __grid_constant__ CUtensorMap tmap_w, const __grid_constant_
         if (warp >= 2 && have && my_cols > 0) {
             bool ok = mbar_wait(recv_bar, 0, abort_flag, (10u << 24) | nt);
             ok = __shfl_sync(0xffffffffu, ok ? 1 : 0, 0) != 0;
-            if (ok && n < p.N) {
-                const float alpha = __ldg(p.alpha);
+            if (ok && n < N) {
+                const float alpha = load_alpha(p.w[gi].alpha, p.alpha_x);
                 // this rank's own partial sits in `recv` terms at part[my_first ..]; eight columns at a time so that
                 // the shared-memory loads of one rank's partials are in flight together
                 const float* own = part + my_first * 128 + n_local;
-                __nv_bfloat16* dst = p.out + static_cast<int64_t>(my_first) * p.N + n;
+                __nv_bfloat16* dst = p.w[gi].out + static_cast<int64_t>(my_first) * N + n;
                 for (uint32_t c0 = 0; c0 < my_cols; c0 += 8) {
                     float acc[8];
 #pragma unroll
@@ -325,7 +352,7 @@ skinny_kernel(const __grid_constant__ CUtensorMap tmap_w, const __grid_constant_
 #pragma unroll
                     for (int j = 0; j < 8; ++j)
                         if (c0 + j < my_cols)
-                            dst[static_cast<int64_t>(c0 + j) * p.N] = __float2bfloat16_rn(__fmul_rn(acc[j], alpha));
+                            dst[static_cast<int64_t>(c0 + j) * N] = __float2bfloat16_rn(__fmul_rn(acc[j], alpha));
                 }
             }
         }
@@ -365,33 +392,75 @@ static int choose_ranks(int n_tiles, int k_tiles, int sms, int forced, int bt) {
     return r;
 }
 
+// One weight of a grouped launch, as the host sees it.
+struct SkinnyItem {
+    const uint8_t* w;         // codes [N, K/2]
+    const uint8_t* sfw;       // tiled scales
+    const float* alpha;
+    __nv_bfloat16* out;       // [M, N]
+    int64_t N;
+    const WeightHandle* wh;   // prepared tensor maps, or NULL
+};
+
+// Ring depth: the deepest ring with which the whole grid is resident at once (as many CTAs per SM as that takes, at
+// most what the TMEM columns allow), since a CTA that has to wait for a free SM starts its weight stream late.
 template <int BT>
-static int launch_skinny(const uint8_t* x, const uint8_t* w, const GemmParams& g, int forced_ranks, cudaStream_t stream,
-                         const WeightHandle* wh) {
+static int choose_stages(int ctas, int sms) {
     using C = SkinnyCfg<BT>;
-    CUtensorMap mw_local, mx;
-    int st = make_operand_map(&mx, x, g.M, g.K / 2, BT);
-    if (st == NVFP4_OK && !wh) st = make_operand_map(&mw_local, w, g.N, g.K / 2, 128);
+    constexpr int kMaxPerSm = kTmemCols / C::kTmemCols;
+    int per_sm = (ctas + sms - 1) / sms;
+    if (per_sm < 1) per_sm = 1;
+    if (per_sm > kMaxPerSm) per_sm = kMaxPerSm;
+    // an SM has 233472 bytes of shared memory, of which 1 KiB per resident CTA is reserved; a CTA asks for its ring
+    // plus 1 KiB of alignment slack plus 256 bytes of barriers
+    int stages = (233472 / per_sm - 1024 - 1024 - 256) / C::kStageBytes;
+    if (stages > C::kMaxStages) stages = C::kMaxStages;
+    if (stages < 2) stages = 2;
+    return stages;
+}
+
+template <int BT>
+static int launch_skinny_group(const uint8_t* x, const uint8_t* sfx, const float* alpha_x, int M, int K,
+                               int64_t sf_group_stride, const SkinnyItem* items, int n_items, int forced_ranks,
+                               cudaStream_t stream) {
+    using C = SkinnyCfg<BT>;
+    if (n_items < 1 || n_items > kMaxGroup) return NVFP4_ERR_BAD_RANGE;
+    SkinnyMaps maps;
+    CUtensorMap mx;
+    int st = make_operand_map(&mx, x, M, K / 2, BT);
+    SkinnyParams p;
+    int n_tiles = 0;
+    p.weights_ready = 1;
+    for (int i = 0; i < n_items && st == NVFP4_OK; ++i) {
+        const SkinnyItem& it = items[i];
+        if (!it.wh) p.weights_ready = 0;
+        if (it.wh) maps.m[i] = it.wh->rows128;
+        else st = make_operand_map(&maps.m[i], it.w, it.N, K / 2, 128);
+        n_tiles += static_cast<int>((it.N + 127) / 128);
+        p.w[i].sfw = it.sfw;
+        p.w[i].alpha = it.alpha;
+        p.w[i].out = it.out;
+        p.w[i].N = static_cast<int>(it.N);
+        p.w[i].tile_end = n_tiles;
+    }
     if (st != NVFP4_OK) return st;
-    const CUtensorMap& mw = wh ? wh->rows128 : mw_local;
+    for (int i = n_items; i < kMaxGroup; ++i) {   // unused slots: defined values, never dereferenced
+        maps.m[i] = maps.m[0];
+        p.w[i] = p.w[n_items - 1];
+    }
     const DeviceInfo di = device_info();
     const int sms = di.sms;
-    const int n_tiles = (g.N + 127) / 128;
-    const int k_tiles = (g.K + kBK - 1) / kBK;
+    const int k_tiles = (K + kBK - 1) / kBK;
     int ranks = choose_ranks(n_tiles, k_tiles, sms, forced_ranks, BT);
-    SkinnyParams p;
-    p.sfx = g.sfa;
-    p.sfw = g.sfb;
-    p.alpha = g.alpha;
-    p.out = g.out;
-    p.M = g.M;
-    p.N = g.N;
-    p.K = g.K;
-    p.sf_group_stride = g.sf_group_stride;
+    p.sfx = sfx;
+    p.alpha_x = alpha_x;
+    p.M = M;
+    p.K = K;
+    p.sf_group_stride = sf_group_stride;
+    p.n_weights = n_items;
     p.k_tiles_per_rank = (k_tiles + ranks - 1) / ranks;
     ranks = (k_tiles + p.k_tiles_per_rank - 1) / p.k_tiles_per_rank;   // no empty range
-    // one CTA per SM with a deep ring when the whole grid is resident at once, else two CTAs per SM
-    p.stages = (n_tiles * ranks <= sms) ? C::kMaxStages : 4;
+    p.stages = choose_stages<BT>(n_tiles * ranks, sms);
     if (p.stages > p.k_tiles_per_rank) p.stages = p.k_tiles_per_rank < 2 ? 2 : p.k_tiles_per_rank;
     // the ring doubles as the reduce-scatter buffers: the partial tile plus one slot per rank of the owned columns
     while (ranks > 1 && (2 * BT + 8) * 512 > p.stages * C::kStageBytes) ++p.stages;
@@ -422,9 +491,22 @@ static int launch_skinny(const uint8_t* x, const uint8_t* w, const GemmParams& g
     attr[1].id = cudaLaunchAttributeProgrammaticStreamSerialization;
     attr[1].val.programmaticStreamSerializationAllowed = 1;
     cfg.attrs = attr;
-    cfg.numAttrs = g_gemm_pdl ? 2 : 1;
-    e = cudaLaunchKernelEx(&cfg, skinny_kernel<BT>, mw, mx, p);
+    cfg.numAttrs = g_dependent_launch ? 2 : 1;
+    e = cudaLaunchKernelEx(&cfg, skinny_kernel<BT>, maps, mx, p);
     return static_cast<int>(e);
+}
+
+template <int BT>
+static int launch_skinny(const uint8_t* x, const uint8_t* w, const GemmParams& g, int forced_ranks, cudaStream_t stream,
+                         const WeightHandle* wh) {
+    SkinnyItem it;
+    it.w = w;
+    it.sfw = g.sfb;
+    it.alpha = g.alpha;
+    it.out = g.out;
+    it.N = g.N;
+    it.wh = wh;
+    return launch_skinny_group<BT>(x, g.sfa, g.alpha2, g.M, g.K, g.sf_group_stride, &it, 1, forced_ranks, stream);
 }
 
 }  // namespace skinny

@@ -31,6 +31,7 @@ struct GemmParams {
     const uint8_t* sfa;
     const uint8_t* sfb;
     const float* alpha;
+    const float* alpha2;      // optional second factor: the output scale is alpha[0] * alpha2[0] (one fp32 multiplication)
     __nv_bfloat16* out;
     int M, N, K;
     int64_t sf_group_stride;  // bytes between consecutive 128-row scale groups = round_up(K/16, 4) * 128
@@ -41,7 +42,17 @@ struct GemmParams {
     int k_rotate;             // != 0: each tile starts its K loop at a different stage (spreads requests for shared A rows)
     float* partial;
     int raster_group;         // m-tiles per band of the tile numbering (see tile_to_mn)
+    // != 0: the weight operand is a prepared weight, constant while launches with it are in flight, and may be read
+    // before griddep_wait(); 0 (raw pointers): it may be the output of the kernel just before this one, like the tokens
+    int weights_ready;
 };
+
+// Output scale of a launch: alpha[0], or alpha[0] * alpha2[0] rounded once (what a separate fp32 multiplication of the
+// activation's and the weight's global scales gives).
+__device__ __forceinline__ float load_alpha(const float* alpha, const float* alpha2) {
+    const float a = __ldg(alpha);
+    return alpha2 ? __fmul_rn(a, __ldg(alpha2)) : a;
+}
 
 // Tile index -> (m tile, n tile).  Tiles are numbered in bands of `group` m-tiles: inside a band the m index runs
 // fastest, then n.  The CTAs that run at the same time then cover a roughly square patch of the output, so every A
@@ -162,6 +173,7 @@ gemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant__ 
                 }
             };
             int early = 0;
+            if (!p.weights_ready) griddep_wait();
             if (static_cast<int>(blockIdx.x) < total_tiles && !p.k_rotate) {
                 const int ks = blockIdx.x / mn_tiles, t2 = blockIdx.x - ks * mn_tiles;
                 int mt, nt;
@@ -277,7 +289,7 @@ gemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant__ 
     } else {
         // ------------------------------------------------------------------ epilogue (warps 2..5)
         const int sp = warp & 3;  // TMEM sub-partition this warp may read: lanes 32*sp .. 32*sp+31
-        const float alpha = __ldg(p.alpha);
+        const float alpha = load_alpha(p.alpha, p.alpha2);
         int acc = 0;
         uint32_t acc_phase = 0;
         bool ok = true;
@@ -360,8 +372,9 @@ gemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant__ 
 
 // out[m, n] = bf16(alpha * sum over K ranges of partial[s][m][n]); ranges are added in ascending order.
 __global__ void __launch_bounds__(256) splitk_reduce_kernel(const float* __restrict__ partial, const float* alpha_ptr,
-                                                            __nv_bfloat16* __restrict__ out, int64_t mn, int splits) {
-    const float alpha = __ldg(alpha_ptr);
+                                                            const float* alpha2_ptr, __nv_bfloat16* __restrict__ out,
+                                                            int64_t mn, int splits) {
+    const float alpha = load_alpha(alpha_ptr, alpha2_ptr);
     for (int64_t i = static_cast<int64_t>(blockIdx.x) * 256 + threadIdx.x; i < mn; i += static_cast<int64_t>(gridDim.x) * 256) {
         float acc = partial[i];
         for (int s = 1; s < splits; ++s) acc = __fadd_rn(acc, partial[static_cast<int64_t>(s) * mn + i]);
@@ -404,7 +417,6 @@ static int make_operand_map(CUtensorMap* map, const void* ptr, int64_t rows, int
 }
 
 // Per-device facts the launchers need on every call, looked up once per device.
-static int g_gemm_pdl = 1;   // programmatic dependent launch of the GEMM kernels (testing hook: nvfp4_gemm_tune_pdl)
 
 struct DeviceInfo {
     int device;
@@ -473,13 +485,13 @@ static int launch(const uint8_t* a, const uint8_t* b, const GemmParams& p, cudaS
     attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;   // may start while its predecessor finishes
     attr[0].val.programmaticStreamSerializationAllowed = 1;
     cfg.attrs = attr;
-    cfg.numAttrs = g_gemm_pdl ? 1 : 0;
+    cfg.numAttrs = g_dependent_launch ? 1 : 0;
     e = cudaLaunchKernelEx(&cfg, gemm_kernel<BN>, ma, mb, p);
     if (e != cudaSuccess || p.k_splits == 1) return static_cast<int>(e);
     const int64_t mn = static_cast<int64_t>(p.M) * p.N;
     int64_t rblocks = (mn + 255) / 256;
     if (rblocks > 148 * 8) rblocks = 148 * 8;
-    splitk_reduce_kernel<<<static_cast<unsigned>(rblocks), 256, 0, stream>>>(p.partial, p.alpha, p.out, mn, p.k_splits);
+    splitk_reduce_kernel<<<static_cast<unsigned>(rblocks), 256, 0, stream>>>(p.partial, p.alpha, p.alpha2, p.out, mn, p.k_splits);
     return static_cast<int>(cudaGetLastError());
 }
 

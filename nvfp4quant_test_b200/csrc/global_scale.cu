@@ -23,6 +23,10 @@ __device__ __forceinline__ uint32_t umax2x16(uint32_t a, uint32_t b) { return __
 template <int DT>
 __global__ void __launch_bounds__(kGsThreads) global_scale_kernel(const void* x, int64_t numel, float fp8_max,
                                                                   float* out, uint32_t* scratch) {
+    // launched as a programmatic dependent: x, the scratch words and `out` belong to the kernel before this one until
+    // it has finished; the kernel behind this one (the quantizer) may be scheduled from here on
+    griddep_wait();
+    griddep_launch();
     constexpr int kPerVec = (DT == NVFP4_DT_F32) ? 4 : 8;
     const int64_t nvec = numel / kPerVec;
     const uint4* xv = static_cast<const uint4*>(x);
@@ -112,10 +116,13 @@ extern "C" int nvfp4_global_scale_launch(const void* x, int x_dtype, int64_t num
     if (blocks < 1) blocks = 1;
     cudaStream_t s = static_cast<cudaStream_t>(stream);
     const unsigned g = static_cast<unsigned>(blocks);
+    const dim3 grid(g), block(kGsThreads);
     switch (x_dtype) {
-        case NVFP4_DT_BF16: global_scale_kernel<NVFP4_DT_BF16><<<g, kGsThreads, 0, s>>>(x, numel, fp8_max, out, scratch); break;
-        case NVFP4_DT_F16: global_scale_kernel<NVFP4_DT_F16><<<g, kGsThreads, 0, s>>>(x, numel, fp8_max, out, scratch); break;
-        default: global_scale_kernel<NVFP4_DT_F32><<<g, kGsThreads, 0, s>>>(x, numel, fp8_max, out, scratch); break;
+        case NVFP4_DT_BF16:
+            return static_cast<int>(launch_dependent(global_scale_kernel<NVFP4_DT_BF16>, grid, block, 0, s, x, numel, fp8_max, out, scratch));
+        case NVFP4_DT_F16:
+            return static_cast<int>(launch_dependent(global_scale_kernel<NVFP4_DT_F16>, grid, block, 0, s, x, numel, fp8_max, out, scratch));
+        default:
+            return static_cast<int>(launch_dependent(global_scale_kernel<NVFP4_DT_F32>, grid, block, 0, s, x, numel, fp8_max, out, scratch));
     }
-    return static_cast<int>(cudaGetLastError());
 }

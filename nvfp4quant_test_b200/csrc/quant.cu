@@ -344,6 +344,9 @@ quant_kernel(const QuantParams p) {
     __shared__ float4 tab[kTabSize];
     constexpr bool FUSED = IMPL == 4;
     static_assert(!FUSED || VARIANT != NVFP4_VARIANT_AMAX, "the fused variant covers the two sweeps");
+    // launched as a programmatic dependent: the input, the global scale and the output buffers may still be in use by
+    // the kernel before this one on the stream
+    if (!FUSED) griddep_wait();
     float gs_inv = FUSED ? 0.0f : __ldg(p.gs_inv);
     // Body 6 = body 3 with a two-dimensional grid: blockIdx.x is the row, blockIdx.y the 256-block column chunk.
     // The row is then uniform over the CTA, so the division below, the row part of the addresses and most of the
@@ -524,30 +527,30 @@ cudaError_t launch_impl(int impl, const QuantParams& p, cudaStream_t stream) {
     if constexpr (VARIANT != NVFP4_VARIANT_AMAX) {
         if ((impl == 8 || impl == 0) && whole) {
             const dim3 grid2(static_cast<unsigned>(p.rows), static_cast<unsigned>(p.width / kThreads));
-            quant_kernel<DT, VARIANT, 8><<<grid2, kThreads, 0, stream>>>(p);
-            return cudaGetLastError();
+            return launch_dependent(quant_kernel<DT, VARIANT, 8>, grid2, dim3(kThreads), 0, stream, p);
         }
     }
     if (impl >= 8) impl = 0;
+    cudaError_t e;
     if (impl == 1)
-        quant_kernel<DT, VARIANT, 1><<<static_cast<unsigned>(grid), kThreads, 0, stream>>>(p);
+        e = launch_dependent(quant_kernel<DT, VARIANT, 1>, static_cast<unsigned>(grid), dim3(kThreads), 0, stream, p);
     else if (impl == 2)
-        quant_kernel<DT, VARIANT, 2><<<static_cast<unsigned>(grid), kThreads, 0, stream>>>(p);
+        e = launch_dependent(quant_kernel<DT, VARIANT, 2>, static_cast<unsigned>(grid), dim3(kThreads), 0, stream, p);
     else if (impl == 5 || (impl == 0 && (p.rows - p.m) * 4 >= p.rows))
-        quant_kernel<DT, VARIANT, 5><<<static_cast<unsigned>(grid), kThreads, 0, stream>>>(p);
+        e = launch_dependent(quant_kernel<DT, VARIANT, 5>, static_cast<unsigned>(grid), dim3(kThreads), 0, stream, p);
     else if ((impl == 6 || impl == 7 || impl == 0) && (p.width % kThreads) == 0 && p.width / kThreads <= 65535 &&
              p.rows <= 0x7fffffffLL) {
         const dim3 grid2(static_cast<unsigned>(p.rows), static_cast<unsigned>(p.width / kThreads));
         // the reference's own windows (11 candidates unweighted, 16 weighted) have an unrolled instantiation
         const bool fixed = VARIANT == NVFP4_VARIANT_MSE ? p.ncand == 11 : VARIANT == NVFP4_VARIANT_WEIGHTED && p.ncand == 16;
         if (fixed && (impl == 7 || (impl == 0 && VARIANT == NVFP4_VARIANT_MSE)))
-            quant_kernel<DT, VARIANT, 7><<<grid2, kThreads, 0, stream>>>(p);
+            e = launch_dependent(quant_kernel<DT, VARIANT, 7>, grid2, dim3(kThreads), 0, stream, p);
         else
-            quant_kernel<DT, VARIANT, 6><<<grid2, kThreads, 0, stream>>>(p);
+            e = launch_dependent(quant_kernel<DT, VARIANT, 6>, grid2, dim3(kThreads), 0, stream, p);
     }
     else
-        quant_kernel<DT, VARIANT, 3><<<static_cast<unsigned>(grid), kThreads, 0, stream>>>(p);
-    return cudaGetLastError();
+        e = launch_dependent(quant_kernel<DT, VARIANT, 3>, static_cast<unsigned>(grid), dim3(kThreads), 0, stream, p);
+    return e;
 }
 
 template <int DT>

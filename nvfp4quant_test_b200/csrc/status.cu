@@ -3,6 +3,10 @@
 
 #include "nvfp4_b200.h"
 
+namespace nvfp4 {
+int g_dependent_launch = 1;   // see common.cuh
+}
+
 extern "C" const char* nvfp4_status_string(int status) {
     switch (status) {
         case NVFP4_OK: return "ok";

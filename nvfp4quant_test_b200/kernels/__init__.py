@@ -11,7 +11,8 @@ from .kernel_ScaleSweep import (  # noqa: F401
 )
 from .kernel_fused import scalesweep_nvfp4_quant_with_global_scale  # noqa: F401
 from .kernel_amax import amax_nvfp4_quant_impl, amax_nvfp4_quant_out, scaled_fp4_quant  # noqa: F401
-from .kernel_gemm import PreparedWeight, cutlass_scaled_fp4_mm, nvfp4_scaled_mm, nvfp4_scaled_mm_prepared  # noqa: F401
+from .kernel_gemm import (PreparedWeight, cutlass_scaled_fp4_mm, nvfp4_scaled_mm, nvfp4_scaled_mm_grouped,  # noqa: F401
+                          nvfp4_scaled_mm_prepared)
 from .kernel_vllm import (  # noqa: F401
     create_fp4_output_tensors,
     round_up,

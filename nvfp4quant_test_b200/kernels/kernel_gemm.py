@@ -143,6 +143,59 @@ def nvfp4_scaled_mm_prepared(a: torch.Tensor, block_scale_a: torch.Tensor, alpha
     return out
 
 
+def nvfp4_scaled_mm_grouped(a: torch.Tensor, block_scale_a: torch.Tensor, alpha_a: torch.Tensor | None,
+                            weights: list[PreparedWeight], alpha_w: list[torch.Tensor],
+                            outs: list[torch.Tensor] | None = None) -> list[torch.Tensor]:
+    """[alpha_w[i] * alpha_a * dq(a) @ dq(weights[i]).T for i] as bf16 [M, N_i] tensors: one activation against several
+    prepared weights of equal K (a layer's q / k / v, or gate / up).  `alpha_a` (the activation's global scale, or None)
+    and each `alpha_w[i]` (the weight's global scale) are one-element float32 CUDA tensors; their product is taken inside
+    the kernel.  At decode-sized M the whole group is one launch (nvfp4_gemm_launch_grouped)."""
+    import ctypes
+
+    n = len(weights)
+    if n == 0:
+        return []
+    if len(alpha_w) != n or (outs is not None and len(outs) != n):
+        raise ValueError("weights, alpha_w and outs must have the same length")
+    if n > 64:
+        raise ValueError("at most 64 weights per call")
+    dev, k = weights[0].device, weights[0].k
+    if a.ndim != 2 or a.dtype != torch.uint8 or a.device != dev:
+        raise ValueError("a must be a uint8 [M, K/2] tensor on the weights' device")
+    if a.shape[1] * 2 != k:
+        raise ValueError(f"a and the weights disagree on K: {a.shape[1] * 2} vs {k}")
+    if not a.is_contiguous():
+        a = a.contiguous()
+    sfa = block_scale_a if block_scale_a.is_contiguous() else block_scale_a.contiguous()
+    m = a.shape[0]
+    if sfa.numel() * sfa.element_size() < _scale_bytes(m, k):
+        raise ValueError("block_scale_a is smaller than the tiled layout of a needs")
+    if alpha_a is not None and (alpha_a.dtype != torch.float32 or alpha_a.device != dev or alpha_a.numel() < 1):
+        raise ValueError("alpha_a must be a float32 tensor on a's device")
+    if outs is None:
+        outs = [torch.empty((m, w.n), dtype=torch.bfloat16, device=dev) for w in weights]
+    for w, al, o in zip(weights, alpha_w, outs):
+        if w.device != dev or w.k != k:
+            raise ValueError("all weights of a group share the device and K")
+        if not w._handle:
+            raise ValueError("a prepared weight of the group has been closed")
+        if al.dtype != torch.float32 or al.device != dev or al.numel() < 1:
+            raise ValueError("alpha_w entries must be float32 tensors on a's device")
+        if o.shape != (m, w.n) or o.dtype != torch.bfloat16 or not o.is_contiguous() or o.device != dev:
+            raise ValueError("outs[i] must be a contiguous bfloat16 [M, N_i] tensor on a's device")
+    if m == 0:
+        return outs
+    handles = (ctypes.c_void_p * n)(*[w._handle.value for w in weights])
+    alphas = (ctypes.c_void_p * n)(*[al.data_ptr() for al in alpha_w])
+    out_ptrs = (ctypes.c_void_p * n)(*[o.data_ptr() for o in outs])
+    with _lib.device_guard(dev):
+        st = _lib.lib().nvfp4_gemm_launch_grouped(handles, n, a.data_ptr(), sfa.data_ptr(),
+                                                  None if alpha_a is None else alpha_a.data_ptr(), alphas, out_ptrs, m,
+                                                  _lib.current_stream_ptr(dev))
+    _lib.check(st, "nvfp4_gemm_launch_grouped")
+    return outs
+
+
 def cutlass_scaled_fp4_mm(a, b, block_scale_a, block_scale_b, alpha, out_dtype):
     """Drop-in name of the vllm op."""
     return nvfp4_scaled_mm(a, b, block_scale_a, block_scale_b, alpha, out_dtype)

@@ -97,6 +97,34 @@ def prepare_layer(qlayer: dict) -> dict:
     return {name: K.PreparedWeight(codes, scales) for name, (codes, scales, _) in qlayer.items()}
 
 
+# matrices that read the same activation in a decoder layer (q / k / v the normed hidden state, gate / up the normed
+# post-attention state); o and down have inputs of their own
+WEIGHT_GROUPS = (("q", "k", "v"), ("o",), ("gate", "up"), ("down",))
+GROUPED_MAX_TOKENS = 128
+
+
+def layer_gemms_grouped(qlayer: dict, acts: dict[int, torch.Tensor], weight_scales: dict, prepared: dict):
+    """The layer's GEMMs at a decode-sized batch, on the current stream: per input width one global scale and one
+    unweighted sweep of the activation, then one grouped launch per WEIGHT_GROUPS entry (the output scale = activation
+    global scale x weight global scale is formed inside the kernel).  Every launch is a programmatic dependent launch
+    of the one before it.  Returns {name: bf16 [tokens, N]}."""
+    out = {}
+    qact: dict[int, tuple] = {}
+    for group in WEIGHT_GROUPS:
+        k = qlayer[group[0]][0].shape[1] * 2
+        if k not in qact:
+            x = acts[k]
+            gs_x, gs_x_inv = H.get_nvfp4_global_scale(x, H.FP8_E4M3_MAX_4OVER6)
+            qa, sa = K.scalesweep_mse_nvfp4_quant_impl(x, gs_x_inv)
+            qact[k] = (qa, sa, gs_x.reshape(1))
+        qa, sa, gs_x = qact[k]
+        vec, slots = weight_scales[k]
+        ys = K.nvfp4_scaled_mm_grouped(qa, sa, gs_x, [prepared[n] for n in group],
+                                       [vec[slots[n]:slots[n] + 1] for n in group])
+        out.update(zip(group, ys))
+    return out
+
+
 def layer_gemms(qlayer: dict, acts: dict[int, torch.Tensor], act_importance: dict[str, torch.Tensor],
                 weight_scales: dict | None = None, side_streams: list | None = None, prepared: dict | None = None):
     """y = x @ W.T for every matrix of the layer with NVFP4 operands; activations quantized with the unweighted sweep
@@ -220,9 +248,16 @@ def run(n_layers: int, token_batches: list[int], seed: int = 0, use_graph: bool 
         gen.manual_seed(seed + 1000 + tokens)
         acts = {k: torch.normal(0.0, 1.0, size=(tokens, k), generator=gen, device=dev, dtype=torch.bfloat16)
                 for k in calib}
+        grouped = tokens <= GROUPED_MAX_TOKENS
+
+        def one_layer(q, ws, pw):
+            if grouped:
+                return layer_gemms_grouped(q, acts, ws, pw)
+            return layer_gemms(q, acts, {}, ws, side, pw)
+
         note(f"tokens {tokens}: eager layer")
         for q, ws, pw in zip(qlayers[:1], wscales, prepared):
-            layer_gemms(q, acts, {}, ws, side, pw)
+            one_layer(q, ws, pw)
         sync()
         graph = None
         if use_graph and qlayers:
@@ -231,7 +266,7 @@ def run(n_layers: int, token_batches: list[int], seed: int = 0, use_graph: bool 
             graph = torch.cuda.CUDAGraph()
             with torch.cuda.graph(graph):
                 for q, ws, pw in zip(qlayers, wscales, prepared):
-                    layer_gemms(q, acts, {}, ws, side, pw)
+                    one_layer(q, ws, pw)
             note(f"tokens {tokens}: first replay")
             graph.replay()
             sync()
@@ -241,13 +276,14 @@ def run(n_layers: int, token_batches: list[int], seed: int = 0, use_graph: bool 
             graph.replay()
         else:
             for q, ws, pw in zip(qlayers, wscales, prepared):
-                layer_gemms(q, acts, {}, ws, side, pw)
+                one_layer(q, ws, pw)
         e1.record()
         sync()
         ms = max_ms(e0.elapsed_time(e1))
         flops = 2.0 * tokens * weights_per_layer() * n_layers
         result["gemm"].append({"tokens": tokens, "ms_all_layers": ms, "tflops": flops / (ms * 1e-3) / 1e12,
-                               "cuda_graph": graph is not None, "streams": n_streams,
+                               "cuda_graph": graph is not None, "streams": 1 if grouped else n_streams,
+                               "launches": "grouped (q+k+v, o, gate+up, down), one stream" if grouped else "one per matrix",
                                "includes": "activation global scale + quantization + 7 GEMMs per layer"})
     if own_group:
         dist.destroy_process_group()

@@ -176,3 +176,14 @@ def test_gemm_prepare_rejects_bad_arguments_and_release_is_safe(L):
     bogus = (ctypes.c_uint32 * 64)()
     assert L.nvfp4_gemm_launch_prepared(ctypes.addressof(bogus), P, P, P, P, 16, None, 0, None) == -3   # not a handle
     assert L.nvfp4_gemm_set_wait_limit_ns(1) == -5 and L.nvfp4_quant_fused_set_wait_limit_ns(1) == -5
+    # grouped launch: count, NULL arrays, NULL entries and things that are not handles are refused before any GPU call
+    one = (ctypes.c_void_p * 1)(ctypes.addressof(bogus))
+    ptr = (ctypes.c_void_p * 1)(P)
+    null = (ctypes.c_void_p * 1)(None)
+    assert L.nvfp4_gemm_launch_grouped(None, 0, P, P, None, None, None, 16, None) == 0
+    assert L.nvfp4_gemm_launch_grouped(one, -1, P, P, None, ptr, ptr, 16, None) == -5
+    assert L.nvfp4_gemm_launch_grouped(one, 65, P, P, None, ptr, ptr, 16, None) == -5
+    assert L.nvfp4_gemm_launch_grouped(None, 1, P, P, None, ptr, ptr, 16, None) == -1
+    assert L.nvfp4_gemm_launch_grouped(null, 1, P, P, None, ptr, ptr, 16, None) == -1
+    assert L.nvfp4_gemm_launch_grouped(one, 1, P, P, None, null, ptr, 16, None) == -1
+    assert L.nvfp4_gemm_launch_grouped(one, 1, P, P, None, ptr, ptr, 16, None) == -3

@@ -209,6 +209,13 @@ def test_llama_stack_layer_shapes(cuda_lib, oracle):
     outs_side = LS.layer_gemms(q, acts, {}, None, side)
     torch.cuda.synchronize()
     assert all(torch.equal(outs[name], outs_side[name]) for name in outs)
+    # and as grouped launches (q+k+v, o, gate+up, down) with the output scales formed inside the kernel: the K ranges
+    # per tile are chosen from a group's total tile count, so sums may differ in the last fp32 bit before the bf16 store
+    outs_grouped = LS.layer_gemms_grouped(q, acts, LS.stack_weight_scales(q), LS.prepare_layer(q))
+    torch.cuda.synchronize()
+    for name, want in outs.items():
+        tol_g = torch.maximum(want.float().abs() * 2.0 ** -7, want.float().abs().max() * 2.0 ** -16)
+        assert bool(((outs_grouped[name].float() - want.float()).abs() <= tol_g).all()), name
     for name in ("k", "down", "gate"):
         n, k = LS.LAYER_SHAPES[name]
         codes, scales, gs_w = q[name]
@@ -394,16 +401,16 @@ def test_saved_quantized_weights_load_on_the_device_and_give_the_same_gemm_bits(
 
 
 def test_llama_stack_run_end_to_end(cuda_lib):
-    """The stack driver itself on a few layers: quantization phase, then the GEMM phase as one CUDA graph with the
-    GEMMs of a layer on four streams, at a decode batch and at 256 tokens (where tile and CTA-pair kernels of different
-    widths run at the same time)."""
+    """The stack driver itself on a few layers: quantization phase, then the GEMM phase as one CUDA graph: at a decode
+    batch grouped launches chained on one stream, at 256 tokens the GEMMs of a layer on four streams (where tile and
+    CTA-pair kernels of different widths run at the same time)."""
     from nvfp4quant_test_b200 import llama_stack as LS
 
     res = LS.run(4, [16, 256])
     assert res["layers"] == 4 and res["quantize_ms"] > 0 and res["quantize_gweights_per_s"] > 10
     assert [g["tokens"] for g in res["gemm"]] == [16, 256]
     for g in res["gemm"]:
-        assert g["cuda_graph"] and g["streams"] == 4 and 0.0 < g["ms_all_layers"] < 50.0
+        assert g["cuda_graph"] and g["streams"] == (1 if g["tokens"] <= 128 else 4) and 0.0 < g["ms_all_layers"] < 50.0
     from nvfp4quant_test_b200.kernels.kernel_gemm import gemm_last_status
 
     assert gemm_last_status() == 0
@@ -440,3 +447,141 @@ def test_prepared_weight_gives_the_same_bits_on_every_kernel_path(cuda_lib):
     pw.close()                                                             # idempotent
     with pytest.raises(ValueError):
         K.nvfp4_scaled_mm_prepared(a, sa, alpha, pw)
+
+
+@pytest.mark.parametrize("M", [1, 16, 33, 100, 256])
+def test_grouped_gemm_equals_one_by_one_calls(cuda_lib, M):
+    """One activation against a group of prepared weights of different N (ragged last tiles included), alphas
+    multiplied inside the kernel: with one K range per tile every output equals the one-by-one prepared call bit for
+    bit (decode-sized M: one launch for the group; M = 256: the per-weight fallback), with the default K ranges it
+    stays within one bf16 ulp; more than 8 weights are cut into several launches."""
+    import nvfp4quant_test_b200.kernels as K
+    from nvfp4quant_test_b200.kernels.kernel_gemm import gemm_last_status
+
+    g = torch.Generator(device="cuda")
+    g.manual_seed(100 + M)
+    k = 1024
+    ns = [512, 136, 128, 1000, 8, 256, 384, 64, 192, 2048]          # ten weights: two launches at decode sizes
+    ws, sws, pws, alphas = [], [], [], []
+    for n in ns:
+        w = torch.randint(0, 256, (n, k // 2), dtype=torch.uint8, device="cuda", generator=g)
+        sw = torch.randint(0x28, 0x48, ((n + 127) // 128 * 128, k // 16), dtype=torch.uint8, device="cuda", generator=g)
+        ws.append(w), sws.append(sw), pws.append(K.PreparedWeight(w, sw))
+        alphas.append(torch.rand(1, device="cuda", generator=g) + 0.5)
+    a = torch.randint(0, 256, (M, k // 2), dtype=torch.uint8, device="cuda", generator=g)
+    sa = torch.randint(0x28, 0x48, ((M + 127) // 128 * 128, k // 16), dtype=torch.uint8, device="cuda", generator=g)
+    alpha_a = torch.rand(1, device="cuda", generator=g) + 0.25
+    try:
+        for ranks in (1, 0):
+            if M <= 128:
+                assert cuda_lib.nvfp4_gemm_force_path(5) == 0 and cuda_lib.nvfp4_gemm_tune(ranks, -1) == 0
+            single = [K.nvfp4_scaled_mm_prepared(a, sa, al * alpha_a, pw) for al, pw in zip(alphas, pws)]
+            outs = [torch.full((M, n), float("nan"), dtype=torch.bfloat16, device="cuda") for n in ns]
+            got = K.nvfp4_scaled_mm_grouped(a, sa, alpha_a, pws, alphas, outs)
+            plain = K.nvfp4_scaled_mm_grouped(a, sa, None, pws[:3], [al * alpha_a for al in alphas[:3]])
+            assert gemm_last_status() == 0
+            for i, (x, y) in enumerate(zip(got, single)):
+                assert not torch.isnan(x).any()
+                if ranks == 1 or M > 128:
+                    assert torch.equal(x, y), (M, ranks, i)
+                else:
+                    tol = torch.maximum(y.float().abs() * 2.0 ** -7, y.float().abs().max() * 2.0 ** -16)
+                    assert bool(((x.float() - y.float()).abs() <= tol).all()), (M, ranks, i)
+            for x, y in zip(plain, got[:3]):
+                if ranks == 1 or M > 128:
+                    assert torch.equal(x, y)
+    finally:
+        cuda_lib.nvfp4_gemm_force_path(0)
+        cuda_lib.nvfp4_gemm_tune(0, -1)
+    with pytest.raises(ValueError):
+        K.nvfp4_scaled_mm_grouped(a, sa, alpha_a, pws, alphas[:-1])
+    assert K.nvfp4_scaled_mm_grouped(a, sa, alpha_a, [], []) == []
+
+
+def test_quantize_then_grouped_gemm_chain_in_a_cuda_graph(cuda_lib, oracle):
+    """global scale -> quantizer -> grouped GEMM -> global scale -> quantizer -> GEMM on one stream, every kernel a
+    programmatic dependent launch, recorded into a CUDA graph and replayed on fresh inputs: each replay must equal the
+    same chain launched with plain stream order (the switch of nvfp4_gemm_tune_pdl), bit for bit."""
+    import nvfp4quant_test_b200.kernels as K
+    from nvfp4quant_test_b200 import helper as H
+    from nvfp4quant_test_b200.kernels.kernel_gemm import gemm_last_status
+
+    g = torch.Generator(device="cuda")
+    g.manual_seed(5)
+    k, tokens = 2048, 8
+    pws, gws = [], []
+    keep = []
+    for n in (2048, 256, 256):
+        w = torch.normal(0.0, 0.02, size=(n, k), generator=g, device="cuda", dtype=torch.bfloat16)
+        gs, gi = H.get_nvfp4_global_scale(w, H.FP8_E4M3_MAX_4OVER6)
+        c, s = K.scalesweep_mse_nvfp4_quant_impl(w, gi)
+        keep.append((c, s))
+        pws.append(K.PreparedWeight(c, s)), gws.append(gs.reshape(1).float())
+    w2 = torch.normal(0.0, 0.02, size=(512, 2048), generator=g, device="cuda", dtype=torch.bfloat16)
+    gs2, gi2 = H.get_nvfp4_global_scale(w2, H.FP8_E4M3_MAX_4OVER6)
+    c2, s2 = K.scalesweep_mse_nvfp4_quant_impl(w2, gi2)
+    pw2, gw2 = K.PreparedWeight(c2, s2), gs2.reshape(1).float()
+    x = torch.empty((tokens, k), dtype=torch.bfloat16, device="cuda")
+
+    def chain():
+        gx, gxi = H.get_nvfp4_global_scale(x, H.FP8_E4M3_MAX_4OVER6)
+        qa, sa = K.scalesweep_mse_nvfp4_quant_impl(x, gxi)
+        q, kk, v = K.nvfp4_scaled_mm_grouped(qa, sa, gx.reshape(1), pws, gws)
+        gq, gqi = H.get_nvfp4_global_scale(q, H.FP8_E4M3_MAX_4OVER6)
+        qq, sq = K.scalesweep_mse_nvfp4_quant_impl(q, gqi)
+        (o,) = K.nvfp4_scaled_mm_grouped(qq, sq, gq.reshape(1), [pw2], [gw2])
+        return q, kk, v, o
+
+    x.normal_(generator=g)
+    chain()
+    torch.cuda.synchronize()
+    graph = torch.cuda.CUDAGraph()
+    with torch.cuda.graph(graph):
+        outs = chain()
+    for trial in range(3):
+        x.normal_(generator=g)
+        graph.replay()
+        got = [t.clone() for t in outs]
+        try:
+            assert cuda_lib.nvfp4_gemm_tune_pdl(0) == 0
+            want = chain()
+        finally:
+            cuda_lib.nvfp4_gemm_tune_pdl(1)
+        torch.cuda.synchronize()
+        for a_, b_ in zip(got, want):
+            assert torch.equal(a_, b_), trial
+        assert float(got[3].float().abs().max()) > 0.0
+    assert gemm_last_status() == 0
+
+
+def test_gemm_right_behind_the_quantizer_of_its_weight(cuda_lib):
+    """Drop-in use as the reference's benchmark chains it: quantize the weight, then multiply, back to back on one
+    stream with raw pointers.  The GEMM is a programmatic dependent launch, so it may be scheduled while the quantizer
+    is still running; it must not read the weight before that kernel is done.  The code buffer holds garbage before
+    every round, so an early read changes the output."""
+    import nvfp4quant_test_b200.kernels as K
+    from nvfp4quant_test_b200 import helper as H
+
+    g = torch.Generator(device="cuda")
+    g.manual_seed(3)
+    n, k, m = 4096, 4096, 16
+    w = torch.normal(0.0, 1.0, size=(n, k), generator=g, device="cuda", dtype=torch.bfloat16)
+    x = torch.normal(0.0, 1.0, size=(m, k), generator=g, device="cuda", dtype=torch.bfloat16)
+    gw, gwi = H.get_nvfp4_global_scale(w, H.FP8_E4M3_MAX_4OVER6)
+    gx, gxi = H.get_nvfp4_global_scale(x, H.FP8_E4M3_MAX_4OVER6)
+    qx, sx = K.scalesweep_mse_nvfp4_quant_impl(x, gxi)
+    alpha = (gw * gx).reshape(1).float()
+    codes, scales = K.create_fp4_output_tensors(n, k, w.device, True)
+    K.scalesweep_mse_nvfp4_quant_out(w, gwi, True, output=codes, output_scale=scales)
+    torch.cuda.synchronize()
+    want = K.nvfp4_scaled_mm(qx, codes, sx, scales.view(torch.float8_e4m3fn), alpha, torch.bfloat16)
+    torch.cuda.synchronize()
+    for m_tokens in (16, 256):
+        xa = x if m_tokens == 16 else x.repeat(16, 1)
+        qa, sa = K.scalesweep_mse_nvfp4_quant_impl(xa, gxi)
+        for _ in range(10):
+            codes.fill_(0x77)
+            scales.view(torch.uint8).fill_(0x38)
+            K.scalesweep_mse_nvfp4_quant_out(w, gwi, True, output=codes, output_scale=scales)
+            got = K.nvfp4_scaled_mm(qa, codes, sa, scales.view(torch.float8_e4m3fn), alpha, torch.bfloat16)
+            assert torch.equal(got[:16], want)
