@@ -42,16 +42,18 @@ __global__ void __launch_bounds__(kGsThreads) global_scale_kernel(const void* x,
     };
     int64_t i = static_cast<int64_t>(blockIdx.x) * kGsThreads + threadIdx.x;
     // four independent 16-byte loads in flight per thread: with one, a resident grid holds too few bytes in
-    // flight to cover the HBM latency
-    for (; i + 3 * stride < nvec; i += 4 * stride) {
-        const uint4 q0 = __ldg(xv + i), q1 = __ldg(xv + i + stride), q2 = __ldg(xv + i + 2 * stride),
-                    q3 = __ldg(xv + i + 3 * stride);
+    // flight to cover the HBM latency.  Slots past the end read as zeros, which never raise a maximum of magnitudes.
+    const uint4 zero = make_uint4(0u, 0u, 0u, 0u);
+    for (; i < nvec; i += 4 * stride) {
+        const uint4 q0 = __ldg(xv + i);
+        const uint4 q1 = i + stride < nvec ? __ldg(xv + i + stride) : zero;
+        const uint4 q2 = i + 2 * stride < nvec ? __ldg(xv + i + 2 * stride) : zero;
+        const uint4 q3 = i + 3 * stride < nvec ? __ldg(xv + i + 3 * stride) : zero;
         fold(q0);
         fold(q1);
         fold(q2);
         fold(q3);
     }
-    for (; i < nvec; i += stride) fold(__ldg(xv + i));
     // ragged tail (numel not a multiple of the vector width): first threads of block 0
     if (blockIdx.x == 0) {
         const int64_t t = nvec * kPerVec + threadIdx.x;
@@ -76,13 +78,22 @@ __global__ void __launch_bounds__(kGsThreads) global_scale_kernel(const void* x,
     if (threadIdx.x == 0) {
         uint32_t b = 0;
         for (int i = 0; i < kGsThreads / 32; ++i) b = max(b, warp_max[i]);
-        atomicMax(&scratch[0], b);
-        __threadfence();
-        const uint32_t ticket = atomicAdd(&scratch[1], 1u);
-        if (ticket == gridDim.x - 1) {
+        // a one-block grid (activations of a few tokens) has its maximum already: no trip through the scratch words,
+        // whose three dependent atomics would cost more than the rest of the kernel
+        bool last = gridDim.x == 1;
+        uint32_t mx = b;
+        if (!last) {
+            atomicMax(&scratch[0], b);
             __threadfence();
-            const uint32_t mx = atomicExch(&scratch[0], 0u);
-            scratch[1] = 0u;
+            const uint32_t ticket = atomicAdd(&scratch[1], 1u);
+            last = ticket == gridDim.x - 1;
+            if (last) {
+                __threadfence();
+                mx = atomicExch(&scratch[0], 0u);
+                scratch[1] = 0u;
+            }
+        }
+        if (last) {
             const float amax = __uint_as_float(mx);
             const float inv_den = __fdiv_rn(1.0f, __fmul_rn(6.0f, fp8_max));
             const float gs = __fmul_rn(amax, inv_den);
@@ -106,7 +117,8 @@ extern "C" int nvfp4_global_scale_launch(const void* x, int x_dtype, int64_t num
         return NVFP4_ERR_MISALIGNED;
     const int per_vec = (x_dtype == NVFP4_DT_F32) ? 4 : 8;
     const int64_t nvec = numel / per_vec;
-    int64_t blocks = (nvec + kGsThreads - 1) / kGsThreads;
+    // up to four 16-byte loads per thread (all in flight at once) stay in one block, which needs no atomics
+    int64_t blocks = nvec <= 4 * kGsThreads ? 1 : (nvec + kGsThreads - 1) / kGsThreads;
     // a few resident blocks per SM is enough to keep HBM busy; more only adds atomics
     // measured at 8192 x 8192 bf16: 1 CTA per SM 29.0 us, 2: 25.4, 3: 25.0, 4: 25.2-26.5, 8: 27.5, 16: 29.2
     int dev = 0, sms = 148;
