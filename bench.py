@@ -205,19 +205,24 @@ def strong_scaling(dev, rank, world, torch, dist, max_over_ranks, barrier):
     del w_full
     codes, scales = K.create_fp4_output_tensors(b - a, DIM, dev, True)
 
+    from nvfp4quant_test_b200.sharding import gather_importance_and_scale, importance_shards
+
+    c0, c1 = importance_shards(DIM, world)[rank]
+
     def step2(_i):
-        imp = H.channel_square_norm(act)
-        gs, _ = H.get_nvfp4_global_scale(w, 256.0)
-        gs = gs.reshape(1).clone()
-        if world > 1:
-            dist.all_reduce(gs, op=dist.ReduceOp.MAX)
-        K.scalesweep_weighted_mse_nvfp4_quant_out(w, imp, gs.reciprocal(), True, output=codes, output_scale=scales)
+        # the importance reduction shards by columns (each rank reads 1 / world of the batch), the weight by rows; one
+        # all-gather carries the importance slices and the local scales
+        imp_part = H.channel_square_norm(act[:, c0:c1])
+        gs_local, _ = H.get_nvfp4_global_scale(w, 256.0)
+        imp, _gs, gs_inv = gather_importance_and_scale(imp_part, gs_local, DIM)
+        K.scalesweep_weighted_mse_nvfp4_quant_out(w, imp, gs_inv, True, output=codes, output_scale=scales)
 
     barrier()
     ms = max_over_ranks(B.time_launches(step2, 20))
     out["config2_weighted_weight_quant"] = {
         "ms": ms, "rows_per_gpu": b - a, "shape": [ROWS, DIM], "gweights_per_s": ROWS * DIM / (ms * 1e-3) / 1e9,
-        "includes": "importance reduction over the [4096, 8192] batch + shard amax + 4-byte MAX all-reduce + weighted sweep"}
+        "includes": "importance reduction over the [4096, 8192] batch (columns / N per GPU) + shard amax + one all-gather "
+                    "of the importance slices and local scales + weighted sweep"}
     del w, act, codes, scales
     # -- GEMM: M = 2048 activations against N = 28672 weight rows, N / world rows per GPU, K = 8192
     M, N, Kd = 2048, 28672, 8192

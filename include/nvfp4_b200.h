@@ -123,6 +123,12 @@ int nvfp4_quant_fused_last_status(void* stream, uint32_t* status);
  * driver computes it with torch, no dedicated kernel).  Fixed summation order: reproducible run to run.
  */
 int nvfp4_channel_sqnorm_launch(const void* x, int x_dtype, int64_t m, int64_t n, float* out, void* stream);
+/* The same for a column slice of a wider batch: x points at the slice's first column, `ld` (>= n, % 4 == 0) is the
+ * row pitch in elements.  Columns are independent and each sum runs over the rows in the same fixed order, so the
+ * slices of several GPUs concatenate to the bits one GPU computes for the whole batch (multi-GPU weight quantization
+ * shards the importance reduction this way; no counterpart in the reference, which runs on one GPU). */
+int nvfp4_channel_sqnorm_launch_strided(const void* x, int x_dtype, int64_t m, int64_t n, int64_t ld, float* out,
+                                        void* stream);
 
 /*
  * The same result as nvfp4_global_scale_launch for callers that cannot allocate device memory

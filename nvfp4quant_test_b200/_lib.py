@@ -18,7 +18,7 @@ ERR_TOO_LARGE = -8
 EXPORTS = (
     "nvfp4_quant_launch", "nvfp4_quant_launch_impl", "nvfp4_quant_fused_launch", "nvfp4_quant_fused_last_status",
     "nvfp4_global_scale_launch", "nvfp4_global_scale_launch_static", "nvfp4_global_scale_static_max_bytes",
-    "nvfp4_channel_sqnorm_launch", "nvfp4_gemm_peak_probe", "nvfp4_gemm_set_wait_limit_ns", "nvfp4_quant_fused_set_wait_limit_ns",
+    "nvfp4_channel_sqnorm_launch", "nvfp4_channel_sqnorm_launch_strided", "nvfp4_gemm_peak_probe", "nvfp4_gemm_set_wait_limit_ns", "nvfp4_quant_fused_set_wait_limit_ns",
     "nvfp4_gemm_launch", "nvfp4_gemm_workspace_bytes", "nvfp4_gemm_prepare", "nvfp4_gemm_launch_prepared", "nvfp4_gemm_launch_grouped", "nvfp4_gemm_release", "nvfp4_gemm_last_status", "nvfp4_gemm_force_path", "nvfp4_gemm_tune", "nvfp4_gemm_tune_raster", "nvfp4_gemm_tune_pdl", "nvfp4_gemm_plan",
     "nvfp4_status_string", "nvfp4_abi_version",
 )
@@ -65,6 +65,8 @@ def lib() -> ctypes.CDLL:
         L.nvfp4_quant_fused_set_wait_limit_ns.argtypes = [ctypes.c_uint64]
         L.nvfp4_channel_sqnorm_launch.restype = ci
         L.nvfp4_channel_sqnorm_launch.argtypes = [vp, ci, i64, i64, vp, vp]
+        L.nvfp4_channel_sqnorm_launch_strided.restype = ci
+        L.nvfp4_channel_sqnorm_launch_strided.argtypes = [vp, ci, i64, i64, i64, vp, vp]
         L.nvfp4_gemm_launch.restype = ci
         L.nvfp4_gemm_launch.argtypes = [vp, vp, vp, vp, vp, vp, i64, i64, i64, vp, ctypes.c_size_t, vp]
         L.nvfp4_gemm_prepare.restype = ci

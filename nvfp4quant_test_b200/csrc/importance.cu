@@ -39,7 +39,8 @@ __device__ __forceinline__ void load4(const void* x, int64_t elem, float v[4]) {
 }
 
 template <int DT>
-__global__ void __launch_bounds__(kSqThreads) channel_sqnorm_kernel(const void* x, int64_t m, int64_t n, float* out) {
+__global__ void __launch_bounds__(kSqThreads) channel_sqnorm_kernel(const void* x, int64_t m, int64_t n, int64_t ld,
+                                                                    float* out) {
     const int lane = threadIdx.x % kSqLanes, rg = threadIdx.x / kSqLanes;
     const int64_t col = static_cast<int64_t>(blockIdx.x) * kSqCols + lane * 4;
     float acc[4] = {0.0f, 0.0f, 0.0f, 0.0f};
@@ -49,7 +50,7 @@ __global__ void __launch_bounds__(kSqThreads) channel_sqnorm_kernel(const void* 
         for (; r + (kSqUnroll - 1) * kSqGroups < m; r += kSqUnroll * kSqGroups) {
             float v[kSqUnroll][4];
 #pragma unroll
-            for (int u = 0; u < kSqUnroll; ++u) load4<DT>(x, (r + u * kSqGroups) * n + col, v[u]);
+            for (int u = 0; u < kSqUnroll; ++u) load4<DT>(x, (r + u * kSqGroups) * ld + col, v[u]);
 #pragma unroll
             for (int u = 0; u < kSqUnroll; ++u)
 #pragma unroll
@@ -57,7 +58,7 @@ __global__ void __launch_bounds__(kSqThreads) channel_sqnorm_kernel(const void* 
         }
         for (; r < m; r += kSqGroups) {
             float v[4];
-            load4<DT>(x, r * n + col, v);
+            load4<DT>(x, r * ld + col, v);
 #pragma unroll
             for (int k = 0; k < 4; ++k) acc[k] = __fmaf_rn(v[k], v[k], acc[k]);
         }
@@ -83,21 +84,28 @@ __global__ void __launch_bounds__(kSqThreads) channel_sqnorm_kernel(const void* 
 }  // namespace
 }  // namespace nvfp4
 
-extern "C" int nvfp4_channel_sqnorm_launch(const void* x, int x_dtype, int64_t m, int64_t n, float* out, void* stream) {
+extern "C" int nvfp4_channel_sqnorm_launch_strided(const void* x, int x_dtype, int64_t m, int64_t n, int64_t ld, float* out,
+                                                   void* stream) {
     using namespace nvfp4;
     if (x_dtype < NVFP4_DT_BF16 || x_dtype > NVFP4_DT_F32) return NVFP4_ERR_BAD_ENUM;
-    if (m < 0 || n < 0 || (n % 4) != 0) return NVFP4_ERR_BAD_SHAPE;
+    if (m < 0 || n < 0 || (n % 4) != 0 || ld < n) return NVFP4_ERR_BAD_SHAPE;
     if (n == 0) return NVFP4_OK;
     if (!out || (!x && m > 0)) return NVFP4_ERR_NULL_POINTER;
+    // a lane reads 4 consecutive elements (8 or 16 bytes) of a row: the row pitch keeps those pieces aligned
+    if ((ld % 4) != 0) return NVFP4_ERR_BAD_SHAPE;
     if ((reinterpret_cast<uintptr_t>(x) & 15) || (reinterpret_cast<uintptr_t>(out) & 3)) return NVFP4_ERR_MISALIGNED;
     const int64_t blocks = (n + kSqCols - 1) / kSqCols;
     if (blocks > 0x7fffffffLL) return NVFP4_ERR_TOO_LARGE;
     cudaStream_t s = static_cast<cudaStream_t>(stream);
     const unsigned g = static_cast<unsigned>(blocks);
     switch (x_dtype) {
-        case NVFP4_DT_BF16: channel_sqnorm_kernel<NVFP4_DT_BF16><<<g, kSqThreads, 0, s>>>(x, m, n, out); break;
-        case NVFP4_DT_F16: channel_sqnorm_kernel<NVFP4_DT_F16><<<g, kSqThreads, 0, s>>>(x, m, n, out); break;
-        default: channel_sqnorm_kernel<NVFP4_DT_F32><<<g, kSqThreads, 0, s>>>(x, m, n, out); break;
+        case NVFP4_DT_BF16: channel_sqnorm_kernel<NVFP4_DT_BF16><<<g, kSqThreads, 0, s>>>(x, m, n, ld, out); break;
+        case NVFP4_DT_F16: channel_sqnorm_kernel<NVFP4_DT_F16><<<g, kSqThreads, 0, s>>>(x, m, n, ld, out); break;
+        default: channel_sqnorm_kernel<NVFP4_DT_F32><<<g, kSqThreads, 0, s>>>(x, m, n, ld, out); break;
     }
     return static_cast<int>(cudaGetLastError());
+}
+
+extern "C" int nvfp4_channel_sqnorm_launch(const void* x, int x_dtype, int64_t m, int64_t n, float* out, void* stream) {
+    return nvfp4_channel_sqnorm_launch_strided(x, x_dtype, m, n, n, out, stream);
 }

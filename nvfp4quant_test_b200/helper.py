@@ -45,13 +45,18 @@ def channel_square_norm(x: torch.Tensor) -> torch.Tensor:
         raise ValueError("x must be a 2D CUDA tensor")
     if x.shape[1] % 4:
         raise ValueError("x.shape[1] must be divisible by 4")
-    if not x.is_contiguous():
+    # a column slice of a wider batch (x_full[:, c0:c1]) is read in place through its row pitch
+    in_place = x.shape[0] <= 1 or (x.stride(1) == 1 and x.stride(0) >= x.shape[1] and x.stride(0) % 4 == 0)
+    if not in_place or x.data_ptr() & 15:
         x = x.contiguous()
+        if x.data_ptr() & 15:
+            x = x.clone()
+    ld = x.stride(0) if x.shape[0] > 1 else x.shape[1]
     out = torch.empty((1, x.shape[1]), dtype=torch.float32, device=x.device)
     with _lib.device_guard(x.device):
-        st = _lib.lib().nvfp4_channel_sqnorm_launch(x.data_ptr(), _lib.dtype_code(x.dtype), x.shape[0], x.shape[1],
-                                                    out.data_ptr(), _lib.current_stream_ptr(x.device))
-    _lib.check(st, "nvfp4_channel_sqnorm_launch")
+        st = _lib.lib().nvfp4_channel_sqnorm_launch_strided(x.data_ptr(), _lib.dtype_code(x.dtype), x.shape[0], x.shape[1],
+                                                            ld, out.data_ptr(), _lib.current_stream_ptr(x.device))
+    _lib.check(st, "nvfp4_channel_sqnorm_launch_strided")
     return out
 
 

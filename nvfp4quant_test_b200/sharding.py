@@ -7,6 +7,10 @@ the tiled scale layout is `k_pad * 128` contiguous bytes, so each rank's scales 
 contiguous slab of the global scale buffer and the shards concatenate bit for bit into
 what a single GPU would have produced.  The only optional communication is a 4-byte MAX
 all-reduce when the global amax has to be taken over sharded data, and a final gather.
+When the importance vector of a weight is itself computed on the fly (channel square norms
+of an activation batch), that reduction shards by COLUMNS - columns are independent, so the
+slices concatenate to the single-GPU bits - and one small all-gather carries both the slices
+and every rank's local scale.
 """
 from __future__ import annotations
 
@@ -97,3 +101,45 @@ def gather_rows(codes: torch.Tensor, scales: torch.Tensor, rows: int, blocks: in
 def column_shards(n: int, world: int, align: int = GROUP_ROWS) -> list[tuple[int, int]]:
     """N-dimension shards for the GEMM: weight rows [start, stop) per rank (same rule as row_shards)."""
     return row_shards(n, world, align)
+
+
+IMPORTANCE_ALIGN = 16   # columns per CTA of the channel-square-norm kernel
+
+
+def importance_shards(n: int, world: int) -> list[tuple[int, int]]:
+    """Column ranges [start, stop) of the importance reduction per rank (starts at multiples of 16 columns)."""
+    return row_shards(n, world, IMPORTANCE_ALIGN)
+
+
+def gather_importance_and_scale(imp_part: torch.Tensor, gs_local: torch.Tensor, n: int, group=None):
+    """(importance [1, n], global_scale, global_scale_inv) for a row-sharded weight whose importance is reduced on the
+    fly: `imp_part` is this rank's slice importance_shards(n, world)[rank] of the channel square norms (fp32), and
+    `gs_local` the global scale of this rank's weight rows (amax_local / (6 * fp8_max), as get_nvfp4_global_scale
+    returns it).  ONE all-gather moves both; the tensor-wide scale is the maximum of the local ones (multiplying by a
+    positive constant is monotone), its reciprocal one fp32 division, as on a single GPU."""
+    imp_part = imp_part.reshape(-1).float()
+    gs_local = gs_local.detach().float().reshape(1)
+    world = dist.get_world_size(group) if dist.is_available() and dist.is_initialized() else 1
+    if world == 1:
+        if imp_part.numel() != n:
+            raise ValueError(f"expected {n} importance values, got {imp_part.numel()}")
+        gs = gs_local.reshape(())
+        return imp_part.reshape(1, n), gs, gs.reciprocal()
+    rank = dist.get_rank(group)
+    shards = importance_shards(n, world)
+    a, b = shards[rank]
+    if imp_part.numel() != b - a:
+        raise ValueError(f"rank {rank} expects {b - a} importance values, got {imp_part.numel()}")
+    width = max(d - c for c, d in shards)
+    mine = torch.zeros(width + 1, dtype=torch.float32, device=imp_part.device)
+    mine[: b - a] = imp_part
+    mine[width:] = gs_local
+    flat = torch.empty(world * (width + 1), dtype=torch.float32, device=imp_part.device)
+    dist.all_gather_into_tensor(flat, mine, group=group)
+    everything = flat.view(world, width + 1)
+    if all(d - c == width for c, d in shards):
+        imp = everything[:, :width].reshape(1, n)
+    else:
+        imp = torch.cat([everything[r, : d - c] for r, (c, d) in enumerate(shards)]).reshape(1, n)
+    gs = everything[:, width].max()
+    return imp.contiguous(), gs, gs.reciprocal()

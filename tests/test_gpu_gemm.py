@@ -174,6 +174,19 @@ def test_channel_square_norm_kernel(cuda_lib):
         assert got.shape == (1, shape[1]) and got.dtype == torch.float32
         assert torch.allclose(got.double(), want, rtol=2e-5, atol=0)
         assert torch.equal(got, H.channel_square_norm(x))       # fixed summation order
+        # column slices are read in place through the row pitch and concatenate to the same bits (how several GPUs
+        # share the reduction); a slice that starts off a 16-byte boundary is copied first, same bits again
+        if shape[1] >= 64:
+            cuts = [0, 16, 48, shape[1] // 2 // 16 * 16, shape[1]]
+            parts = [H.channel_square_norm(x[:, a:b]) for a, b in zip(cuts, cuts[1:]) if b > a]
+            assert torch.equal(torch.cat(parts, 1), got)
+            assert torch.equal(H.channel_square_norm(x[:, 4:36]), got[:, 4:36])
+    L = cuda_lib
+    x = torch.zeros((8, 64), dtype=torch.bfloat16, device="cuda")
+    out = torch.zeros(64, dtype=torch.float32, device="cuda")
+    assert L.nvfp4_channel_sqnorm_launch_strided(x.data_ptr(), 0, 8, 32, 16, out.data_ptr(), None) == -2    # ld < n
+    assert L.nvfp4_channel_sqnorm_launch_strided(x.data_ptr(), 0, 8, 32, 62, out.data_ptr(), None) == -2    # ld % 4
+    assert L.nvfp4_channel_sqnorm_launch_strided(x.data_ptr() + 8, 0, 8, 32, 64, out.data_ptr(), None) == -4
 
 
 def test_llama_stack_layer_shapes(cuda_lib, oracle):

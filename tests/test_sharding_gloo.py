@@ -77,3 +77,40 @@ def test_sharded_quantization_matches_single_rank(tmp_path, rows, cols):
     mp.spawn(_worker, args=(world, port, rows, cols, str(tmp_path)), nprocs=world, join=True)
     for r in range(world):
         assert (tmp_path / f"rank{r}.ok").read_text() == "1"
+
+
+def _imp_worker(rank, world, port, n, tmp):
+    sys.path.insert(0, str(ROOT))
+    os.environ["MASTER_ADDR"] = "127.0.0.1"
+    os.environ["MASTER_PORT"] = str(port)
+    dist.init_process_group("gloo", rank=rank, world_size=world)
+    try:
+        from nvfp4quant_test_b200 import sharding as S
+
+        g = torch.Generator().manual_seed(5)
+        full = torch.rand(n, generator=g) * 100.0
+        scales = torch.tensor([0.25, 0.75, 0.5][:world])
+        a, b = S.importance_shards(n, world)[rank]
+        imp, gs, gs_inv = S.gather_importance_and_scale(full[a:b].clone(), scales[rank], n)
+        ok = (imp.shape == (1, n) and torch.equal(imp.reshape(-1), full) and float(gs) == float(scales.max())
+              and float(gs_inv) == float(torch.tensor(1.0) / scales.max()))
+        try:
+            S.gather_importance_and_scale(full[a:b][:-1], scales[rank], n)
+            ok = False
+        except ValueError:
+            pass
+        pathlib.Path(tmp, f"rank{rank}.ok").write_text("1" if ok else "0")
+    finally:
+        dist.destroy_process_group()
+
+
+@pytest.mark.parametrize("world,n", [(2, 8192), (3, 208)])
+def test_sharded_importance_gathers_to_the_full_vector_and_the_max_scale(tmp_path, world, n):
+    from nvfp4quant_test_b200.sharding import importance_shards
+
+    sh = importance_shards(n, world)
+    assert sh[0][0] == 0 and sh[-1][1] == n and all(a % 16 == 0 or a == n for a, _ in sh)
+    port = 31500 + (os.getpid() % 2000) + world
+    mp.spawn(_imp_worker, args=(world, port, n, str(tmp_path)), nprocs=world, join=True)
+    for r in range(world):
+        assert (tmp_path / f"rank{r}.ok").read_text() == "1"
