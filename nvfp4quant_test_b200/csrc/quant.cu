@@ -40,6 +40,8 @@ constexpr int kThreads = 256;
 #endif
 // The two-dimensional-grid body has less index arithmetic alive and takes one more CTA per SM (40 registers, a few
 // bytes of spill outside the loop): 121.1 -> 118.5 us at 8192 x 8192; the flat body gets slower with the same bound.
+// Weighted sweep, two-dimensional grid, at 8192 x 8192: 5 CTAs (48 registers, spills) 223 us, 4 CTAs (64) 192 us,
+// 3 CTAs (80) 199 us, 2 CTAs (90, importance pairs kept in registers) 205 us.
 #ifndef NVFP4_QUANT_MIN_BLOCKS_2D
 #define NVFP4_QUANT_MIN_BLOCKS_2D 6
 #endif
@@ -199,11 +201,6 @@ __device__ __forceinline__ uint32_t sweep_paired(const float v[16], const float 
     uint64_t vp[8];  // (v[2p], v[2p+1])
 #pragma unroll
     for (int p = 0; p < 8; ++p) vp[p] = pack_f32x2(v[2 * p], v[2 * p + 1]);
-#ifdef NVFP4_W_HOIST
-    uint64_t ww[16];
-#pragma unroll
-    for (int j = 0; j < 16; ++j) ww[j] = WEIGHTED ? pack_f32x2(w[j], w[j]) : 0ull;
-#endif
     float best = __int_as_float(0x7f800000);
     uint32_t best_raw = 0;
     auto trip = [&](int i) {
@@ -231,13 +228,8 @@ __device__ __forceinline__ uint32_t sweep_paired(const float v[16], const float 
                 e2m1_diff_pair(mul_f32x2(vp[p], inv_a), a0, a1);
                 e2m1_diff_pair(mul_f32x2(vp[p], inv_b), b0, b1);
                 const uint64_t d0 = pack_f32x2(a0, b0), d1 = pack_f32x2(a1, b1);
-#ifdef NVFP4_W_HOIST
-                const uint64_t t = mul_f32x2(mul_f32x2(d0, d0), ww[2 * p]);
-                pe[p] = fma_f32x2(mul_f32x2(d1, d1), ww[2 * p + 1], t);
-#else
                 const uint64_t t = mul_f32x2(mul_f32x2(d0, d0), pack_f32x2(w[2 * p], w[2 * p]));
                 pe[p] = fma_f32x2(mul_f32x2(d1, d1), pack_f32x2(w[2 * p + 1], w[2 * p + 1]), t);
-#endif
             }
             tot2 = add_f32x2(add_f32x2(add_f32x2(pe[0], pe[1]), add_f32x2(pe[2], pe[3])),
                              add_f32x2(add_f32x2(pe[4], pe[5]), add_f32x2(pe[6], pe[7])));
