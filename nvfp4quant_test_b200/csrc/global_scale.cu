@@ -42,17 +42,25 @@ __global__ void __launch_bounds__(kGsThreads) global_scale_kernel(const void* x,
     };
     int64_t i = static_cast<int64_t>(blockIdx.x) * kGsThreads + threadIdx.x;
     // four independent 16-byte loads in flight per thread: with one, a resident grid holds too few bytes in
-    // flight to cover the HBM latency.  Slots past the end read as zeros, which never raise a maximum of magnitudes.
-    const uint4 zero = make_uint4(0u, 0u, 0u, 0u);
-    for (; i < nvec; i += 4 * stride) {
-        const uint4 q0 = __ldg(xv + i);
-        const uint4 q1 = i + stride < nvec ? __ldg(xv + i + stride) : zero;
-        const uint4 q2 = i + 2 * stride < nvec ? __ldg(xv + i + 2 * stride) : zero;
-        const uint4 q3 = i + 3 * stride < nvec ? __ldg(xv + i + 3 * stride) : zero;
+    // flight to cover the HBM latency
+    for (; i + 3 * stride < nvec; i += 4 * stride) {
+        const uint4 q0 = __ldg(xv + i), q1 = __ldg(xv + i + stride), q2 = __ldg(xv + i + 2 * stride),
+                    q3 = __ldg(xv + i + 3 * stride);
         fold(q0);
         fold(q1);
         fold(q2);
         fold(q3);
+    }
+    // the last, partial round the same way (a few-token activation is nothing but this round): slots past the end
+    // read as zeros, which never raise a maximum of magnitudes
+    if (i < nvec) {
+        const uint4 zero = make_uint4(0u, 0u, 0u, 0u);
+        const uint4 q0 = __ldg(xv + i);
+        const uint4 q1 = i + stride < nvec ? __ldg(xv + i + stride) : zero;
+        const uint4 q2 = i + 2 * stride < nvec ? __ldg(xv + i + 2 * stride) : zero;
+        fold(q0);
+        fold(q1);
+        fold(q2);
     }
     // ragged tail (numel not a multiple of the vector width): first threads of block 0
     if (blockIdx.x == 0) {
