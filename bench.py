@@ -205,16 +205,17 @@ def strong_scaling(dev, rank, world, torch, dist, max_over_ranks, barrier):
     del w_full
     codes, scales = K.create_fp4_output_tensors(b - a, DIM, dev, True)
 
-    from nvfp4quant_test_b200.sharding import gather_importance_and_scale, importance_shards
+    from nvfp4quant_test_b200.sharding import ImportanceGather
 
-    c0, c1 = importance_shards(DIM, world)[rank]
+    ig = ImportanceGather(DIM, dev)
+    c0, c1 = ig.columns
 
     def step2(_i):
-        # the importance reduction shards by columns (each rank reads 1 / world of the batch), the weight by rows; one
-        # all-gather carries the importance slices and the local scales
-        imp_part = H.channel_square_norm(act[:, c0:c1])
-        gs_local, _ = H.get_nvfp4_global_scale(w, 256.0)
-        imp, _gs, gs_inv = gather_importance_and_scale(imp_part, gs_local, DIM)
+        # the importance reduction shards by columns (each rank reads 1 / world of the batch), the weight by rows; both
+        # kernels write into the send buffer of one all-gather that carries the importance slices and the local scales
+        H.channel_square_norm(act[:, c0:c1], out=ig.imp_slot)
+        H.get_nvfp4_global_scale(w, 256.0, out=ig.scale_slot)
+        imp, _gs, gs_inv = ig.gather()
         K.scalesweep_weighted_mse_nvfp4_quant_out(w, imp, gs_inv, True, output=codes, output_scale=scales)
 
     barrier()

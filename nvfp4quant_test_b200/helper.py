@@ -17,10 +17,14 @@ FP8_E4M3_MAX_4OVER6 = 256.0
 _scratch = _lib.StreamScratch(2)
 
 
-def get_nvfp4_global_scale(x: torch.Tensor, FP8_MAX: float = FP8_E4M3_MAX_NVFP4):
-    """(global_scale, global_scale_inv) as 0-dim float32 CUDA tensors; amax(|x|)/(6*FP8_MAX) and its reciprocal."""
+def get_nvfp4_global_scale(x: torch.Tensor, FP8_MAX: float = FP8_E4M3_MAX_NVFP4, out: torch.Tensor | None = None):
+    """(global_scale, global_scale_inv) as 0-dim float32 CUDA tensors; amax(|x|)/(6*FP8_MAX) and its reciprocal.
+    `out` (optional): a contiguous float32 [2] CUDA tensor to write them into instead of a fresh one."""
     if not x.is_cuda:
         raise ValueError("x must be a CUDA tensor")
+    if out is not None and (out.dtype != torch.float32 or out.device != x.device or out.shape != (2,)
+                            or not out.is_contiguous()):
+        raise ValueError("out must be a contiguous float32 [2] tensor on x's device")
     if not x.is_contiguous():
         x = x.contiguous()
     if x.data_ptr() & 15:
@@ -30,7 +34,8 @@ def get_nvfp4_global_scale(x: torch.Tensor, FP8_MAX: float = FP8_E4M3_MAX_NVFP4)
         x = x.clone()
     stream = _lib.current_stream_ptr(x.device)
     scratch = _scratch.get(x.device, stream)
-    out = torch.empty(2, dtype=torch.float32, device=x.device)
+    if out is None:
+        out = torch.empty(2, dtype=torch.float32, device=x.device)
     with _lib.device_guard(x.device):
         st = _lib.lib().nvfp4_global_scale_launch(x.data_ptr(), _lib.dtype_code(x.dtype), x.numel(), float(FP8_MAX),
                                                   out.data_ptr(), scratch.data_ptr(), stream)
@@ -38,11 +43,15 @@ def get_nvfp4_global_scale(x: torch.Tensor, FP8_MAX: float = FP8_E4M3_MAX_NVFP4)
     return out[0], out[1]
 
 
-def channel_square_norm(x: torch.Tensor) -> torch.Tensor:
+def channel_square_norm(x: torch.Tensor, out: torch.Tensor | None = None) -> torch.Tensor:
     """fp32 [1, dim]: squared L2 norm of every input channel (column) of the 2-D batch x - the importance
-    vector for the operand x is multiplied with (README.md:11 of the reference)."""
+    vector for the operand x is multiplied with (README.md:11 of the reference).  `out` (optional): a contiguous
+    float32 [1, dim] CUDA tensor to write into."""
     if x.ndim != 2 or not x.is_cuda:
         raise ValueError("x must be a 2D CUDA tensor")
+    if out is not None and (out.dtype != torch.float32 or out.device != x.device or out.shape != (1, x.shape[1])
+                            or not out.is_contiguous()):
+        raise ValueError("out must be a contiguous float32 [1, dim] tensor on x's device")
     if x.shape[1] % 4:
         raise ValueError("x.shape[1] must be divisible by 4")
     # a column slice of a wider batch (x_full[:, c0:c1]) is read in place through its row pitch
@@ -52,7 +61,8 @@ def channel_square_norm(x: torch.Tensor) -> torch.Tensor:
         if x.data_ptr() & 15:
             x = x.clone()
     ld = x.stride(0) if x.shape[0] > 1 else x.shape[1]
-    out = torch.empty((1, x.shape[1]), dtype=torch.float32, device=x.device)
+    if out is None:
+        out = torch.empty((1, x.shape[1]), dtype=torch.float32, device=x.device)
     with _lib.device_guard(x.device):
         st = _lib.lib().nvfp4_channel_sqnorm_launch_strided(x.data_ptr(), _lib.dtype_code(x.dtype), x.shape[0], x.shape[1],
                                                             ld, out.data_ptr(), _lib.current_stream_ptr(x.device))

@@ -111,35 +111,54 @@ def importance_shards(n: int, world: int) -> list[tuple[int, int]]:
     return row_shards(n, world, IMPORTANCE_ALIGN)
 
 
+class ImportanceGather:
+    """Send / receive buffers for a row-sharded weight whose importance is reduced on the fly, allocated once.
+
+    Every rank reduces the channel square norms of its column slice `columns` of the activation batch straight into
+    `imp_slot` and the global scale of its weight rows, (amax_local / (6 * fp8_max), its reciprocal) as
+    get_nvfp4_global_scale computes them, straight into `scale_slot`; `gather()` then moves both with ONE all-gather
+    and returns (importance [1, n], global_scale, global_scale_inv) of the whole weight.  The tensor-wide scale is the
+    largest local one (multiplying the amax by a positive constant is monotone) and its reciprocal the smallest local
+    reciprocal (a correctly rounded division is monotone too), so both are the bits a single GPU computes."""
+
+    def __init__(self, n: int, device, group=None):
+        self.n, self.group = n, group
+        self.world = dist.get_world_size(group) if dist.is_available() and dist.is_initialized() else 1
+        self.rank = dist.get_rank(group) if self.world > 1 else 0
+        self.shards = importance_shards(n, self.world)
+        self.columns = self.shards[self.rank]
+        self.width = max(b - a for a, b in self.shards)
+        self._mine = torch.zeros(self.width + 2, dtype=torch.float32, device=device)
+        self._all = torch.empty(self.world * (self.width + 2), dtype=torch.float32, device=device)
+        a, b = self.columns
+        self.imp_slot = self._mine[: b - a].view(1, b - a)
+        self.scale_slot = self._mine[self.width:]
+        self._even = all(d - c == self.width for c, d in self.shards)
+
+    def gather(self):
+        w = self.width
+        if self.world == 1:
+            return self.imp_slot, self.scale_slot[0], self.scale_slot[1]
+        dist.all_gather_into_tensor(self._all, self._mine, group=self.group)
+        table = self._all.view(self.world, w + 2)
+        if self._even:
+            imp = table[:, :w].reshape(1, self.n)          # one copy: the slices sit w + 2 apart
+        else:
+            imp = torch.cat([table[r, : d - c] for r, (c, d) in enumerate(self.shards)]).reshape(1, self.n)
+        return imp, table[:, w].amax(), table[:, w + 1].amin()
+
+
 def gather_importance_and_scale(imp_part: torch.Tensor, gs_local: torch.Tensor, n: int, group=None):
-    """(importance [1, n], global_scale, global_scale_inv) for a row-sharded weight whose importance is reduced on the
-    fly: `imp_part` is this rank's slice importance_shards(n, world)[rank] of the channel square norms (fp32), and
-    `gs_local` the global scale of this rank's weight rows (amax_local / (6 * fp8_max), as get_nvfp4_global_scale
-    returns it).  ONE all-gather moves both; the tensor-wide scale is the maximum of the local ones (multiplying by a
-    positive constant is monotone), its reciprocal one fp32 division, as on a single GPU."""
-    imp_part = imp_part.reshape(-1).float()
-    gs_local = gs_local.detach().float().reshape(1)
-    world = dist.get_world_size(group) if dist.is_available() and dist.is_initialized() else 1
-    if world == 1:
-        if imp_part.numel() != n:
-            raise ValueError(f"expected {n} importance values, got {imp_part.numel()}")
-        gs = gs_local.reshape(())
-        return imp_part.reshape(1, n), gs, gs.reciprocal()
-    rank = dist.get_rank(group)
-    shards = importance_shards(n, world)
-    a, b = shards[rank]
-    if imp_part.numel() != b - a:
-        raise ValueError(f"rank {rank} expects {b - a} importance values, got {imp_part.numel()}")
-    width = max(d - c for c, d in shards)
-    mine = torch.zeros(width + 1, dtype=torch.float32, device=imp_part.device)
-    mine[: b - a] = imp_part
-    mine[width:] = gs_local
-    flat = torch.empty(world * (width + 1), dtype=torch.float32, device=imp_part.device)
-    dist.all_gather_into_tensor(flat, mine, group=group)
-    everything = flat.view(world, width + 1)
-    if all(d - c == width for c, d in shards):
-        imp = everything[:, :width].reshape(1, n)
-    else:
-        imp = torch.cat([everything[r, : d - c] for r, (c, d) in enumerate(shards)]).reshape(1, n)
-    gs = everything[:, width].max()
-    return imp.contiguous(), gs, gs.reciprocal()
+    """(importance [1, n], global_scale, global_scale_inv) from this rank's importance slice
+    importance_shards(n, world)[rank] and the global scale of its weight rows: ImportanceGather for callers that hold
+    the two as separate tensors (it copies them into the send buffer)."""
+    g = ImportanceGather(n, imp_part.device, group)
+    imp_part = imp_part.reshape(1, -1).float()
+    if imp_part.shape[1] != g.imp_slot.shape[1]:
+        raise ValueError(f"rank {g.rank} expects {g.imp_slot.shape[1]} importance values, got {imp_part.shape[1]}")
+    g.imp_slot.copy_(imp_part)
+    gs = gs_local.detach().float().reshape(1)
+    g.scale_slot[0:1].copy_(gs)
+    g.scale_slot[1:2].copy_(gs.reciprocal())
+    imp, gs_all, gs_inv = g.gather()
+    return imp.contiguous(), gs_all.reshape(()), gs_inv.reshape(())

@@ -1,5 +1,6 @@
 """GPU, two or more devices: the N-sharded GEMM (weight rows split over the ranks, one process per GPU over NCCL)
-gives, after a gather along N, the bits of the one-GPU GEMM.  Skipped when fewer than two GPUs are visible."""
+gives, after a gather along N, the bits of the one-GPU GEMM; row-sharded quantization with the importance reduced by
+column slices gives the bytes of one GPU.  Skipped when fewer than two GPUs are visible."""
 import os
 import pathlib
 import subprocess
@@ -48,6 +49,19 @@ import nvfp4quant_test_b200.helper as H
 _, gi = H.get_nvfp4_global_scale(w, 256.0)
 qs, ss = K.scalesweep_mse_nvfp4_quant_impl(w[ra:rb].contiguous(), gi)
 l2, h2 = scale_slab(ra, rb, Kd // 16)
+assert torch.equal(qs, qf[ra:rb]) and torch.equal(ss.view(torch.uint8).reshape(-1), sf.view(torch.uint8).reshape(-1)[l2:h2])
+# importance reduced by column slices + local scales of the row shards, one all-gather: the bits of one GPU, and the
+# weighted sweep of this rank's rows with them equals its rows inside the whole
+from nvfp4quant_test_b200.sharding import ImportanceGather
+ig = ImportanceGather(Kd, dev)
+c0, c1 = ig.columns
+H.channel_square_norm(x[:, c0:c1], out=ig.imp_slot)
+H.get_nvfp4_global_scale(w[ra:rb].contiguous(), 256.0, out=ig.scale_slot)
+imp, gs_all, gs_inv = ig.gather()
+gs_one, gi_one = H.get_nvfp4_global_scale(w, 256.0)
+assert torch.equal(imp, H.channel_square_norm(x)) and torch.equal(gs_all, gs_one) and torch.equal(gs_inv, gi_one)
+qs, ss = K.scalesweep_weighted_mse_nvfp4_quant_impl(w[ra:rb].contiguous(), imp, gs_inv)
+qf, sf = K.scalesweep_weighted_mse_nvfp4_quant_impl(w, H.channel_square_norm(x), gi_one)
 assert torch.equal(qs, qf[ra:rb]) and torch.equal(ss.view(torch.uint8).reshape(-1), sf.view(torch.uint8).reshape(-1)[l2:h2])
 dist.barrier()
 dist.destroy_process_group()
