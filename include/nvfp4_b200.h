@@ -71,8 +71,8 @@ int nvfp4_quant_launch(int variant, const void* x, int x_dtype, const float* imp
                        const float* gs_inv, uint8_t* codes, uint8_t* scales, int64_t m, int64_t n,
                        int64_t padded_n, int lower, int upper, int swizzled, void* stream);
 
-/* Same, choosing the kernel body: 0 = default (5 when a quarter or more of the scale layout's rows are
- * padding, else 6 where it applies, else 3), 1 = scalar (one candidate at a time, the plainest transcription), 2 = one candidate per trip with
+/* Same, choosing the kernel body: 0 = default (9 for tensors of a few tokens, see there; else 5 when a quarter or more
+ * of the scale layout's rows are padding, else 8 / 7 / 6 where they apply, else 3), 1 = scalar (one candidate at a time, the plainest transcription), 2 = one candidate per trip with
  * packed multiplies and the mixed-precision subtract, 3 = two candidates per trip sharing one f32x2 FMA chain,
  * 5 = 3 with warps that hold only padding rows skipping the sweep, 6 = 3 on a two-dimensional grid (row =
  * blockIdx.x, uniform over the CTA; taken by default when the row is a whole number of 256-block chunks wide,
@@ -80,7 +80,9 @@ int nvfp4_quant_launch(int variant, const void* x, int x_dtype, const float* imp
  * the sweep unrolled (default for the unweighted sweep with the reference's window; other windows make it 6),
  * 8 = 7 without any validity predicate, for tensors in which every slot of the scale layout is a real block (m a
  * multiple of 128 in the tiled layout, padded_n == n, rows a whole number of 256-block chunks wide, the reference's
- * window); the default there, elsewhere 8 means the default.
+ * window); the default there, elsewhere 8 means the default; 9 = 3 in CTAs of 64 threads over the real rows' slots,
+ * which spreads a tensor of a few tokens over four times as many SMs, plus a few CTAs that zero the padding rows of the
+ * tiled scale layout (the default up to 32768 real blocks, e.g. 64 tokens x 8192; 24576 for the weighted sweep).
  * 4 is the fused form, which has its own entry point below.  All give identical bytes; exposed for testing and
  * timing. */
 int nvfp4_quant_launch_impl(int impl, int variant, const void* x, int x_dtype, const float* importance,

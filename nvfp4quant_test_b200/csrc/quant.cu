@@ -48,7 +48,20 @@ constexpr int kThreads = 256;
 #ifndef NVFP4_QUANT_MIN_BLOCKS_W2D
 #define NVFP4_QUANT_MIN_BLOCKS_W2D 4
 #endif
+// Body 9 (a few tokens): CTAs of 64 threads over the slots of the real rows only.  A 256-thread CTA puts two warps on
+// every scheduler of one SM, and a warp's sweep is ~750 instructions; 64-thread CTAs spread the same blocks over four
+// times as many SMs with at most one warp per scheduler.  The padding rows of the tiled scale layout (127 of 128 for
+// one token) get a few CTAs at the end of the grid that write their zero words.
+constexpr int kSmallThreads = 64;
+// Real 16-element blocks up to which body 9 is the default.  Measured in a chain of launches (us, body 9 against the
+// better of the other bodies): unweighted 1 x 4096 1.72 / 2.38, 1 x 14336 1.78 / 2.74, 32 x 8192 1.94 / 2.81, 64 x 8192
+// 2.50 / 2.84, 128 x 4096 2.55 / 2.54, 96 x 8192 3.57 / 3.37; weighted 1 x 8192 2.35 / 3.85, 48 x 8192 3.59 / 4.87,
+// 64 x 8192 3.61 / 4.07, 128 x 4096 3.59 / 3.40, 96 x 8192 6.39 / 5.28.
+constexpr int64_t kSmallBlocks = 32768;
+constexpr int64_t kSmallBlocksWeighted = 24576;
+__host__ __device__ constexpr int block_threads(int impl) { return impl == 9 ? kSmallThreads : kThreads; }
 constexpr int min_blocks(int variant, int impl) {
+    if (impl == 9) return 8;
     return variant == NVFP4_VARIANT_WEIGHTED ? (impl >= 6 ? NVFP4_QUANT_MIN_BLOCKS_W2D : 4)
            : (impl >= 6 && variant == NVFP4_VARIANT_MSE) ? NVFP4_QUANT_MIN_BLOCKS_2D
                                                          : NVFP4_QUANT_MIN_BLOCKS;
@@ -340,9 +353,10 @@ __device__ __forceinline__ uint32_t sweep_single(const float v[16], const float 
 }
 
 template <int DT, int VARIANT, int IMPL>
-__global__ void __launch_bounds__(kThreads, min_blocks(VARIANT, IMPL))
+__global__ void __launch_bounds__(block_threads(IMPL), min_blocks(VARIANT, IMPL))
 quant_kernel(const QuantParams p) {
-    static_assert(kThreads == kTabSize, "one table entry per thread");
+    constexpr int T = block_threads(IMPL);   // threads per CTA
+    static_assert(kTabSize % T == 0, "every thread builds the same number of table entries");
     __shared__ float4 tab[kTabSize];
     constexpr bool FUSED = IMPL == 4;
     static_assert(!FUSED || VARIANT != NVFP4_VARIANT_AMAX, "the fused variant covers the two sweeps");
@@ -356,8 +370,9 @@ quant_kernel(const QuantParams p) {
     // chunks wide (e.g. 512 blocks per row at 8192 columns); narrow or ragged widths keep the flat numbering.
     constexpr bool GRID2D = IMPL == 6 || IMPL == 7 || IMPL == 8;   // 7 = 6 with the reference's candidate count compiled in
     constexpr bool WHOLE = IMPL == 8;                              // 8 = 7 on tensors without any padding: no predicates
-    const int64_t id = GRID2D ? 0 : static_cast<int64_t>(blockIdx.x) * kThreads + threadIdx.x;
-    const bool in_range = GRID2D ? true : id < p.total;
+    constexpr bool SMALL = IMPL == 9;   // threads for the slots of the real rows only (see the end of the kernel)
+    const int64_t id = GRID2D ? 0 : static_cast<int64_t>(blockIdx.x) * T + threadIdx.x;
+    const bool in_range = GRID2D ? true : id < (SMALL ? p.m * p.width : p.total);
     int64_t row = 0, col = 0;
     if (GRID2D) {
         row = blockIdx.x;
@@ -373,6 +388,23 @@ quant_kernel(const QuantParams p) {
         }
     }
     const bool valid = WHOLE ? true : (in_range && row < p.m && col < p.bout);
+    if (SMALL && static_cast<int64_t>(blockIdx.x) * T >= p.m * p.width) {
+        // A CTA behind the real rows' slots.  The rows m .. rows-1 of the tiled scale layout (127 of 128 for one token)
+        // hold no data; these CTAs write their zero scale bytes, four 32-bit words (of four columns each) per thread,
+        // and leave before the candidate table is built.  (Rows beyond m exist only in the tiled layout, whose width is
+        // a multiple of 4; the launcher sizes this part of the grid, and at most 127 rows are padding.)
+        griddep_launch();
+        const uint32_t words_per_row = static_cast<uint32_t>(p.width >> 2);
+        const uint32_t words = static_cast<uint32_t>(p.rows - p.m) * words_per_row;
+        const uint32_t real_ctas = static_cast<uint32_t>((p.m * p.width + T - 1) / T);
+        const uint32_t fill_threads = (gridDim.x - real_ctas) * T;
+        for (uint32_t wi = (blockIdx.x - real_ctas) * T + threadIdx.x; wi < words; wi += fill_threads) {
+            const uint32_t r = wi / words_per_row;
+            const uint32_t c = (wi - r * words_per_row) * 4u;
+            *reinterpret_cast<uint32_t*>(p.scales + swizzled_scale_offset(p.m + r, c, p.k_pad)) = 0u;
+        }
+        return;
+    }
 
     float v[16], w[16];
 #pragma unroll
@@ -391,13 +423,16 @@ quant_kernel(const QuantParams p) {
     // one multiplier per block is two reciprocals away from the scale byte, and without the table there is no
     // CTA-wide barrier between the loads and their use.
     if (VARIANT != NVFP4_VARIANT_AMAX) {
-        const uint32_t raw = static_cast<uint32_t>(min(max(static_cast<int>(threadIdx.x) - kTabPad, 1), 126));
-        const float s = e4m3_to_f32(raw);
-        float4 e;
-        e.x = e.y = div_full(1.0f, s);
-        e.z = __fmul_rn(s, s);
-        e.w = __uint_as_float(raw);
-        tab[threadIdx.x] = e;
+#pragma unroll
+        for (int t = threadIdx.x; t < kTabSize; t += T) {   // one entry per thread with 256 threads, four with 64
+            const uint32_t raw = static_cast<uint32_t>(min(max(t - kTabPad, 1), 126));
+            const float s = e4m3_to_f32(raw);
+            float4 e;
+            e.x = e.y = div_full(1.0f, s);
+            e.z = __fmul_rn(s, s);
+            e.w = __uint_as_float(raw);
+            tab[t] = e;
+        }
         __syncthreads();
     }
 
@@ -459,7 +494,7 @@ quant_kernel(const QuantParams p) {
     // 128 rows for a single token) has nothing to sweep and only writes its zero scale bytes below.  A separate
     // instantiation because the vote and branch cost the full-size kernel 6 % (8192 x 8192: 123.7 -> 131.8 us);
     // the launcher picks it when at least a quarter of the slot grid is padding rows.
-    if (IMPL == 5 && !__any_sync(0xffffffffu, valid)) {
+    if ((IMPL == 5 || IMPL == 9) && !__any_sync(0xffffffffu, valid)) {
         // nothing
     } else if (VARIANT == NVFP4_VARIANT_AMAX) {
         const float amax = max_abs16(v);
@@ -482,8 +517,9 @@ quant_kernel(const QuantParams p) {
         const int first_idx = min(max(base_raw + p.lower, -kTabPad), 127) + kTabPad;
         sbyte = (IMPL == 1)   ? sweep_scalar<W>(v, w, first_idx, p.ncand, tab)
                 : (IMPL == 2) ? sweep_single<W>(v, w, first_idx, p.ncand, tab)
-                : (IMPL == 7 || IMPL == 8) ? sweep_paired<W, W ? 16 : 11>(v, w, first_idx, p.ncand, tab)
-                              : sweep_paired<W>(v, w, first_idx, p.ncand, tab);
+                : (IMPL == 7 || IMPL == 8 || (IMPL == 9 && p.ncand == (W ? 16 : 11)))
+                    ? sweep_paired<W, W ? 16 : 11>(v, w, first_idx, p.ncand, tab)
+                    : sweep_paired<W>(v, w, first_idx, p.ncand, tab);
         // sbyte is 0 only when no candidate had a comparable (non-NaN, < inf) error: 1/0 as the reference computes it
         inv = (sbyte == 0) ? div_full(1.0f, 0.0f) : tab[sbyte + kTabPad].x;
     }
@@ -526,11 +562,23 @@ cudaError_t launch_impl(int impl, const QuantParams& p, cudaStream_t stream) {
     const bool whole = VARIANT != NVFP4_VARIANT_AMAX && p.rows == p.m && p.bin == p.bout && p.bout == p.width &&
                        (p.width % kThreads) == 0 && p.width / kThreads <= 65535 && p.rows <= 0x7fffffffLL &&
                        (VARIANT == NVFP4_VARIANT_MSE ? p.ncand == 11 : p.ncand == 16);
+    const bool small = VARIANT != NVFP4_VARIANT_AMAX &&
+                       p.m * p.bout <= (VARIANT == NVFP4_VARIANT_WEIGHTED ? kSmallBlocksWeighted : kSmallBlocks);
     if constexpr (VARIANT != NVFP4_VARIANT_AMAX) {
-        if ((impl == 8 || impl == 0) && whole) {
+        if ((impl == 8 || (impl == 0 && !small)) && whole) {
             const dim3 grid2(static_cast<unsigned>(p.rows), static_cast<unsigned>(p.width / kThreads));
             return launch_dependent(quant_kernel<DT, VARIANT, 8>, grid2, dim3(kThreads), 0, stream, p);
         }
+    }
+    // body 9: tensors of a few tokens (up to kSmallBlocks real blocks), where latency is all that matters
+    if (impl == 9 || (impl == 0 && small)) {
+        // CTAs for the slots of the real rows, then CTAs that zero the padding rows' scale words (4 words per thread)
+        const int64_t pad_words = (p.rows - p.m) * (p.width >> 2);
+        if (pad_words > 0x7fffffffLL) return cudaErrorInvalidValue;   // at most 127 rows: a width beyond 2^26 columns
+        const int64_t grid9 = (p.m * p.width + kSmallThreads - 1) / kSmallThreads +
+                              (pad_words + 4 * kSmallThreads - 1) / (4 * kSmallThreads);
+        if (grid9 > 0x7fffffffLL) return cudaErrorInvalidValue;
+        return launch_dependent(quant_kernel<DT, VARIANT, 9>, static_cast<unsigned>(grid9), dim3(kSmallThreads), 0, stream, p);
     }
     if (impl >= 8) impl = 0;
     cudaError_t e;
@@ -573,7 +621,7 @@ extern "C" int nvfp4_quant_launch_impl(int impl, int variant, const void* x, int
     using namespace nvfp4;
     if (variant < NVFP4_VARIANT_MSE || variant > NVFP4_VARIANT_AMAX) return NVFP4_ERR_BAD_ENUM;
     if (x_dtype < NVFP4_DT_BF16 || x_dtype > NVFP4_DT_F32) return NVFP4_ERR_BAD_ENUM;
-    if (impl < 0 || impl > 8 || impl == 4) return NVFP4_ERR_BAD_ENUM;
+    if (impl < 0 || impl > 9 || impl == 4) return NVFP4_ERR_BAD_ENUM;
     if (m < 0 || n < 0 || (n % kBlock) != 0 || (padded_n % kBlock) != 0 || padded_n < n) return NVFP4_ERR_BAD_SHAPE;
     if (variant != NVFP4_VARIANT_AMAX && (upper < lower || upper - lower + 1 > 64)) return NVFP4_ERR_BAD_RANGE;
     QuantParams p;

@@ -59,7 +59,7 @@ def test_cuda_matches_oracle_bit_for_bit(cuda_lib, probe_lib, oracle, name):
     idx = util.logical_scale_index(m, blocks, c["swizzled"])
     pad = np.ones(want_scales.size, dtype=bool)
     pad[idx] = False
-    for impl in (0, 1, 2, 3, 5, 6, 7):
+    for impl in (0, 1, 2, 3, 5, 6, 7, 9):
         codes, scales, intact = _run_cuda(c, gs_inv, impl)
         assert intact, f"impl {impl} wrote outside its buffers"
         assert np.array_equal(codes, want_codes), f"impl {impl}: {(codes != want_codes).sum()} code bytes differ"
@@ -480,7 +480,7 @@ def test_two_dimensional_grid_bodies(cuda_lib, oracle, m, n, padded_n, swizzled)
         if variant != "amax":
             want_codes, want_scales = util.oracle_quant_case(oracle, c, gs_inv)
             assert np.array_equal(flat_codes, want_codes) and np.array_equal(flat_scales[idx], want_scales[idx])
-        for impl in (0, 6, 7):
+        for impl in (0, 6, 7, 9):
             codes, scales, intact = _run_cuda(c, gs_inv, impl)
             assert intact, f"{variant} impl {impl} wrote outside its buffers"
             assert np.array_equal(codes, flat_codes), f"{variant} impl {impl}"
@@ -519,7 +519,7 @@ def test_whole_tile_body(cuda_lib, oracle, m, n, dtype, swizzled):
             if m <= 256:
                 want_codes, want_scales = util.oracle_quant_case(oracle, c, gs_inv)
                 assert np.array_equal(ref_codes, want_codes) and np.array_equal(ref_scales, want_scales)
-            for impl in (0, 8):
+            for impl in (0, 8, 9):
                 codes, scales, intact = _run_cuda(c, gs_inv, impl)
                 assert intact, f"{variant} impl {impl} wrote outside its buffers"
                 assert np.array_equal(codes, ref_codes), f"{variant} impl {impl}: {(codes != ref_codes).sum()} code bytes"
