@@ -103,6 +103,20 @@ __device__ __forceinline__ uint64_t fma_f32x2(uint64_t a, uint64_t b, uint64_t c
 // next launch did not ask for it).
 __device__ __forceinline__ void griddep_wait() { asm volatile("griddepcontrol.wait;" ::: "memory"); }
 __device__ __forceinline__ void griddep_launch() { asm volatile("griddepcontrol.launch_dependents;" ::: "memory"); }
+// Reads that follow griddep_wait().  The compiler takes a non-coherent load (__ldg) to read memory that never changes
+// and may move it ahead of any barrier, the wait included - where the kernel before this one has not written the data
+// yet.  after_wait(p) hands a pointer back as a value produced behind the wait, so that loads through it stay there
+// (volatile asm statements keep their order); load_f32_after_wait is a plain coherent load for single words.
+template <class T>
+__device__ __forceinline__ T* after_wait(T* p) {
+    asm volatile("" : "+l"(p)::"memory");
+    return p;
+}
+__device__ __forceinline__ float load_f32_after_wait(const float* p) {
+    float v;
+    asm volatile("ld.global.f32 %0, [%1];" : "=f"(v) : "l"(p) : "memory");
+    return v;
+}
 
 // 1 (default): the library's kernels are launched with the programmatic-stream-serialization attribute; 0: plain
 // launches.  One switch for the whole library (testing hook: nvfp4_gemm_tune_pdl); defined in status.cu.

@@ -50,8 +50,9 @@ struct GemmParams {
 // Output scale of a launch: alpha[0], or alpha[0] * alpha2[0] rounded once (what a separate fp32 multiplication of the
 // activation's and the weight's global scales gives).
 __device__ __forceinline__ float load_alpha(const float* alpha, const float* alpha2) {
-    const float a = __ldg(alpha);
-    return alpha2 ? __fmul_rn(a, __ldg(alpha2)) : a;
+    // called behind griddep_wait(): the scales may be the work of the kernels before this one
+    const float a = load_f32_after_wait(alpha);
+    return alpha2 ? __fmul_rn(a, load_f32_after_wait(alpha2)) : a;
 }
 
 // Tile index -> (m tile, n tile).  Tiles are numbered in bands of `group` m-tiles: inside a band the m index runs

@@ -24,11 +24,13 @@ template <int DT>
 __global__ void __launch_bounds__(kGsThreads) global_scale_kernel(const void* x, int64_t numel, float fp8_max,
                                                                   float* out, uint32_t* scratch) {
     // launched as a programmatic dependent: x, the scratch words and `out` belong to the kernel before this one until
-    // it has finished; the kernel behind this one (the quantizer) may be scheduled from here on
-    griddep_wait();
+    // it has finished.  The kernel behind this one (the quantizer, which waits before it touches anything) may be
+    // scheduled at once.
     griddep_launch();
+    griddep_wait();
     constexpr int kPerVec = (DT == NVFP4_DT_F32) ? 4 : 8;
     const int64_t nvec = numel / kPerVec;
+    x = after_wait(x);   // loads of x stay behind the wait
     const uint4* xv = static_cast<const uint4*>(x);
     const int64_t stride = static_cast<int64_t>(gridDim.x) * kGsThreads;
     uint32_t acc = 0;

@@ -360,10 +360,17 @@ quant_kernel(const QuantParams p) {
     __shared__ float4 tab[kTabSize];
     constexpr bool FUSED = IMPL == 4;
     static_assert(!FUSED || VARIANT != NVFP4_VARIANT_AMAX, "the fused variant covers the two sweeps");
-    // launched as a programmatic dependent: the input, the global scale and the output buffers may still be in use by
-    // the kernel before this one on the stream
+    // Launched as a programmatic dependent: the input, the global scale and the output buffers may still be in use by
+    // the kernel before this one on the stream, so everything waits.  The kernel BEHIND this one may be scheduled right
+    // away, even before that wait is over: whatever it does ahead of its own wait (a GEMM streams a prepared, constant
+    // weight) depends on neither this kernel nor the ones before it, and its wait covers this kernel's completion,
+    // which in turn comes after this wait.
+    griddep_launch();
     if (!FUSED) griddep_wait();
-    float gs_inv = FUSED ? 0.0f : __ldg(p.gs_inv);
+    // everything the kernel before this one may have written is read through pointers taken behind the wait
+    const void* const x_in = after_wait(p.x);
+    const float* const importance_in = after_wait(p.importance);
+    float gs_inv = FUSED ? 0.0f : load_f32_after_wait(p.gs_inv);
     // Body 6 = body 3 with a two-dimensional grid: blockIdx.x is the row, blockIdx.y the 256-block column chunk.
     // The row is then uniform over the CTA, so the division below, the row part of the addresses and most of the
     // tiled scale offset leave the per-thread instruction stream.  Used when the slot grid is a whole number of
@@ -393,7 +400,6 @@ quant_kernel(const QuantParams p) {
         // hold no data; these CTAs write their zero scale bytes, four 32-bit words (of four columns each) per thread,
         // and leave before the candidate table is built.  (Rows beyond m exist only in the tiled layout, whose width is
         // a multiple of 4; the launcher sizes this part of the grid, and at most 127 rows are padding.)
-        griddep_launch();
         const uint32_t words_per_row = static_cast<uint32_t>(p.width >> 2);
         const uint32_t words = static_cast<uint32_t>(p.rows - p.m) * words_per_row;
         const uint32_t real_ctas = static_cast<uint32_t>((p.m * p.width + T - 1) / T);
@@ -413,11 +419,10 @@ quant_kernel(const QuantParams p) {
         w[j] = 0.0f;
     }
     if (WHOLE || (valid && col < p.bin)) {
-        load16<DT>(p.x, row * p.n + col * kBlock, v);
-        if (VARIANT == NVFP4_VARIANT_WEIGHTED) load16<NVFP4_DT_F32>(p.importance, col * kBlock, w);
+        load16<DT>(x_in, row * p.n + col * kBlock, v);
+        if (VARIANT == NVFP4_VARIANT_WEIGHTED) load16<NVFP4_DT_F32>(importance_in, col * kBlock, w);
     }
 
-    griddep_launch();   // a kernel queued behind this one with a programmatic dependency may start its own prologue
     // The global scale and the block's elements were requested above; the candidate table is built while they are
     // on their way (at small batch sizes nothing else hides a trip to memory).  The amax variant needs no table: its
     // one multiplier per block is two reciprocals away from the scale byte, and without the table there is no

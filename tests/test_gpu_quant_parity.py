@@ -537,3 +537,31 @@ def test_global_scale_of_views_that_start_off_a_16_byte_boundary(cuda_lib):
         gs, gs_inv = H.get_nvfp4_global_scale(x, 448.0)
         ref = x.abs().max().float() / (6.0 * 448.0)
         assert bool(gs == ref) and bool(gs_inv == ref.reciprocal())
+
+
+def test_quantizer_right_behind_the_global_scale_kernel_reads_the_new_scale(cuda_lib):
+    """global scale -> quantizer back to back, both programmatic dependent launches, with the scale buffer holding a
+    wrong value before every round: the quantizer is scheduled while the scale kernel still runs and must not read the
+    scale (or its input) ahead of its wait.  Small and large tensors, both sweeps."""
+    import nvfp4quant_test_b200.kernels as K
+    from nvfp4quant_test_b200 import helper as H
+
+    g = torch.Generator(device="cuda")
+    g.manual_seed(21)
+    for shape in ((1, 4096), (48, 8192), (1024, 4096)):
+        x = torch.normal(0.0, 1.0, size=shape, generator=g, device="cuda", dtype=torch.bfloat16)
+        imp = torch.rand((1, shape[1]), generator=g, device="cuda") + 0.5
+        gs, gs_inv = H.get_nvfp4_global_scale(x, 256.0)
+        want_m = K.scalesweep_mse_nvfp4_quant_impl(x, gs_inv)
+        want_w = K.scalesweep_weighted_mse_nvfp4_quant_impl(x, imp, gs_inv)
+        torch.cuda.synchronize()
+        buf = torch.empty(2, dtype=torch.float32, device="cuda")
+        for _ in range(6):
+            buf.fill_(3.0)
+            H.get_nvfp4_global_scale(x, 256.0, out=buf)
+            got_m = K.scalesweep_mse_nvfp4_quant_impl(x, buf[1])
+            buf2 = torch.full((2,), 0.125, dtype=torch.float32, device="cuda")
+            H.get_nvfp4_global_scale(x, 256.0, out=buf2)
+            got_w = K.scalesweep_weighted_mse_nvfp4_quant_impl(x, imp, buf2[1])
+            for got, want in ((got_m, want_m), (got_w, want_w)):
+                assert torch.equal(got[0], want[0]) and torch.equal(got[1].view(torch.uint8), want[1].view(torch.uint8)), shape
