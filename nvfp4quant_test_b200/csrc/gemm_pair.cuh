@@ -88,6 +88,9 @@ gemm_pair_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_consta
                  const GemmParams p) {
     using C = PairCfg<BN>;
     extern __shared__ uint8_t smem_raw[];
+    // The kernel queued behind this one may be scheduled at once: ahead of its own wait it reads nothing but a
+    // prepared (constant) weight, and that wait covers this kernel's completion.
+    griddep_launch();
     const uint32_t raw_addr = smem_u32(smem_raw);
     const uint32_t base = (raw_addr + 1023u) & ~1023u;
     uint8_t* aligned = smem_raw + (base - raw_addr);
@@ -134,7 +137,6 @@ gemm_pair_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_consta
     tc_fence_after();
     const uint32_t tmem_base = *tmem_slot;
     if (threadIdx.x == 0) trace_mark(1, 2);
-    griddep_launch();                 // a GEMM queued behind this one may start on its weights
     if (warp >= 2) griddep_wait();    // the epilogue reads alpha and writes the output: only after the previous kernel
 
     const int m_tiles = (p.M + 255) / 256;

@@ -91,6 +91,9 @@ __global__ void __launch_bounds__(kThreads)
 skinny_kernel(const __grid_constant__ SkinnyMaps maps, const __grid_constant__ CUtensorMap tmap_x, const SkinnyParams p) {
     using C = SkinnyCfg<BT>;
     extern __shared__ uint8_t smem_raw[];
+    // The kernel queued behind this one may be scheduled at once: ahead of its own wait it reads nothing but a
+    // prepared (constant) weight, and that wait covers this kernel's completion.
+    griddep_launch();
     const uint32_t raw_addr = smem_u32(smem_raw);
     const uint32_t base = (raw_addr + 1023u) & ~1023u;
     uint8_t* aligned = smem_raw + (base - raw_addr);
@@ -225,7 +228,6 @@ skinny_kernel(const __grid_constant__ SkinnyMaps maps, const __grid_constant__ C
     __syncthreads();
     tc_fence_after();
     const uint32_t tmem_base = *tmem_slot;
-    griddep_launch();   // a GEMM queued behind this one may begin: its weight stream does not depend on our output
     if (warp >= 2) griddep_wait();   // the epilogue reads alpha (and writes out): only once the previous kernel is done
 
     if (warp == 0) {

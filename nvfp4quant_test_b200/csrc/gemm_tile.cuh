@@ -72,6 +72,9 @@ __global__ void __launch_bounds__(kThreads, 1)
 gemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant__ CUtensorMap tmap_b, const GemmParams p) {
     using C = Cfg<BN>;
     extern __shared__ uint8_t smem_raw[];
+    // The kernel queued behind this one may be scheduled at once: ahead of its own wait it reads nothing but a
+    // prepared (constant) weight, and that wait covers this kernel's completion.
+    griddep_launch();
     const uint32_t raw_addr = smem_u32(smem_raw);
     const uint32_t base = (raw_addr + 1023u) & ~1023u;
     uint8_t* aligned = smem_raw + (base - raw_addr);
@@ -123,7 +126,6 @@ gemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant__ 
     tc_fence_after();
     const uint32_t tmem_base = *tmem_slot;   // meaningful in warps 1..5 only
     if (threadIdx.x == 32) trace_mark(0, 2);
-    griddep_launch();                 // a GEMM queued behind this one may start on its weights
     if (warp >= 2) griddep_wait();    // alpha, and the output buffer, belong to whatever ran before: epilogue only after it
 
     const int m_tiles = (p.M + kBM - 1) / kBM;
