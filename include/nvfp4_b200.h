@@ -199,9 +199,9 @@ int nvfp4_gemm_release(void* handle);
  * the common factor (the activation's global scale) or is NULL (factor 1).  The product is one fp32 multiplication,
  * so with alpha_a the result equals nvfp4_gemm_launch_prepared with alpha = alpha_w[i][0] * alpha_a[0] computed by a
  * separate fp32 multiplication, without that extra launch.  handles / alpha_w / outs_bf16 are HOST arrays read during the call.
- * For decode-sized M on shapes the decode-sized kernel serves, up to 8 weights go out as ONE launch whose weight tiles
- * are numbered through the group (fixed costs paid once, every SM on the combined weight stream); otherwise one
- * launch per weight.  Outputs agree with the one-by-one calls to fp32 rounding before the bf16 store (bit for bit when
+ * Up to 64 tokens (and wherever the kernel choice takes the decode-sized kernel for the group's total N), up to 8 weights
+ * go out as ONE launch whose weight tiles are numbered through the group (fixed costs paid once, every SM on the
+ * combined weight stream); otherwise one launch per weight.  Outputs agree with the one-by-one calls to fp32 rounding before the bf16 store (bit for bit when
  * the K ranges per tile agree; they are chosen from the group's total tile count).  No workspace.
  */
 int nvfp4_gemm_launch_grouped(void* const* handles, int n_weights, const uint8_t* a, const uint8_t* sfa,

@@ -100,7 +100,7 @@ def prepare_layer(qlayer: dict) -> dict:
 # matrices that read the same activation in a decoder layer (q / k / v the normed hidden state, gate / up the normed
 # post-attention state); o and down have inputs of their own
 WEIGHT_GROUPS = (("q", "k", "v"), ("o",), ("gate", "up"), ("down",))
-GROUPED_MAX_TOKENS = 32    # beyond, the per-matrix kernels on forked streams are faster (64 tokens: 1.88 against 2.25 ms)
+GROUPED_MAX_TOKENS = 64    # beyond, the per-matrix kernels on forked streams are faster (96 tokens: 1.95 against 2.05 ms)
 
 
 def layer_gemms_grouped(qlayer: dict, acts: dict[int, torch.Tensor], weight_scales: dict, prepared: dict):
