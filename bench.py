@@ -248,6 +248,7 @@ def strong_scaling(dev, rank, world, torch, dist, max_over_ranks, barrier):
             "quantize_ms": res["quantize_ms"], "quantize_first_pass_ms": res["quantize_first_pass_ms"],
             "quantize_gweights_per_s": res["quantize_gweights_per_s"],
             "gemm_phase_ms_all_layers": {str(g["tokens"]): g["ms_all_layers"] for g in res["gemm"]},
+            "gemm_phase_eager_ms_all_layers": {str(g["tokens"]): g["eager_ms_all_layers"] for g in res["gemm"]},
             "layers_per_gpu": 32 // world if world <= 32 else 0,
             "includes": "per layer: activation global scale + ScaleSweep quantization + 7 GEMMs, one CUDA graph per rank"}
     return out

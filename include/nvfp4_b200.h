@@ -115,6 +115,14 @@ int nvfp4_global_scale_launch(const void* x, int x_dtype, int64_t numel, float f
 int nvfp4_quant_fused_launch(int variant, const void* x, int x_dtype, const float* importance, float fp8_max,
                              float* gs_out, uint32_t* scratch, uint8_t* codes, uint8_t* scales, int64_t m, int64_t n,
                              int64_t padded_n, int lower, int upper, int swizzled, void* stream);
+/*
+ * The same two steps as two launches from ONE host call (global scale kernel, then the quantizer reading gs_out[1]):
+ * for callers that pay per host call, e.g. an eager decode loop.  Any variant (amax included), any size; `scratch` = the
+ * 2 zeroed uint32 of nvfp4_global_scale_launch.  Bytes and scales equal the two separate calls.
+ */
+int nvfp4_quant_chain_launch(int variant, const void* x, int x_dtype, const float* importance, float fp8_max,
+                             float* gs_out, uint32_t* scratch, uint8_t* codes, uint8_t* scales, int64_t m, int64_t n,
+                             int64_t padded_n, int lower, int upper, int swizzled, void* stream);
 /* Synchronises `stream`; *status = 0, or 1 if a fused launch on this device gave up its grid-wide wait (its
  * outputs are then invalid and its scratch must be zeroed again).  Reading a non-zero status clears it. */
 int nvfp4_quant_fused_last_status(void* stream, uint32_t* status);

@@ -16,7 +16,7 @@ DT_BF16, DT_F16, DT_F32 = 0, 1, 2
 ERR_TOO_LARGE = -8
 
 EXPORTS = (
-    "nvfp4_quant_launch", "nvfp4_quant_launch_impl", "nvfp4_quant_fused_launch", "nvfp4_quant_fused_last_status",
+    "nvfp4_quant_launch", "nvfp4_quant_launch_impl", "nvfp4_quant_fused_launch", "nvfp4_quant_chain_launch", "nvfp4_quant_fused_last_status",
     "nvfp4_global_scale_launch", "nvfp4_global_scale_launch_static", "nvfp4_global_scale_static_max_bytes",
     "nvfp4_channel_sqnorm_launch", "nvfp4_channel_sqnorm_launch_strided", "nvfp4_gemm_peak_probe", "nvfp4_gemm_set_wait_limit_ns", "nvfp4_quant_fused_set_wait_limit_ns",
     "nvfp4_gemm_launch", "nvfp4_gemm_workspace_bytes", "nvfp4_gemm_prepare", "nvfp4_gemm_launch_prepared", "nvfp4_gemm_launch_grouped", "nvfp4_gemm_release", "nvfp4_gemm_last_status", "nvfp4_gemm_force_path", "nvfp4_gemm_tune", "nvfp4_gemm_tune_raster", "nvfp4_gemm_tune_pdl", "nvfp4_gemm_plan",
@@ -49,6 +49,8 @@ def lib() -> ctypes.CDLL:
         L.nvfp4_quant_launch_impl.argtypes = [ci, ci, vp, ci, vp, vp, vp, vp, i64, i64, i64, ci, ci, ci, vp]
         L.nvfp4_quant_fused_launch.restype = ci
         L.nvfp4_quant_fused_launch.argtypes = [ci, vp, ci, vp, f32, vp, vp, vp, vp, i64, i64, i64, ci, ci, ci, vp]
+        L.nvfp4_quant_chain_launch.restype = ci
+        L.nvfp4_quant_chain_launch.argtypes = [ci, vp, ci, vp, f32, vp, vp, vp, vp, i64, i64, i64, ci, ci, ci, vp]
         L.nvfp4_quant_fused_last_status.restype = ci
         L.nvfp4_quant_fused_last_status.argtypes = [vp, vp]
         L.nvfp4_global_scale_launch.restype = ci

@@ -691,6 +691,22 @@ cudaError_t launch_fused_variant(int variant, const QuantParams& p, int sms, cud
 }  // namespace
 }  // namespace nvfp4
 
+// Global scale, then the quantizer with that scale, as two launches from one host call: what get_nvfp4_global_scale followed
+// by scalesweep_*_quant_out do (helper.py:96-100, bench.py:57-67 of the reference), for callers that pay per host call
+// (an eager decode loop).  gs_out[0] = amax|x| / (6 * fp8_max), gs_out[1] = 1 / gs_out[0]; `scratch` = the 2 zeroed words
+// of nvfp4_global_scale_launch.  Both kernels are programmatic dependent launches; bytes equal the two separate calls.
+extern "C" int nvfp4_quant_chain_launch(int variant, const void* x, int x_dtype, const float* importance, float fp8_max,
+                                        float* gs_out, uint32_t* scratch, uint8_t* codes, uint8_t* scales, int64_t m,
+                                        int64_t n, int64_t padded_n, int lower, int upper, int swizzled, void* stream) {
+    if (m <= 0 || n <= 0) return NVFP4_ERR_BAD_SHAPE;   // an empty tensor has no maximum
+    if (!(fp8_max > 0.0f)) return NVFP4_ERR_BAD_RANGE;
+    if (!gs_out) return NVFP4_ERR_NULL_POINTER;
+    const int st = nvfp4_global_scale_launch(x, x_dtype, m * n, fp8_max, gs_out, scratch, stream);
+    if (st != NVFP4_OK) return st;
+    return nvfp4_quant_launch(variant, x, x_dtype, importance, gs_out + 1, codes, scales, m, n, padded_n, lower, upper,
+                              swizzled, stream);
+}
+
 extern "C" int nvfp4_quant_fused_launch(int variant, const void* x, int x_dtype, const float* importance, float fp8_max,
                                         float* gs_out, uint32_t* scratch, uint8_t* codes, uint8_t* scales, int64_t m,
                                         int64_t n, int64_t padded_n, int lower, int upper, int swizzled, void* stream) {

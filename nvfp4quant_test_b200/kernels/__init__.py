@@ -19,3 +19,4 @@ from .kernel_vllm import (  # noqa: F401
     swizzle_vllm_fp4_scale,
     unswizzle_vllm_fp4_scale,
 )
+from .linear import ActivationQuantizer, LinearGroup  # noqa: F401

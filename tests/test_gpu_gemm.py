@@ -598,3 +598,38 @@ def test_gemm_right_behind_the_quantizer_of_its_weight(cuda_lib):
             K.scalesweep_mse_nvfp4_quant_out(w, gwi, True, output=codes, output_scale=scales)
             got = K.nvfp4_scaled_mm(qa, codes, sa, scales.view(torch.float8_e4m3fn), alpha, torch.bfloat16)
             assert torch.equal(got[:16], want)
+
+
+def test_preallocated_decode_blocks_equal_the_allocating_entry_points(cuda_lib):
+    """kernels.ActivationQuantizer (global scale + sweep from one host call) and kernels.LinearGroup (grouped GEMM into
+    preallocated outputs), and llama_stack.DecodeLayer built from them: the same bits as get_nvfp4_global_scale +
+    scalesweep_mse_nvfp4_quant_impl + nvfp4_scaled_mm_grouped, call after call on changing inputs."""
+    import nvfp4quant_test_b200.kernels as K
+    from nvfp4quant_test_b200 import helper as H
+    from nvfp4quant_test_b200 import llama_stack as LS
+
+    dev = torch.device("cuda")
+    calib = LS.make_calibration(dev)
+    importance = {k: H.channel_square_norm(x) for k, x in calib.items()}
+    q = LS.quantize_layer(LS.make_layer(1, dev), importance)
+    ws, pw = LS.stack_weight_scales(q), LS.prepare_layer(q)
+    gen = torch.Generator(device=dev)
+    gen.manual_seed(9)
+    for tokens in (1, 24):
+        layer = LS.DecodeLayer(q, ws, pw, tokens, dev)
+        for _ in range(3):
+            acts = {kk: torch.normal(0.0, 1.0, size=(tokens, kk), generator=gen, device=dev, dtype=torch.bfloat16)
+                    for kk in calib}
+            got = layer(acts)
+            want = LS.layer_gemms_grouped(q, acts, ws, pw)
+            for name in want:
+                assert torch.equal(got[name], want[name]), (tokens, name)
+            for kk, quantizer in layer.quantizers.items():
+                gs, gi = H.get_nvfp4_global_scale(acts[kk], H.FP8_E4M3_MAX_4OVER6)
+                codes, scales = K.scalesweep_mse_nvfp4_quant_impl(acts[kk], gi)
+                assert torch.equal(quantizer.codes, codes) and torch.equal(quantizer.scales.view(torch.uint8), scales.view(torch.uint8))
+                assert torch.equal(quantizer.global_scale, torch.stack([gs, gi]))
+    with pytest.raises(ValueError):
+        layer({kk: v[:1] for kk, v in acts.items()})                       # wrong token count
+    with pytest.raises(ValueError):
+        K.LinearGroup([pw["q"], pw["down"]], [ws[4096][0][:1], ws[14336][0][:1]], 4)   # different K
