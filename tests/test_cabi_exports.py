@@ -164,6 +164,16 @@ def test_gemm_kernel_choice_by_shape(L):
     assert L.nvfp4_gemm_plan(1, 4096, 100, 148, ctypes.byref(p_), ctypes.byref(r_)) == -2
 
 
+def test_quant_chain_launch_rejects_bad_arguments_before_launching(L):
+    P = 0x1000
+    f = L.nvfp4_quant_chain_launch
+    assert f(0, P, 0, None, 256.0, P, P, P, P, 0, 64, 64, -3, 7, 1, None) == -2      # empty tensor: no maximum
+    assert f(0, P, 0, None, 0.0, P, P, P, P, 4, 64, 64, -3, 7, 1, None) == -5        # fp8_max must be positive
+    assert f(0, P, 0, None, 256.0, None, P, P, P, 4, 64, 64, -3, 7, 1, None) == -1   # no place for the scale
+    assert f(0, P, 7, None, 256.0, P, P, P, P, 4, 64, 64, -3, 7, 1, None) == -3      # dtype (refused by the first launch)
+    assert f(0, P + 2, 0, None, 256.0, P, P, P, P, 4, 64, 64, -3, 7, 1, None) == -4  # misaligned input
+
+
 def test_gemm_prepare_rejects_bad_arguments_and_release_is_safe(L):
     h = ctypes.c_void_p()
     P = 0x1000   # fake, aligned, never dereferenced: tensor maps only record the address
