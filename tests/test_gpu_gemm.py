@@ -633,3 +633,127 @@ def test_preallocated_decode_blocks_equal_the_allocating_entry_points(cuda_lib):
         layer({kk: v[:1] for kk, v in acts.items()})                       # wrong token count
     with pytest.raises(ValueError):
         K.LinearGroup([pw["q"], pw["down"]], [ws[4096][0][:1], ws[14336][0][:1]], 4)   # different K
+
+
+def test_random_launch_chains_do_not_depend_on_dependent_launch(cuda_lib):
+    """Seeded random programs over a small pool of reused buffers - global scale, the three quantizers, GEMMs with raw
+    pointers (also on a weight quantized by the launch just before), with prepared weights and grouped, GEMM outputs
+    fed back as the next activation, torch kernels in between - run back to back on one stream with every library
+    kernel a programmatic dependent launch, eagerly and as a CUDA graph, must leave every buffer with the bits the same
+    program leaves under plain stream order (nvfp4_gemm_tune_pdl(0)).  Buffers are reused on purpose, so that the
+    programs are full of read-after-write and write-after-read pairs between neighbouring launches."""
+    import random
+
+    import nvfp4quant_test_b200.kernels as K
+    from nvfp4quant_test_b200 import helper as H
+    from nvfp4quant_test_b200.kernels.kernel_gemm import gemm_last_status
+
+    dev = torch.device("cuda")
+    gen = torch.Generator(device=dev)
+    gen.manual_seed(1234)
+    kdim = 512
+    const_w = []                                                  # constant, prepared weights [n, kdim]
+    for n in (512, 256, 512):
+        w = torch.normal(0.0, 0.05, size=(n, kdim), generator=gen, device=dev, dtype=torch.bfloat16)
+        gs, gi = H.get_nvfp4_global_scale(w, 256.0)
+        c, s = K.scalesweep_mse_nvfp4_quant_impl(w, gi)
+        const_w.append((K.PreparedWeight(c, s), gs.reshape(1).clone(), c, s))
+    torch.cuda.synchronize()
+
+    def build_state(m):
+        st = {"x": torch.normal(0.0, 1.0, size=(m, kdim), generator=gen, device=dev, dtype=torch.bfloat16),
+              "src": torch.normal(0.0, 1.0, size=(m, kdim), generator=gen, device=dev, dtype=torch.bfloat16),
+              "wsrc": torch.normal(0.0, 0.05, size=(512, kdim), generator=gen, device=dev, dtype=torch.bfloat16),
+              "imp": torch.rand((1, kdim), generator=gen, device=dev) + 0.5,
+              "gs": torch.ones(2, dtype=torch.float32, device=dev),
+              "wgs": torch.ones(2, dtype=torch.float32, device=dev),
+              "alpha": torch.ones(1, dtype=torch.float32, device=dev),
+              "y": [torch.zeros((m, n), dtype=torch.bfloat16, device=dev) for n in (512, 256, 512)]}
+        st["qx"], st["sx"] = K.create_fp4_output_tensors(m, kdim, dev, True)
+        st["qw"], st["sw"] = K.create_fp4_output_tensors(512, kdim, dev, True)
+        H.get_nvfp4_global_scale(st["x"], 256.0, out=st["gs"])
+        K.scalesweep_mse_nvfp4_quant_out(st["x"], st["gs"][1], True, output=st["qx"], output_scale=st["sx"])
+        H.get_nvfp4_global_scale(st["wsrc"], 256.0, out=st["wgs"])
+        K.scalesweep_mse_nvfp4_quant_out(st["wsrc"], st["wgs"][1], True, output=st["qw"], output_scale=st["sw"])
+        return st
+
+    def run_program(prog, st):
+        f8 = torch.float8_e4m3fn
+        for op, arg in prog:
+            if op == "new_x":                       # a torch kernel rewrites the activation
+                st["x"].copy_(st["src"]).mul_(arg)
+            elif op == "feed_back":                 # a GEMM output becomes the activation (n == kdim for y[0], y[2])
+                st["x"].copy_(st["y"][arg])
+            elif op == "scale":
+                H.get_nvfp4_global_scale(st["x"], 256.0, out=st["gs"])
+            elif op == "quant":
+                if arg == 0:
+                    K.scalesweep_mse_nvfp4_quant_out(st["x"], st["gs"][1], True, output=st["qx"], output_scale=st["sx"])
+                elif arg == 1:
+                    K.scalesweep_weighted_mse_nvfp4_quant_out(st["x"], st["imp"], st["gs"][1], True, output=st["qx"],
+                                                              output_scale=st["sx"])
+                else:
+                    K.amax_nvfp4_quant_out(st["x"], st["gs"][1], True, output=st["qx"], output_scale=st["sx"])
+            elif op == "requant_w":                 # the raw-pointer weight is rewritten right before it is used
+                st["wsrc"].mul_(arg)
+                H.get_nvfp4_global_scale(st["wsrc"], 256.0, out=st["wgs"])
+                K.scalesweep_mse_nvfp4_quant_out(st["wsrc"], st["wgs"][1], True, output=st["qw"], output_scale=st["sw"])
+            elif op == "alpha":
+                torch.mul(st["gs"][0:1], st["wgs"][0:1], out=st["alpha"])
+            elif op == "mm_raw":
+                K.nvfp4_scaled_mm(st["qx"], st["qw"], st["sx"].view(f8), st["sw"].view(f8), st["alpha"], torch.bfloat16,
+                                  out=st["y"][0])
+            elif op == "mm_prepared":
+                pw, gw, _, _ = const_w[arg]
+                K.nvfp4_scaled_mm_prepared(st["qx"], st["sx"].view(f8), gw, pw, out=st["y"][arg])
+            elif op == "mm_grouped":
+                K.nvfp4_scaled_mm_grouped(st["qx"], st["sx"].view(f8), st["gs"][0:1], [c[0] for c in const_w],
+                                          [c[1] for c in const_w], st["y"])
+
+    def bits(t):                                    # bit patterns: NaNs (programs overflow on purpose) compare equal
+        return t.contiguous().view(torch.uint8).clone()
+
+    def snapshot(st):
+        return [bits(st[k]) for k in ("x", "gs", "wgs", "alpha", "qx", "qw", "sx", "sw")] + [bits(y) for y in st["y"]]
+
+    rng = random.Random(99)
+    ops = ["new_x", "feed_back", "scale", "quant", "requant_w", "alpha", "mm_raw", "mm_prepared", "mm_grouped"]
+    try:
+        for trial in range(30):
+            m = rng.choice([1, 8, 24, 40, 150])
+            prog = []
+            for _ in range(rng.randint(8, 16)):
+                op = rng.choice(ops)
+                arg = {"new_x": rng.choice([0.5, 1.5, 3.0]), "feed_back": rng.choice([0, 2]), "quant": rng.choice([0, 1, 2]),
+                       "requant_w": rng.choice([0.5, 2.0]), "mm_prepared": rng.randrange(3)}.get(op)
+                prog.append((op, arg))
+            gen.manual_seed(500 + trial)
+            base = build_state(m)
+            torch.cuda.synchronize()
+            results = []
+            for mode in ("plain", "pdl", "pdl_graph"):
+                st = {k: ([t.clone() for t in v] if isinstance(v, list) else v.clone()) for k, v in base.items()}
+                assert cuda_lib.nvfp4_gemm_tune_pdl(0 if mode == "plain" else 1) == 0
+                torch.cuda.synchronize()
+                if mode == "pdl_graph":
+                    side = torch.cuda.Stream()
+                    side.wait_stream(torch.cuda.current_stream())
+                    with torch.cuda.stream(side):
+                        warm = {k: ([t.clone() for t in v] if isinstance(v, list) else v.clone()) for k, v in base.items()}
+                        run_program(prog, warm)      # first launches of every kernel outside the capture
+                    torch.cuda.current_stream().wait_stream(side)
+                    torch.cuda.synchronize()
+                    graph = torch.cuda.CUDAGraph()
+                    with torch.cuda.graph(graph):
+                        run_program(prog, st)
+                    graph.replay()
+                else:
+                    run_program(prog, st)
+                torch.cuda.synchronize()
+                results.append(snapshot(st))
+            for other, name in ((results[1], "eager"), (results[2], "graph")):
+                for i, (a_, b_) in enumerate(zip(results[0], other)):
+                    assert torch.equal(a_, b_), f"trial {trial} (m = {m}) {name}: buffer {i} differs; program {prog}"
+        assert gemm_last_status() == 0
+    finally:
+        cuda_lib.nvfp4_gemm_tune_pdl(1)
