@@ -15,6 +15,11 @@
 // records a status word and every role leaves its loop, so a fault in the pipeline logic
 // surfaces as an error code rather than a hung device.
 //
+// Launches are programmatic dependent launches (see common.cuh): a kernel lets the one queued behind it be scheduled from its
+// first instruction and itself waits before it touches anything an earlier kernel may have written; a prepared weight is a
+// constant by contract and is streamed ahead of that wait.  nvfp4_gemm_launch_grouped multiplies one activation with several
+// prepared weights in one launch of the decode-sized kernel.
+//
 // This file holds the C entry points and the kernel choice; the kernels live in gemm_tile.cuh (one CTA per tile),
 // gemm_pair.cuh (CTA pairs, cta_group::2) and gemm_skinny.cuh (decode-sized batches, K ranges across a cluster),
 // all on the PTX wrappers of tc_ptx.cuh.  One translation unit, so that there is one status word.
