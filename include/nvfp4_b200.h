@@ -94,7 +94,8 @@ int nvfp4_quant_launch_impl(int impl, int variant, const void* x, int x_dtype, c
  * replaces helper.py:96-100 (get_nvfp4_global_scale).
  * `scratch` = 2 uint32 that must be zero before the first call; the kernel
  * leaves them zero again, so one scratch serves any number of calls issued in
- * stream order.  Concurrent calls need separate scratch.
+ * stream order.  Concurrent calls need separate scratch; so do launches recorded into different CUDA graphs that may be
+ * replayed at the same time, even when they were captured on one stream (see nvfp4_stream_capture_id).
  */
 int nvfp4_global_scale_launch(const void* x, int x_dtype, int64_t numel, float fp8_max, float* out,
                               uint32_t* scratch, void* stream);
@@ -258,6 +259,11 @@ int nvfp4_gemm_last_status(void* stream, uint32_t* status_host);
 int nvfp4_gemm_set_wait_limit_ns(uint64_t ns);
 int nvfp4_quant_fused_set_wait_limit_ns(uint64_t ns);
 
+/* *id_host = 0 while `stream` is not being captured into a CUDA graph, else the id of the capture.  Host bookkeeping: the
+ * scratch words of nvfp4_global_scale_launch / nvfp4_quant_fused_launch may be shared by launches that are ordered on one
+ * stream, but graphs captured one after the other on the same stream can be replayed at the same time on different
+ * streams, so every capture needs scratch of its own (the Python helpers key their scratch by this id). */
+int nvfp4_stream_capture_id(void* stream, unsigned long long* id_host);
 const char* nvfp4_status_string(int status);
 int nvfp4_abi_version(void);
 

@@ -20,7 +20,7 @@ EXPORTS = (
     "nvfp4_global_scale_launch", "nvfp4_global_scale_launch_static", "nvfp4_global_scale_static_max_bytes",
     "nvfp4_channel_sqnorm_launch", "nvfp4_channel_sqnorm_launch_strided", "nvfp4_gemm_peak_probe", "nvfp4_gemm_set_wait_limit_ns", "nvfp4_quant_fused_set_wait_limit_ns",
     "nvfp4_gemm_launch", "nvfp4_gemm_workspace_bytes", "nvfp4_gemm_prepare", "nvfp4_gemm_launch_prepared", "nvfp4_gemm_launch_grouped", "nvfp4_gemm_release", "nvfp4_gemm_last_status", "nvfp4_gemm_force_path", "nvfp4_gemm_tune", "nvfp4_gemm_tune_raster", "nvfp4_gemm_tune_pdl", "nvfp4_gemm_plan",
-    "nvfp4_status_string", "nvfp4_abi_version",
+    "nvfp4_status_string", "nvfp4_abi_version", "nvfp4_stream_capture_id",
 )
 
 _lib = None
@@ -75,6 +75,8 @@ def lib() -> ctypes.CDLL:
         L.nvfp4_gemm_prepare.argtypes = [vp, vp, i64, i64, vp]
         L.nvfp4_gemm_launch_prepared.restype = ci
         L.nvfp4_gemm_launch_prepared.argtypes = [vp, vp, vp, vp, vp, i64, vp, ctypes.c_size_t, vp]
+        L.nvfp4_stream_capture_id.restype = ci
+        L.nvfp4_stream_capture_id.argtypes = [vp, vp]
         L.nvfp4_gemm_launch_grouped.restype = ci
         L.nvfp4_gemm_launch_grouped.argtypes = [vp, ci, vp, vp, vp, vp, vp, i64, vp]
         L.nvfp4_gemm_release.restype = ci
@@ -155,24 +157,58 @@ def device_guard(device):
     return torch.cuda.device(device)
 
 
+def capture_id(stream: int) -> int:
+    """0 unless `stream` (a cudaStream_t as an integer) is being captured into a CUDA graph, else the capture's id."""
+    out = ctypes.c_ulonglong(0)
+    if lib().nvfp4_stream_capture_id(stream, ctypes.byref(out)) != 0:
+        return 0
+    return out.value
+
+
 class StreamScratch:
     """Small zero-initialised device buffers keyed by (device, stream): launches on one stream may share a scratch
-    (the kernels leave it zeroed), launches that may overlap need their own.  Holds at most `capacity` entries and
-    drops the least recently used one beyond that, so a process that keeps creating streams does not grow it without
-    bound (a dropped buffer goes back to torch's caching allocator, which only hands it out again in stream order)."""
+    (the kernels leave it zeroed), launches that may overlap need their own.  Holds at most `capacity` stream entries
+    and drops the least recently used one beyond that, so a process that keeps creating streams does not grow it
+    without bound (a dropped buffer goes back to torch's caching allocator, which only hands it out again in stream
+    order).
+
+    Launches recorded into a CUDA graph get a scratch per CAPTURE instead: graphs captured one after the other on the
+    same stream may be replayed at the same time on different streams.  Those buffers are taken from a few zeroed
+    spares that are set aside outside captures (a buffer created during a capture would add a fill node to the graph;
+    that is what happens when the spares run out) and are kept for the life of the process, since a graph that uses
+    one may be replayed at any time (8 or 16 bytes each)."""
+
+    SPARES = 8
 
     def __init__(self, words: int, capacity: int = 32):
         from collections import OrderedDict
 
         self.words, self.capacity, self._d = words, capacity, OrderedDict()
+        self._captures, self._spare = {}, {}
 
-    def get(self, device, stream: int):
+    def _zeros(self, device):
         import torch
 
+        return torch.zeros(self.words, dtype=torch.int32, device=device)
+
+    def get(self, device, stream: int):
+        on_gpu = getattr(device, "type", "cpu") == "cuda"
+        cap = capture_id(stream) if on_gpu else 0
+        if cap:
+            key = (device, cap, stream)      # a capture may span forked streams: one scratch per stream of it
+            buf = self._captures.get(key)
+            if buf is None:
+                spare = self._spare.get(device)
+                buf = self._captures[key] = spare.pop() if spare else self._zeros(device)
+            return buf
+        if on_gpu:
+            spare = self._spare.setdefault(device, [])
+            while len(spare) < self.SPARES:
+                spare.append(self._zeros(device))
         key = (device, stream)
         buf = self._d.get(key)
         if buf is None:
-            buf = self._d[key] = torch.zeros(self.words, dtype=torch.int32, device=device)
+            buf = self._d[key] = self._zeros(device)
             while len(self._d) > self.capacity:
                 self._d.popitem(last=False)
         else:

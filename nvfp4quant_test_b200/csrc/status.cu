@@ -26,3 +26,17 @@ extern "C" const char* nvfp4_status_string(int status) {
 }
 
 extern "C" int nvfp4_abi_version(void) { return 1; }
+
+// 0 while `stream` is not being captured into a CUDA graph, else the id of the capture (unique per capture sequence of the
+// process).  Host bookkeeping only: callers that hand out scratch buffers per stream use it to tell captures apart, because
+// graphs captured one after the other on the same stream may later be replayed at the same time on different streams.
+extern "C" int nvfp4_stream_capture_id(void* stream, unsigned long long* id_host) {
+    if (!id_host) return NVFP4_ERR_NULL_POINTER;
+    *id_host = 0;
+    cudaStreamCaptureStatus status = cudaStreamCaptureStatusNone;
+    unsigned long long id = 0;
+    const cudaError_t e = cudaStreamGetCaptureInfo(static_cast<cudaStream_t>(stream), &status, &id);
+    if (e != cudaSuccess) return static_cast<int>(e);
+    if (status == cudaStreamCaptureStatusActive) *id_host = id;
+    return NVFP4_OK;
+}

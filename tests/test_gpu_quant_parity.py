@@ -565,3 +565,34 @@ def test_quantizer_right_behind_the_global_scale_kernel_reads_the_new_scale(cuda
             got_w = K.scalesweep_weighted_mse_nvfp4_quant_impl(x, imp, buf2[1])
             for got, want in ((got_m, want_m), (got_w, want_w)):
                 assert torch.equal(got[0], want[0]) and torch.equal(got[1].view(torch.uint8), want[1].view(torch.uint8)), shape
+
+
+def test_global_scale_in_graphs_replayed_at_the_same_time(cuda_lib):
+    """Two CUDA graphs captured one after the other (torch captures on one and the same side stream), each with
+    several multi-block global-scale launches, replayed at the same time on two streams: the launches of one graph must
+    not share scratch words with the other's (helper.get_nvfp4_global_scale hands out scratch per capture), and an
+    eager call afterwards still finds its scratch zeroed."""
+    from nvfp4quant_test_b200 import helper as H
+
+    g = torch.Generator(device="cuda")
+    g.manual_seed(77)
+    xs = [torch.normal(0.0, float(i + 1), size=(96, 8192), generator=g, device="cuda", dtype=torch.bfloat16) for i in range(2)]
+    want = [x.abs().max().float() / (6 * 256.0) for x in xs]
+    graphs, outs = [], []
+    for x in xs:
+        H.get_nvfp4_global_scale(x, 256.0)
+        torch.cuda.synchronize()
+        graph = torch.cuda.CUDAGraph()
+        with torch.cuda.graph(graph):
+            out = [H.get_nvfp4_global_scale(x, 256.0)[0] for _ in range(6)]
+        graphs.append(graph), outs.append(out)
+    streams = [torch.cuda.Stream() for _ in graphs]
+    for _ in range(200):
+        for graph, s in zip(graphs, streams):
+            with torch.cuda.stream(s):
+                graph.replay()
+    torch.cuda.synchronize()
+    for out, w in zip(outs, want):
+        assert all(torch.equal(o, w) for o in out)
+    for x, w in zip(xs, want):
+        assert torch.equal(H.get_nvfp4_global_scale(x, 256.0)[0], w)

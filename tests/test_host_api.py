@@ -229,3 +229,9 @@ def test_bench_reference_arm_prints_one_schema_complete_line():
     assert d["cpu_baseline"]["kind"] == "port" and d["cpu_baseline"]["cores"] >= 1 and d["cpu_baseline"]["value"] == d["value"]
     assert d["e2e"] == {"value": d["value"], "unit": "GB/s", "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0}
     assert d["gpu_launches"] == 0 and d["steps"] == 1 and 0.01 < d["value"] < 50.0
+
+
+def test_capture_id_is_zero_without_a_capture():
+    from nvfp4quant_test_b200 import _lib
+
+    assert _lib.capture_id(0) == 0          # no GPU, or the default stream outside a capture
