@@ -757,3 +757,54 @@ def test_random_launch_chains_do_not_depend_on_dependent_launch(cuda_lib):
         assert gemm_last_status() == 0
     finally:
         cuda_lib.nvfp4_gemm_tune_pdl(1)
+
+
+def test_graphs_of_different_token_counts_replayed_at_the_same_time(cuda_lib):
+    """Three CUDA graphs of a few Llama-shaped layers (1 token: grouped decode-sized launches; 256 and 1024 tokens: tile
+    and CTA-pair kernels on forked streams, global-scale launches that go through scratch words) replayed at the same
+    time on three streams: every replay leaves the bits of the plain, eager run, and no bounded wait runs out."""
+    from nvfp4quant_test_b200 import helper as H
+    from nvfp4quant_test_b200 import llama_stack as LS
+    from nvfp4quant_test_b200.kernels.kernel_gemm import gemm_last_status
+
+    dev = torch.device("cuda", torch.cuda.current_device())
+    calib = LS.make_calibration(dev)
+    importance = {k: H.channel_square_norm(x) for k, x in calib.items()}
+    qlayers = [LS.quantize_layer(LS.make_layer(i, dev), importance) for i in range(3)]
+    wscales = [LS.stack_weight_scales(q) for q in qlayers]
+    prepared = [LS.prepare_layer(q) for q in qlayers]
+    side = [torch.cuda.Stream(device=dev) for _ in range(4)]
+    items = []
+    for tokens in (1, 256, 1024):
+        gen = torch.Generator(device=dev)
+        gen.manual_seed(tokens)
+        acts = {k: torch.normal(0.0, 1.0, size=(tokens, k), generator=gen, device=dev, dtype=torch.bfloat16) for k in calib}
+        if tokens <= LS.GROUPED_MAX_TOKENS:
+            layers = [LS.DecodeLayer(q, ws, pw, tokens, dev) for q, ws, pw in zip(qlayers, wscales, prepared)]
+
+            def fn(layers=layers, acts=acts):
+                return [layer(acts) for layer in layers][-1]
+        else:
+            def fn(acts=acts):
+                return [LS.layer_gemms(q, acts, {}, ws, side, pw) for q, ws, pw in zip(qlayers, wscales, prepared)][-1]
+        try:
+            assert cuda_lib.nvfp4_gemm_tune_pdl(0) == 0
+            truth = {k: v.clone() for k, v in fn().items()}
+        finally:
+            cuda_lib.nvfp4_gemm_tune_pdl(1)
+        fn()
+        torch.cuda.synchronize()
+        graph = torch.cuda.CUDAGraph()
+        with torch.cuda.graph(graph):
+            out = fn()
+        items.append((graph, out, truth, fn, acts))      # fn / acts own the buffers the graph points into
+    streams = [torch.cuda.Stream(device=dev) for _ in items]
+    for _ in range(60):
+        for (graph, *_rest), s in zip(items, streams):
+            with torch.cuda.stream(s):
+                graph.replay()
+    torch.cuda.synchronize()
+    assert gemm_last_status() == 0
+    for graph, out, truth, _fn, _acts in items:
+        for name, want in truth.items():
+            assert torch.equal(out[name].view(torch.int16), want.view(torch.int16)), name
