@@ -25,7 +25,9 @@ extern "C" const char* nvfp4_status_string(int status) {
     return "unknown status";
 }
 
-extern "C" int nvfp4_abi_version(void) { return 1; }
+// 2: grouped GEMM launch, one-call quantizer chain, strided importance reduction, capture id (additions only: every
+// version-1 entry point keeps its signature and meaning)
+extern "C" int nvfp4_abi_version(void) { return 2; }
 
 // 0 while `stream` is not being captured into a CUDA graph, else the id of the capture (unique per capture sequence of the
 // process).  Host bookkeeping only: callers that hand out scratch buffers per stream use it to tell captures apart, because
